@@ -1,0 +1,52 @@
+"""Build the CUDA library in-tree for sm_100a with nvcc (no JIT cache, no torch extension).
+
+`python -m megakernels_b200.build` compiles `csrc/mk_api.cu` into `libmk_b200.so` next to this
+file.  The reference JIT-compiles its extension at import time instead
+(`qwen3.5-0.8b/qwen_mk/_ext.py:12-30`); here the library is prebuilt so that it can be carried to
+a machine and loaded without a compiler.  `MK_B200_DEFINES` adds `-D...` flags for A/B builds, the
+counterpart of the reference's `QWEN_MK_DEFINES`.
+"""
+
+import os
+import shlex
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, "libmk_b200.so")
+SOURCES = ["mk_api.cu"]
+HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", os.path.join("..", "..", "include", "mk_b200.h")]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
+              "-shared", "-Xcompiler", "-fPIC"]
+
+
+def stale():
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    csrc = os.path.join(HERE, "csrc")
+    return any(os.path.getmtime(os.path.join(csrc, f)) > t for f in SOURCES + HEADERS)
+
+
+def build(force=False, verbose=False):
+    """Compile if the library is missing or older than its sources.  Returns the library path."""
+    if not force and not stale():
+        return LIB
+    nvcc = os.environ.get("NVCC", "nvcc")
+    csrc = os.path.join(HERE, "csrc")
+    cmd = [nvcc, *NVCC_FLAGS, *shlex.split(os.environ.get("MK_B200_DEFINES", "")), "-o", LIB,
+           *[os.path.join(csrc, s) for s in SOURCES]]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+        print(" ".join(cmd))
+    out = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose:
+        print(out.stdout, out.stderr)
+    if out.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + out.stdout + out.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

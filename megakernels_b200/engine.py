@@ -1,0 +1,338 @@
+"""Python driver for the B200 decode megakernel: packs weights, owns state, launches steps.
+
+The class keeps the interface of the reference's `Megakernel`
+(`qwen3.5-0.8b/qwen_mk/engine.py:49-327`): the same constructor arguments, `run`, `prefill`,
+`generate`, `reset`, and the attributes its session, benchmark and test code read (`cfg`, `grid`,
+`pos`, `epoch`, `conv_hist`, `state`, `state_bak`, `k_cache`, `v_cache`, `weight_bytes`,
+`last_step_ns`, `embed`, `final_norm`).  Differences, all additions:
+
+* `model` may be a `(Config, weights dict)` pair instead of a checkpoint path, because no
+  checkpoint can be downloaded where this library is tested;
+* `quant="int8"` is per output channel (see `quant.py`) and covers the embedding table;
+* the KV cache is paged (`KV_BLOCK` positions per page, `block_table` maps logical to physical
+  pages) and its element type is selectable (`kv_dtype`);
+* PyTorch only allocates device memory and provides the stream; every launch goes through the C
+  ABI in `include/mk_b200.h`.
+"""
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from .config import Config
+from .quant import quantize_int8_rows
+
+# Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
+# of the per-launch output buffers.
+MAX_STEPS_PER_LAUNCH = 1024
+PF_BYTES = 0
+
+
+def rope_tables(cfg, max_seq, device):
+    """cos / sin [max_seq, rotary_dim / 2] in fp32 (definition: `qwen_mk/reference.py:18-23`)."""
+    idx = torch.arange(0, cfg.rotary_dim, 2, dtype=torch.int64).float()
+    inv_freq = 1.0 / (cfg.rope_theta ** (idx / cfg.rotary_dim))
+    ang = torch.arange(max_seq, dtype=torch.float32)[:, None] * inv_freq[None, :]
+    return ang.cos().to(device), ang.sin().to(device)
+
+
+class Megakernel:
+    def __init__(self, model, max_seq=8192, device="cuda", pf_bytes=PF_BYTES, quant="bf16", mtp=False,
+                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000):
+        if quant not in ("bf16", "int8"):
+            raise ValueError(f"quant must be 'bf16' or 'int8', got {quant!r}")
+        if kv_dtype not in ("bf16", "fp32"):
+            raise ValueError(f"kv_dtype must be 'bf16' or 'fp32', got {kv_dtype!r}")
+        if mtp:
+            raise NotImplementedError("the MTP draft head is not part of this build yet")
+        if not torch.cuda.is_available():
+            raise RuntimeError("the decode megakernel needs a CUDA device; there is no CPU path")
+        self.lib = _lib.load()
+        self.quant, self.kv_dtype, self.pf_bytes = quant, kv_dtype, pf_bytes
+        self.spin_limit_ns = int(spin_limit_ms * 1e6)
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device(device.type, torch.cuda.current_device())
+        torch.cuda.set_device(device)
+        self.device = device
+        if isinstance(model, (tuple, list)):
+            self.cfg, w = model
+        else:
+            from . import weights as _weights
+            self.cfg, w = _weights.load(model, "cpu")
+        cfg = self.cfg
+        assert isinstance(cfg, Config) or hasattr(cfg, "layer_types")
+        self._check_shape(cfg)
+        self.KV_BLOCK = _lib.query("KV_BLOCK")
+        self.max_seq = (max_seq + self.KV_BLOCK - 1) // self.KV_BLOCK * self.KV_BLOCK
+        self.grid = torch.cuda.get_device_properties(device).multi_processor_count
+        self._keep = []   # every tensor whose address the kernel holds
+
+        def keep(t):
+            t = t.contiguous()
+            self._keep.append(t)
+            return t.data_ptr()
+
+        def f32(t):
+            return keep(t.to(device=device, dtype=torch.float32))
+
+        q8 = quant == "int8"
+
+        def mat(t):
+            """A GEMV weight in the kernel's format: (address, scale address)."""
+            t = t.to(device)
+            if q8:
+                q, s = quantize_int8_rows(t)
+                return keep(q), keep(s)
+            return keep(t.to(torch.bfloat16)), 0
+
+        kvt = torch.float32 if kv_dtype == "fp32" else torch.bfloat16
+        n_blocks = self.max_seq // self.KV_BLOCK
+        ring = _lib.query("CONV_RING")
+        zeros = lambda *shape, dtype=torch.float32: torch.zeros(*shape, device=device, dtype=dtype)
+        self.conv_hist, self.state, self.state_bak, self.k_cache, self.v_cache = [], [], [], [], []
+        F = _lib.LAYER_FIELDS
+        layer_vals = []
+        for i, kind in enumerate(cfg.layer_types):
+            m = f"layers.{i}."
+            rec = dict.fromkeys(F, 0)
+            gu = torch.stack([w[m + "mlp.gate_proj.weight"], w[m + "mlp.up_proj.weight"]], dim=1).reshape(-1, cfg.hidden)
+            rec["w_gu"], rec["s_gu"] = mat(gu)
+            rec["w_down"], rec["s_down"] = mat(w[m + "mlp.down_proj.weight"])
+            rec["in_norm"] = f32(w[m + "input_layernorm.weight"])
+            rec["post_norm"] = f32(w[m + "post_attention_layernorm.weight"])
+            if kind == "linear_attention":
+                p = m + "linear_attn."
+                w_in = torch.cat([w[p + "in_proj_qkv.weight"], w[p + "in_proj_z.weight"],
+                                  w[p + "in_proj_b.weight"], w[p + "in_proj_a.weight"]])
+                rec["w_in"], rec["s_in"] = mat(w_in)
+                rec["w_out"], rec["s_out"] = mat(w[p + "out_proj.weight"])
+                rec["conv_w"] = f32(w[p + "conv1d.weight"].reshape(-1, cfg.conv_k))
+                rec["A_log"] = f32(w[p + "A_log"])
+                rec["dt_bias"] = f32(w[p + "dt_bias"])
+                rec["gdn_norm"] = f32(w[p + "norm.weight"])
+                hist = zeros(cfg.conv_dim, ring)
+                st = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)   # [head][v][k]: the oracle's transposed
+                bak = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)
+                self.conv_hist.append(hist)
+                self.state.append(st)
+                self.state_bak.append(bak)
+                rec["conv_hist"], rec["state"], rec["state_bak"] = keep(hist), keep(st), keep(bak)
+                rec["kind"] = 0
+            else:
+                p = m + "self_attn."
+                w_in = torch.cat([w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"]])
+                rec["w_in"], rec["s_in"] = mat(w_in)
+                rec["w_out"], rec["s_out"] = mat(w[p + "o_proj.weight"])
+                rec["q_norm"] = f32(w[p + "q_norm.weight"])
+                rec["k_norm"] = f32(w[p + "k_norm.weight"])
+                kc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+                vc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+                self.k_cache.append(kc)
+                self.v_cache.append(vc)
+                rec["k_cache"], rec["v_cache"] = keep(kc), keep(vc)
+                rec["kind"] = 1
+            layer_vals += [rec[f] for f in F]
+
+        cos, sin = rope_tables(cfg, self.max_seq, device)
+        u64 = dict(device=device, dtype=torch.int64)
+        proj_max = max(cfg.gdn_in_rows, cfg.attn_in_rows)
+        mix = cfg.n_heads * cfg.head_dim
+        # flag-in-data activation buffers: (epoch << 32) | fp32 bits
+        self.ll = [torch.zeros(n, **u64) for n in (cfg.hidden, proj_max, mix, cfg.intermediate, 2 * self.grid)]
+        max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
+        self.attn_part = zeros(cfg.n_kv_heads * max_splits * part_stride)
+        self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
+        self.block_table = torch.arange(n_blocks, device=device, dtype=torch.int32)
+        self.status = zeros(4, dtype=torch.int32)
+
+        self.embed = w["embed_tokens.weight"].to(device)
+        self.final_norm = w["norm.weight"].to(device)
+        embed_ptr, embed_scale = mat(self.embed)
+        if "lm_head.weight" in w:
+            lm_ptr, lm_scale = mat(w["lm_head.weight"])
+        else:
+            lm_ptr, lm_scale = embed_ptr, embed_scale
+        g = dict.fromkeys(_lib.GLOBAL_FIELDS, 0)
+        g.update(embed=embed_ptr, embed_scale=embed_scale, lm_head=lm_ptr, lm_scale=lm_scale,
+                 final_norm=f32(self.final_norm), rope_cos=keep(cos), rope_sin=keep(sin),
+                 xl=keep(self.ll[0]), projl=keep(self.ll[1]), mixl=keep(self.ll[2]), actl=keep(self.ll[3]),
+                 lml=keep(self.ll[4]), attn_part=keep(self.attn_part), attn_flag=keep(self.attn_flag),
+                 block_table=keep(self.block_table), status=keep(self.status))
+        del w
+        self.mtp = self.draft_ids = None
+        self.draft_vocab = 0
+
+        desc = _lib.ModelDesc(shape=_lib.MK_SHAPE_QWEN35_08B, n_layers=cfg.n_layers, vocab=cfg.vocab,
+                              max_seq=self.max_seq, quant=_lib.MK_QUANT[quant], kv_dtype=_lib.MK_KV[kv_dtype],
+                              draft_vocab=0, device=device.index)
+        self._h = ctypes.c_void_p()
+        _lib.check(self.lib.mk_create(ctypes.byref(desc), ctypes.byref(self._h)))
+        lv, gv = _lib.i64_array(layer_vals), _lib.i64_array([g[f] for f in _lib.GLOBAL_FIELDS])
+        _lib.check(self.lib.mk_set_params(self._h, lv, len(lv), None, 0, gv, len(gv)))
+        self.weight_bytes = self._weight_bytes()
+        self.last_step_ns = []
+        self.launches = 0
+        self.reset()
+
+    # ------------------------------------------------------------------------------------------
+    @staticmethod
+    def _check_shape(c):
+        want = dict(hidden=1024, intermediate=3584, n_heads=8, n_kv_heads=2, head_dim=256, rotary_dim=64,
+                    lin_heads=16, lin_k_dim=128, lin_v_dim=128, conv_k=4)
+        bad = {k: getattr(c, k) for k, v in want.items() if getattr(c, k) != v}
+        if bad:
+            raise ValueError(f"this build only has the 0.8B hybrid shape {want}; got {bad}")
+        if abs(c.eps - 1e-6) > 1e-12:
+            raise ValueError("rms_norm_eps must be 1e-6")
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mk_destroy(h)
+            self._h = None
+
+    def _weight_bytes(self):
+        """Bytes of weights streamed per decode step: (layers, LM head)."""
+        c = self.cfg
+        per = {"linear_attention": c.gdn_in_rows * c.hidden + c.hidden * c.lin_heads * c.lin_v_dim,
+               "full_attention": c.attn_in_rows * c.hidden + c.hidden * c.n_heads * c.head_dim}
+        mlp = 3 * c.intermediate * c.hidden
+        b = 1 if self.quant == "int8" else 2
+        return int(sum(per[t] + mlp for t in c.layer_types) * b), int(c.vocab * c.hidden * b)
+
+    def state_bytes(self):
+        """Recurrent-state bytes read plus written per decode step."""
+        c = self.cfg
+        return 2 * 4 * len(self.state) * c.lin_heads * c.lin_k_dim * c.lin_v_dim
+
+    def kv_bytes_per_pos(self):
+        c = self.cfg
+        return len(self.k_cache) * 2 * c.n_kv_heads * c.head_dim * (4 if self.kv_dtype == "fp32" else 2)
+
+    def reset(self):
+        """Start a new sequence (cached K/V need no clearing: positions are rewritten)."""
+        for t in self.conv_hist + self.state + self.ll:
+            t.zero_()
+        self.attn_flag.zero_()
+        self.status.zero_()
+        self.epoch = 1   # the buffers are zero, so epoch 0 never looks ready
+        self.pos = 0
+
+    def set_block_table(self, table):
+        """Map logical KV pages to physical pages (a permutation of range(max_seq / KV_BLOCK))."""
+        t = torch.as_tensor(table, dtype=torch.int32, device=self.device)
+        if t.shape != self.block_table.shape or sorted(t.tolist()) != list(range(len(t))):
+            raise ValueError("block table must be a permutation of all pages")
+        self.block_table.copy_(t)
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def run(self, tokens, n_generate=1, temperature=0.0, seed=0, stop_ids=(), return_logits=False, prof=None,
+            prof_step=0, timing=False, all_logits=False, track_mtp=False, return_resid=False):
+        """Feed `tokens`, then let the model continue for up to `n_generate` predicted tokens.
+
+        One kernel launch, exactly as the reference's `run` (`qwen_mk/engine.py:198-250`): prompt
+        tokens are fed one per step, each predicted token is fed back on the GPU; a predicted stop
+        id ends the launch and is reported but not fed.  Returns the predicted ids, plus their
+        logits with `return_logits`, or the logits of every fed token with `all_logits`.
+        """
+        tokens = [int(t) for t in tokens]
+        if not tokens:
+            raise ValueError("need at least one input token")
+        if n_generate < 1:
+            raise ValueError("n_generate must be >= 1")
+        n_forced = len(tokens)
+        n_steps = n_forced + n_generate - 1
+        if self.pos + n_steps > self.max_seq:
+            raise ValueError(f"sequence would exceed max_seq={self.max_seq}")
+        dev = self.device
+        forced = torch.tensor(tokens, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
+        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=dev)
+        out = torch.zeros(n_steps, dtype=torch.int64, device=dev)
+        info = torch.zeros(8, dtype=torch.int32, device=dev)
+        ts = torch.zeros(n_steps + 1, dtype=torch.int64, device=dev) if timing else None
+        lm_from = 0 if all_logits else n_forced - 1
+        logits = torch.empty(n_steps, self.cfg.vocab, device=dev) if return_logits or all_logits else None
+        resid = torch.empty(n_steps, self.cfg.hidden, device=dev) if (track_mtp or return_resid) else None
+        ptr = lambda t: t.data_ptr() if t is not None else 0
+        a = _lib.LaunchArgs(forced=forced.data_ptr(), n_forced=n_forced, n_steps=n_steps, lm_from=lm_from,
+                            start_pos=self.pos, epoch_base=self.epoch, seed=seed & 0xFFFFFFFF,
+                            inv_temperature=1.0 / temperature if temperature > 0 else 0.0, n_stop=len(stop_ids),
+                            stop_ids=stops.data_ptr(), tokens_out=out.data_ptr(), logits_out=ptr(logits),
+                            resid_out=ptr(resid), step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof),
+                            prof_step=prof_step, grid=self.grid, pf_bytes=self.pf_bytes,
+                            spin_limit_ns=self.spin_limit_ns)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(self.lib.mk_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+        self.launches += 1
+        done, epoch, _ = info[:3].tolist()          # synchronises with the launch
+        if int(self.status[0]) != 0:
+            where = ctypes.c_int32()
+            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
+        self.pos += done
+        self.epoch = epoch & 0xFFFFFFFF
+        if self.epoch > 0xFFFF0000:
+            raise RuntimeError("epoch counter exhausted; call reset()")
+        if timing:
+            t = ts[: done + 1].cpu()
+            self.last_step_ns = (t[1:] - t[:-1]).tolist()
+        self.last_resid = resid[:done] if resid is not None else None
+        ids = (0xFFFFFFFF - (out[n_forced - 1: done] & 0xFFFFFFFF)).tolist()
+        if all_logits:
+            return ids, logits[:done]
+        if return_logits:
+            return ids, logits[n_forced - 1: done]
+        return ids
+
+    def prefill(self, tokens, chunk=512):
+        """Feed all but the last token; returns the last one (`qwen_mk/engine.py:296-301`)."""
+        tokens = list(tokens)
+        for i in range(0, len(tokens) - 1, chunk):
+            self.run(tokens[i: min(i + chunk, len(tokens) - 1)])
+        return tokens[-1]
+
+    def generate(self, prompt_ids, max_new_tokens=256, temperature=0.0, seed=0, stop_ids=(), chunk=16, spec=False):
+        """Yield generated ids (`qwen_mk/engine.py:307-327`).  The state ends exactly after the last
+        fed token, so a conversation can continue by passing the next prompt."""
+        if spec:
+            raise NotImplementedError("speculative decoding needs the MTP head, which this build lacks")
+        last = self.prefill(prompt_ids)
+        produced = 0
+        while produced < max_new_tokens:
+            n = min(chunk, max_new_tokens - produced, MAX_STEPS_PER_LAUNCH)
+            ids = self.run([last], n_generate=n, temperature=temperature, seed=seed, stop_ids=stop_ids)
+            for t in ids:
+                yield t
+                produced += 1
+            if ids and ids[-1] in stop_ids:
+                return
+            last = ids[-1]
+        self.pending = last
+
+    # ---- state access in the oracle's layouts (for tests, snapshots and state import) -----------
+    def deltanet_state(self, i):
+        """Recurrent state of the i-th DeltaNet layer as [head][k][v] (the reference decoder's layout,
+        `qwen_mk/reference.py:54`; the kernel stores [head][v][k])."""
+        return self.state[i].transpose(1, 2).contiguous()
+
+    def kv_rows(self, i, n):
+        """K, V of the i-th attention layer for positions [0, n) as [kv_head, n, head_dim] fp32."""
+        bt = self.block_table.long()
+        pos = torch.arange(n, device=self.device)
+        blk, off = bt[pos // self.KV_BLOCK], pos % self.KV_BLOCK
+        k = self.k_cache[i][blk, :, off].transpose(0, 1).float()
+        v = self.v_cache[i][blk, :, off].transpose(0, 1).float()
+        return k, v
+
+    def snapshot(self):
+        """Copy of the recurrent state (conv history + DeltaNet state) and the position."""
+        return [t.clone() for t in self.conv_hist + self.state], self.pos
+
+    def restore(self, snap):
+        tensors, pos = snap
+        for dst, src in zip(self.conv_hist + self.state, tensors):
+            dst.copy_(src)
+        self.pos = pos
