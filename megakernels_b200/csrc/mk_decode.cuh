@@ -54,7 +54,13 @@ struct Ctx {
     u64 limit_ns;
     int* status;
     bool dead;          // this thread saw a wait run out
+    u64* prof;          // this CTA's timestamp rows for the step being profiled, or null
 };
+
+// Per-op timestamps (enter, inputs staged, work done, outputs published), consumer thread 0 only.
+__device__ __forceinline__ void prof_stamp(const Ctx& c, int op, int field) {
+    if (c.prof && c.tid == 0) c.prof[(size_t)op * PROF_FIELDS + field] = globaltimer();
+}
 
 struct Spin {
     uint32_t it = 0;
@@ -369,7 +375,7 @@ __device__ __forceinline__ void load_embedding(const Params& P, int token, int t
 // Task t < GDN_TASKS: head t / 8, value columns [16 * (t % 8), +16).  Warp w owns value column w of the
 // slice; a lane holds 4 consecutive key indices of that column's state row.
 template <class S>
-__device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out) {
+__device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::GDN_SLICE == NCW && S::LIN_DK == 128, "one warp per value column, 4 keys per lane");
     constexpr int SL = S::LIN_DV / S::GDN_SLICE;  // slices per head
     if (c.cta >= S::GDN_TASKS) return;
@@ -401,6 +407,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
         qkv_s[c.tid] = ll_wait(c, P.projl + off, e_proj, W_PROJ);
     }
     consumer_sync();
+    prof_stamp(c, op, 1);
     const float4 q4 = *reinterpret_cast<const float4*>(qkv_s + 4 * c.lane);
     const float4 k4 = *reinterpret_cast<const float4*>(qkv_s + S::LIN_DK + 4 * c.lane);
     const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
@@ -421,6 +428,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     s3 = fmaf(kw, delta, s3);
     *reinterpret_cast<float4*>(srow) = make_float4(s0, s1, s2, s3);
     const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
+    prof_stamp(c, op, 2);
     __threadfence();  // conv history of the q/k channels is read by sibling CTAs in the next steps
     if (c.lane == 0) ll_store(P.mixl + h * S::LIN_DV + vcol, e_out, o);
     consumer_sync();  // the scratch aliases the GEMV input vector that the next prologue writes
@@ -464,7 +472,7 @@ __device__ __forceinline__ void store1(void* base, size_t elem, float v) {
 // normalised output itself; otherwise it writes (acc, m, l) partials and raises a flag, and the
 // split-0 task of each KV head merges all partials in split order.
 template <class S, bool KVF32>
-__device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out) {
+__device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
     const int n = pos + 1;
     const int max_splits = min(c.grid / S::NKV, MAX_SPLITS);
@@ -538,6 +546,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             vnew_s[d + 1] = round_kv<KVF32>(vb);
         }
         consumer_sync();
+        prof_stamp(c, op, 1);
     }
     const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
     auto kv_elem = [&](int p) -> size_t {
@@ -634,6 +643,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         }
     }
     u64* out = P.mixl + (size_t)(g * S::QPK) * S::HD;
+    prof_stamp(c, op, 2);
     if (nsplit == 1) {
         __threadfence();  // the appended K/V row is read by other CTAs in later steps
         ll_store(out + (2 * hp) * S::HD + d, e_out, acc0 / stat_s[S::QPK + 2 * hp]);
@@ -708,7 +718,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
-    c.cons_n = 0; c.red_n = 0; c.dead = false;
+    c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr;
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
     if (c.tid == 0) {
@@ -760,6 +770,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     for (int s = 0; s < A.n_steps; s++) {
         const uint32_t e0 = A.epoch_base + (uint32_t)s * (uint32_t)OPS;   // epoch of layer 0's op A
         const int pos = A.start_pos + s;
+        c.prof = (A.prof && s == A.prof_step) ? A.prof + (size_t)c.cta * PROF_MAX_OPS * PROF_FIELDS : nullptr;
         if (c.cta == 0 && c.tid == 0 && A.step_ts) A.step_ts[s] = globaltimer();
         int token;
         if (s < A.n_forced) {
@@ -789,6 +800,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             const bool attn = L.kind != 0;
             // ---- A: in-projection
             {
+                const int op = l * OPS_PER_LAYER;
+                prof_stamp(c, op, 0);
                 int r0, r1;
                 cta_rows(attn ? S::ATT_IN : S::GDN_IN, 1, c.cta, c.grid, r0, r1);
                 const int nrows = r1 - r0;
@@ -796,18 +809,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 if (Q8 && c.tid < nrows) sc = L.s_in[r0 + c.tid];
                 if (l > 0) ll_wait2(c, P.xl + 2 * c.tid, eA - 1, W_X, x0, x1);
                 stage_rmsnorm<S, Q8>(c, x0, x1, L.in_norm);
+                prof_stamp(c, op, 1);
                 float* out_s = c.sm.out_s;
                 gemv_stream<S::HID, Q8, 1, Q8 ? 2 : 1>(c, r0, r1, [&](int row, int, float v) {
                     if (c.lane == 0) out_s[row - r0] = v;
                 });
                 consumer_sync();
+                prof_stamp(c, op, 2);
                 if (c.tid < nrows) ll_store(P.projl + r0 + c.tid, eA, out_s[c.tid] * sc);
+                prof_stamp(c, op, 3);
             }
             // ---- B: mixer
-            if (attn) attn_op<S, KVF32>(c, P, L, pos, eA, eB);
-            else gdn_op<S>(c, P, L, pos, eA, eB);
+            prof_stamp(c, l * OPS_PER_LAYER + 1, 0);
+            if (attn) attn_op<S, KVF32>(c, P, L, pos, eA, eB, l * OPS_PER_LAYER + 1);
+            else gdn_op<S>(c, P, L, pos, eA, eB, l * OPS_PER_LAYER + 1);
+            prof_stamp(c, l * OPS_PER_LAYER + 1, 3);
             // ---- C: out-projection + residual
             {
+                const int op = l * OPS_PER_LAYER + 2;
+                prof_stamp(c, op, 0);
                 const int nrows = xr1 - xr0;
                 float sc = 1.f;
                 if (Q8 && c.tid < nrows) sc = L.s_out[xr0 + c.tid];
@@ -837,20 +857,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                     c.sm.xs[xs_index<Q8>(k + 3)] = m[3] * inv * gw.w * silu_f(z[3]);
                 }
                 consumer_sync();
+                prof_stamp(c, op, 1);
                 float* out_s = c.sm.out_s;
                 gemv_stream<S::MIX, Q8, 2, 1>(c, xr0, xr1, [&](int row, int seg, float v) {
                     if (c.lane == 0) out_s[(row - xr0) * 2 + seg] = v;
                 });
                 consumer_sync();
+                prof_stamp(c, op, 2);
                 if (c.tid < nrows) {
                     const float y = (out_s[2 * c.tid] + out_s[2 * c.tid + 1]) * sc;
                     const float xn = c.sm.xown[c.tid] + y;
                     c.sm.xown[c.tid] = xn;
                     ll_store(P.xl + xr0 + c.tid, eC, xn);
                 }
+                prof_stamp(c, op, 3);
             }
             // ---- D: gate/up + SwiGLU
             {
+                const int op = l * OPS_PER_LAYER + 3;
+                prof_stamp(c, op, 0);
                 int r0, r1;
                 cta_rows(2 * S::INTER, 2, c.cta, c.grid, r0, r1);
                 const int npairs = (r1 - r0) / 2;
@@ -858,18 +883,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 if (Q8 && c.tid < npairs) sc = *reinterpret_cast<const float2*>(L.s_gu + r0 + 2 * c.tid);
                 ll_wait2(c, P.xl + 2 * c.tid, eC, W_X, x0, x1);
                 stage_rmsnorm<S, Q8>(c, x0, x1, L.post_norm);
+                prof_stamp(c, op, 1);
                 float* out_s = c.sm.out_s;
                 gemv_stream<S::HID, Q8, 1, Q8 ? 2 : 1>(c, r0, r1, [&](int row, int, float v) {
                     if (c.lane == 0) out_s[row - r0] = v;
                 });
                 consumer_sync();
+                prof_stamp(c, op, 2);
                 if (c.tid < npairs) {
                     const float gate = out_s[2 * c.tid] * sc.x, up = out_s[2 * c.tid + 1] * sc.y;
                     ll_store(P.actl + r0 / 2 + c.tid, eD, silu_f(gate) * up);
                 }
+                prof_stamp(c, op, 3);
             }
             // ---- E: down-projection + residual
             {
+                const int op = l * OPS_PER_LAYER + 4;
+                prof_stamp(c, op, 0);
                 const int nrows = xr1 - xr0;
                 float sc = 1.f;
                 if (Q8 && c.tid < nrows) sc = L.s_down[xr0 + c.tid];
@@ -880,12 +910,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                     c.sm.xs[xs_index<Q8>(k + 1)] = b;
                 }
                 consumer_sync();
+                prof_stamp(c, op, 1);
                 float* out_s = c.sm.out_s;
                 constexpr int KS = Q8 ? 2 : 4;   // bf16 rows are 7 KB: 4 per chunk, so 4 warps share a row
                 gemv_stream<S::INTER, Q8, KS, 1>(c, xr0, xr1, [&](int row, int seg, float v) {
                     if (c.lane == 0) out_s[(row - xr0) * KS + seg] = v;
                 });
                 failed = consumer_any(c.dead);
+                prof_stamp(c, op, 2);
                 if (c.tid < nrows) {
                     float y = 0.f;
 #pragma unroll
@@ -896,6 +928,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                     ll_store(P.xl + xr0 + c.tid, eE, xn);
                     if (A.resid_out && l == P.n_layers - 1) A.resid_out[(size_t)s * S::HID + xr0 + c.tid] = xn;
                 }
+                prof_stamp(c, op, 3);
             }
             if (failed) break;
         }
@@ -903,10 +936,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         // ---- LM head
         if (s >= A.lm_from) {
             const uint32_t eL = e0 + (uint32_t)OPS - 1;
+            const int op = P.n_layers * OPS_PER_LAYER;
+            prof_stamp(c, op, 0);
             const int nrows = lr1 - lr0;
             if (Q8) for (int i = c.tid; i < nrows; i += NCT) c.sm.scale_s[i] = P.lm_scale[lr0 + i];
             ll_wait2(c, P.xl + 2 * c.tid, eL - 1, W_X, x0, x1);
             stage_rmsnorm<S, Q8>(c, x0, x1, P.final_norm);
+            prof_stamp(c, op, 1);
             u64 best = 0;
             float* logits = A.logits_out ? A.logits_out + (size_t)s * P.vocab : nullptr;
             const float invT = A.inv_temperature;
@@ -925,12 +961,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             });
             if (c.lane == 0) c.sm.best_s[c.warp] = best;
             failed = consumer_any(c.dead);
+            prof_stamp(c, op, 2);
             if (c.tid == 0) {
                 u64 b = 0;
                 for (int i = 0; i < NCW; i++) b = c.sm.best_s[i] > b ? c.sm.best_s[i] : b;
                 ll_store_bits(P.lml + 2 * c.cta, eL, (uint32_t)(b >> 32));
                 ll_store_bits(P.lml + 2 * c.cta + 1, eL, (uint32_t)b);
             }
+            prof_stamp(c, op, 3);
             consumer_sync();   // best_s is read by thread 0 above before anyone reuses it
             if (failed) break;
         }

@@ -287,6 +287,12 @@ class Megakernel:
             return ids, logits[n_forced - 1: done]
         return ids
 
+    def prof_buffer(self):
+        """Zeroed timestamp buffer for `run(prof=...)`: [grid, PROF_MAX_OPS, PROF_FIELDS] GPU nanoseconds
+        (op entered, inputs staged, work done, outputs published), as `qwen_mk/engine.py:303-305`."""
+        return torch.zeros(self.grid, _lib.query("PROF_MAX_OPS"), _lib.query("PROF_FIELDS"), dtype=torch.int64,
+                           device=self.device)
+
     def prefill(self, tokens, chunk=512):
         """Feed all but the last token; returns the last one (`qwen_mk/engine.py:296-301`)."""
         tokens = list(tokens)

@@ -1,6 +1,6 @@
 """Weight-only quantisers for the decode kernel.
 
-int8 per output channel: one fp32 scale per row, `scale = absmax(row) / 127`, symmetric,
+int8 per output channel: one fp32 scale per row, `scale = absmax(row) * fl32(1/127)`, symmetric,
 `q = round(w / scale)` in [-127, 127].  The kernel stores `q + 128` as an unsigned byte so that
 a byte-permute can splice it into the mantissa of 2^23 and one subtraction recovers `q` exactly.
 
@@ -13,6 +13,7 @@ the packed bytes to the kernel, and check the kernel against a decoder that runs
 
 import torch
 
+INV_127 = float(torch.tensor(1.0 / 127.0, dtype=torch.float32))
 ROW_SLICE = 16384  # rows per pass, so the LM head never needs a multi-GB fp32 temporary
 
 
@@ -23,7 +24,9 @@ def quantize_int8_rows(w):
     scale = torch.empty(R, dtype=torch.float32, device=w.device)
     for r in range(0, R, ROW_SLICE):
         blk = w[r: r + ROW_SLICE].float()
-        s = (blk.abs().amax(dim=1) / 127.0).clamp_min(1e-12)
+        # absmax * fl(1/127), not absmax / 127: CUDA kernels turn a division by a scalar into a
+        # multiplication by its reciprocal, and the scales must not depend on the device
+        s = (blk.abs().amax(dim=1) * INV_127).clamp_min(1e-12)
         scale[r: r + ROW_SLICE] = s
         q[r: r + ROW_SLICE] = (torch.round(blk / s[:, None]).clamp_(-127, 127) + 128).to(torch.uint8)
     return q, scale
