@@ -161,6 +161,13 @@ int64_t mk_query(int what);
  * bandwidth is the denominator sanity check.  Replaces common/bw.cu:10-17,42-83. */
 int mk_bw_probe(uint64_t src, int64_t bytes, int mode, uint64_t sink, int device, void* stream);
 
+/* The kernel's work partition, exposed so that packers and tests can reproduce it on the host:
+ * rows [*r0, *r1) of a `rows`-row matrix that CTA `cta` of `grid` owns (`unit` rows stay together),
+ * and the number of cached positions one attention task scans for a context of `n` positions.
+ * Restates `block_slice` (qwen3.5-0.8b/csrc/megakernel.cu:118-121) and `attn_split` (:732-753). */
+int mk_plan_rows(int rows, int unit, int cta, int grid, int* r0, int* r1);
+int mk_plan_attn_chunk(int n, int max_splits);
+
 const char* mk_last_error(void);
 
 #ifdef __cplusplus

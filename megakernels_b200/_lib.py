@@ -10,7 +10,7 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmk_b200.so")
+LIB_PATH = os.path.join(HERE, os.environ.get("MK_B200_LIBNAME", "libmk_b200.so"))
 
 MK_OK, MK_ERR_BADARG, MK_ERR_TIMEOUT, MK_ERR_CUDA, MK_ERR_UNSUPPORTED = 0, -1, -2, -3, -4
 MK_QUANT = {"bf16": 0, "int8": 1}
@@ -28,7 +28,7 @@ QUERIES = ["SMEM_BYTES", "N_THREADS", "CONV_RING", "KV_BLOCK", "MAX_SPLITS", "PA
            "PROF_MAX_OPS", "PROF_FIELDS", "SPEC_T", "MAX_LAYERS", "LAYER_FIELDS", "GLOBAL_FIELDS", "SLOT_BYTES",
            "STAGES", "MAX_LM_ROWS"]
 EXPORTS = ["mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_status", "mk_query", "mk_bw_probe",
-           "mk_last_error"]
+           "mk_plan_rows", "mk_plan_attn_chunk", "mk_last_error"]
 
 
 class MkError(RuntimeError):
@@ -77,8 +77,11 @@ def load():
     lib.mk_query.restype = ctypes.c_int64
     lib.mk_bw_probe.argtypes = [ctypes.c_uint64, ctypes.c_int64, ctypes.c_int, ctypes.c_uint64, ctypes.c_int,
                                 ctypes.c_void_p]
+    lib.mk_plan_rows.argtypes = [ctypes.c_int] * 4 + [P(ctypes.c_int), P(ctypes.c_int)]
+    lib.mk_plan_attn_chunk.argtypes = [ctypes.c_int, ctypes.c_int]
+    lib.mk_plan_attn_chunk.restype = ctypes.c_int
     lib.mk_last_error.restype = ctypes.c_char_p
-    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_status", "mk_bw_probe"):
+    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_status", "mk_bw_probe", "mk_plan_rows"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib
@@ -91,6 +94,12 @@ def check(code):
 
 def query(name):
     return int(load().mk_query(QUERIES.index(name)))
+
+
+def plan_rows(rows, unit, cta, grid):
+    r0, r1 = ctypes.c_int(), ctypes.c_int()
+    check(load().mk_plan_rows(rows, unit, cta, grid, ctypes.byref(r0), ctypes.byref(r1)))
+    return r0.value, r1.value
 
 
 def i64_array(values):

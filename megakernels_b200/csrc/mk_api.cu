@@ -203,6 +203,8 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
         return fail(MK_ERR_BADARG, "mk_launch: grid %d too small or too large for this shape", grid);
     if ((e->desc.vocab + grid - 1) / grid > MAX_LM_ROWS) return fail(MK_ERR_BADARG, "mk_launch: vocab %d needs more than %d LM-head rows per CTA", e->desc.vocab, MAX_LM_ROWS);
     if (grid < Qwen35_08B::GDN_TASKS) return fail(MK_ERR_BADARG, "mk_launch: grid %d < %d DeltaNet tasks", grid, (int)Qwen35_08B::GDN_TASKS);
+    if (attn_chunk(a->start_pos + a->n_steps, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
+        return fail(MK_ERR_BADARG, "mk_launch: context of %d positions is too long for %d CTAs", a->start_pos + a->n_steps, grid);
     const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1;
     if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
         return fail(MK_ERR_BADARG, "mk_launch: epoch counter exhausted or zero; reset the engine");
@@ -378,6 +380,18 @@ extern "C" int mk_bw_probe(uint64_t src, int64_t bytes, int mode, uint64_t sink,
     }
     MK_CUDA(cudaGetLastError());
     return MK_OK;
+}
+
+extern "C" int mk_plan_rows(int rows, int unit, int cta, int grid, int* r0, int* r1) {
+    if (rows < 0 || unit < 1 || grid < 1 || cta < 0 || cta >= grid || rows % unit || !r0 || !r1)
+        return fail(MK_ERR_BADARG, "mk_plan_rows: bad arguments");
+    cta_rows(rows, unit, cta, grid, *r0, *r1);
+    return MK_OK;
+}
+
+extern "C" int mk_plan_attn_chunk(int n, int max_splits) {
+    if (n < 1 || max_splits < 1) return fail(MK_ERR_BADARG, "mk_plan_attn_chunk: bad arguments");
+    return attn_chunk(n, max_splits);
 }
 
 extern "C" const char* mk_last_error(void) { return g_err; }

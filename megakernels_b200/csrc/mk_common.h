@@ -19,7 +19,7 @@ constexpr int MAX_CHUNK_POS = 448;        // positions one attention task scans 
 constexpr int MAX_LM_ROWS = 2048;         // LM-head rows one CTA can own (per-row scales staged in smem)
 constexpr int MAX_BODY_ROWS = 64;         // rows of a layer GEMV one CTA can own
 constexpr int OPS_PER_LAYER = 5;
-constexpr int PROF_FIELDS = 4;
+constexpr int PROF_FIELDS = 6;          // enter, staged, done, published, ring-wait ns, spare
 constexpr int PROF_MAX_OPS = MAX_LAYERS * OPS_PER_LAYER + 8;
 constexpr int SPEC_T = 2;
 

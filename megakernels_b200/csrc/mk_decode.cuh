@@ -55,11 +55,18 @@ struct Ctx {
     int* status;
     bool dead;          // this thread saw a wait run out
     u64* prof;          // this CTA's timestamp rows for the step being profiled, or null
+    u64 wait_acc;       // time consumer thread 0 spent waiting for ring chunks in the current op
 };
 
 // Per-op timestamps (enter, inputs staged, work done, outputs published), consumer thread 0 only.
-__device__ __forceinline__ void prof_stamp(const Ctx& c, int op, int field) {
-    if (c.prof && c.tid == 0) c.prof[(size_t)op * PROF_FIELDS + field] = globaltimer();
+__device__ __forceinline__ void prof_stamp(Ctx& c, int op, int field) {
+    if (c.prof && c.tid == 0) {
+        c.prof[(size_t)op * PROF_FIELDS + field] = globaltimer();
+        if (field == 3) {
+            c.prof[(size_t)op * PROF_FIELDS + 4] = c.wait_acc;
+            c.wait_acc = 0;
+        }
+    }
 }
 
 struct Spin {
@@ -103,6 +110,15 @@ __device__ __forceinline__ void mbar_wait(Ctx& c, uint64_t* b, uint32_t parity, 
     }
 }
 
+// Pause between two polls of a word that is not ready.  Thousands of threads poll the same few
+// cache lines; without a pause their loads queue up in front of the store they are waiting for.
+#ifndef MK_POLL_SLEEP_NS
+#define MK_POLL_SLEEP_NS 0
+#endif
+__device__ __forceinline__ void poll_backoff() {
+    if (MK_POLL_SLEEP_NS > 0) __nanosleep(MK_POLL_SLEEP_NS);
+}
+
 // Wait until the word shows `epoch`; returns its fp32 payload.
 __device__ __forceinline__ float ll_wait(Ctx& c, const u64* p, uint32_t epoch, int where) {
     Spin s;
@@ -112,6 +128,7 @@ __device__ __forceinline__ float ll_wait(Ctx& c, const u64* p, uint32_t epoch, i
             c.dead = true;
             break;
         }
+        poll_backoff();
         w = ll_load(p);
     }
     return __uint_as_float((uint32_t)w);
@@ -125,6 +142,7 @@ __device__ __forceinline__ void ll_wait2(Ctx& c, const u64* p, uint32_t epoch, i
             c.dead = true;
             break;
         }
+        poll_backoff();
         ll_load2(p, w0, w1);
     }
     a = __uint_as_float((uint32_t)w0);
@@ -232,7 +250,13 @@ __device__ __forceinline__ void gemv_stream(Ctx& c, int r0, int r1, Sink&& sink)
         const int nr = min(RPC, r1 - base);
         const uint32_t n = c.cons_n++;
         const int slot = (int)(n % NSTAGE);
-        mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
+        if (c.prof && c.tid == 0) {
+            const u64 t = globaltimer();
+            mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
+            c.wait_acc += globaltimer() - t;
+        } else {
+            mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
+        }
         const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
         if (KSPLIT > 1) {
             for (int item = c.warp; item < nr * KSPLIT; item += NCW) {
@@ -718,7 +742,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
-    c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr;
+    c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr; c.wait_acc = 0;
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
     if (c.tid == 0) {
