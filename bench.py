@@ -152,6 +152,7 @@ def run_reference(args):
 
 
 def main():
+    global PROMPT, GENERATE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -160,7 +161,10 @@ def main():
     ap.add_argument("--quant", default="int8", choices=["int8", "bf16"])
     ap.add_argument("--kv-dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="shrink the case (profiling only)")
+    ap.add_argument("--generate", type=int, default=GENERATE, help="shrink the case (profiling only)")
     args = ap.parse_args()
+    PROMPT, GENERATE = args.prompt, args.generate
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)
