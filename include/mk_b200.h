@@ -34,6 +34,7 @@ enum { MK_SHAPE_QWEN35_08B = 1 };
 /* Field order of one layer's pointer record (MK_LAYER_FIELDS int64 values per layer).
  * Replaces the 18-field record of qwen3.5-0.8b/csrc/binding.cpp:18-37. */
 enum {
+    /* the four matrices are in the kernel's tile layout (megakernels_b200/pack.py), int8 or bf16 */
     MK_L_W_IN = 0,      /* DeltaNet: [qkv|z|b|a rows, hidden]; attention: [per-head q|gate, k, v rows, hidden] */
     MK_L_W_OUT,         /* [hidden, 2048]                                                     */
     MK_L_W_GU,          /* [2*intermediate, hidden], rows interleaved gate0, up0, gate1, ...  */
@@ -45,7 +46,7 @@ enum {
     MK_L_A_LOG,         /* fp32 [heads]                                                       */
     MK_L_DT_BIAS,       /* fp32 [heads]                                                       */
     MK_L_GDN_NORM,      /* fp32 [v_dim]                                                       */
-    MK_L_CONV_HIST,     /* fp32 [conv_dim, MK_CONV_RING] ring indexed by position & 7         */
+    MK_L_CONV_HIST,     /* fp32 [128 tasks, 272 channels, MK_CONV_RING]: per recurrence task, ring by position & 7 */
     MK_L_STATE,         /* fp32 [heads, v_dim, k_dim]                                         */
     MK_L_STATE_BAK,     /* same shape; spare copy used by speculative cycles                  */
     MK_L_Q_NORM,        /* fp32 [head_dim]                                                    */
@@ -60,9 +61,9 @@ enum {
 /* Field order of the model-wide pointer record (MK_GLOBAL_FIELDS int64 values).
  * Replaces the 20-entry list of qwen3.5-0.8b/csrc/binding.cpp:47-66. */
 enum {
-    MK_G_EMBED = 0,     /* token embedding table in the kernel's weight format [vocab, hidden] */
+    MK_G_EMBED = 0,     /* token embedding table, plain row-major [vocab, hidden], int8 or bf16 */
     MK_G_EMBED_SCALE,   /* fp32 [vocab] (int8) or 0                                            */
-    MK_G_LM_HEAD,       /* LM head rows in the kernel's weight format (== embed when tied)     */
+    MK_G_LM_HEAD,       /* LM head [vocab, hidden] in the kernel's tile layout                 */
     MK_G_LM_SCALE,
     MK_G_FINAL_NORM,    /* fp32 [hidden]                                                       */
     MK_G_ROPE_COS,      /* fp32 [max_seq, rotary_dim/2]                                        */
@@ -72,7 +73,7 @@ enum {
     MK_G_MIXL,          /* u64 [tokens, 2048]          mixer (DeltaNet / attention) output     */
     MK_G_ACTL,          /* u64 [tokens, intermediate]  MLP activation                          */
     MK_G_LML,           /* u64 [tokens, grid, 2]       per-CTA LM-head winners                 */
-    MK_G_ATTN_PART,     /* fp32 [tokens, kv_heads, MK_MAX_SPLITS, MK_PART_STRIDE]              */
+    MK_G_ATTN_PART,     /* u64 [tokens, kv_heads, MK_MAX_SPLITS, MK_PART_STRIDE] split partials, flag-in-data words */
     MK_G_ATTN_FLAG,     /* u32 [tokens, kv_heads, MK_MAX_SPLITS]                               */
     MK_G_BLOCK_TABLE,   /* int32 [max_seq / MK_KV_BLOCK]: logical KV block -> physical block   */
     MK_G_STATUS,        /* int32 [4]: [0] error code of the first wait that ran out, [1] where */
@@ -91,6 +92,7 @@ typedef struct mk_model_desc {
     int32_t kv_dtype;     /* MK_KV_*                                           */
     int32_t draft_vocab;  /* rows of the draft head (0: no MTP head)           */
     int32_t device;       /* CUDA device ordinal                               */
+    int32_t grid;         /* CTAs the weights were packed for (0: one per SM)  */
 } mk_model_desc;
 
 /* Per-launch arguments.  Replaces `Args` of qwen3.5-0.8b/csrc/megakernel.h:134-161 and the 26

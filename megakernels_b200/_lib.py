@@ -39,7 +39,7 @@ class MkError(RuntimeError):
 
 class ModelDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
-                ("shape", "n_layers", "vocab", "max_seq", "quant", "kv_dtype", "draft_vocab", "device")]
+                ("shape", "n_layers", "vocab", "max_seq", "quant", "kv_dtype", "draft_vocab", "device", "grid")]
 
 
 class LaunchArgs(ctypes.Structure):

@@ -91,8 +91,10 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
     if (d->quant != MK_QUANT_BF16 && d->quant != MK_QUANT_INT8) return fail(MK_ERR_UNSUPPORTED, "mk_create: quant %d", d->quant);
     if (d->kv_dtype != MK_KV_BF16 && d->kv_dtype != MK_KV_F32) return fail(MK_ERR_UNSUPPORTED, "mk_create: kv_dtype %d", d->kv_dtype);
     if (d->vocab < 1 || d->max_seq < 1 || d->max_seq % KV_BLOCK) return fail(MK_ERR_BADARG, "mk_create: vocab %d / max_seq %d (must be a multiple of %d)", d->vocab, d->max_seq, KV_BLOCK);
+    if (d->max_seq > MAX_BLOCKS * KV_BLOCK) return fail(MK_ERR_BADARG, "mk_create: max_seq %d exceeds %d", d->max_seq, MAX_BLOCKS * KV_BLOCK);
     int n_sm = 0;
     MK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, d->device));
+    if (d->grid < 0 || d->grid > n_sm) return fail(MK_ERR_BADARG, "mk_create: grid %d exceeds the %d SMs (every CTA must be resident)", d->grid, n_sm);
     int slot = -1;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -102,6 +104,7 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
     if (slot < 0) return fail(MK_ERR_BADARG, "mk_create: all %d engine slots are in use", MAX_ENGINES);
     mk_engine* e = new mk_engine();
     e->desc = *d;
+    if (e->desc.grid == 0) e->desc.grid = n_sm;
     e->slot = slot;
     e->n_sm = n_sm;
     e->params_set = false;
@@ -147,7 +150,7 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     p.mixl = as_ptr<unsigned long long*>(g[MK_G_MIXL]);
     p.actl = as_ptr<unsigned long long*>(g[MK_G_ACTL]);
     p.lml = as_ptr<unsigned long long*>(g[MK_G_LML]);
-    p.attn_part = as_ptr<float*>(g[MK_G_ATTN_PART]);
+    p.attn_part = as_ptr<unsigned long long*>(g[MK_G_ATTN_PART]);
     p.attn_flag = as_ptr<unsigned*>(g[MK_G_ATTN_FLAG]);
     p.block_table = as_ptr<const int*>(g[MK_G_BLOCK_TABLE]);
     p.status = as_ptr<int*>(g[MK_G_STATUS]);
@@ -195,13 +198,11 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch: lm_from out of range");
     if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch: tokens_out / out_info missing");
     if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch: stop ids missing");
-    const int grid = a->grid > 0 ? a->grid : e->n_sm;
-    if (grid > e->n_sm) return fail(MK_ERR_BADARG, "mk_launch: grid %d exceeds the %d SMs (every CTA must be resident)", grid, e->n_sm);
+    const int grid = a->grid > 0 ? a->grid : e->desc.grid;
+    if (grid != e->desc.grid) return fail(MK_ERR_BADARG, "mk_launch: grid %d, but the weights are packed for %d CTAs", grid, e->desc.grid);
     // per-CTA ownership limits of the kernel's shared-memory staging
-    const int in_rows = (Qwen35_08B::GDN_IN + grid - 1) / grid + 1;
-    if (in_rows > MAX_BODY_ROWS || (Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID)
+    if ((Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID)
         return fail(MK_ERR_BADARG, "mk_launch: grid %d too small or too large for this shape", grid);
-    if ((e->desc.vocab + grid - 1) / grid > MAX_LM_ROWS) return fail(MK_ERR_BADARG, "mk_launch: vocab %d needs more than %d LM-head rows per CTA", e->desc.vocab, MAX_LM_ROWS);
     if (grid < Qwen35_08B::GDN_TASKS) return fail(MK_ERR_BADARG, "mk_launch: grid %d < %d DeltaNet tasks", grid, (int)Qwen35_08B::GDN_TASKS);
     if (attn_chunk(a->start_pos + a->n_steps, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
         return fail(MK_ERR_BADARG, "mk_launch: context of %d positions is too long for %d CTAs", a->start_pos + a->n_steps, grid);

@@ -16,7 +16,7 @@ constexpr int KV_BLOCK = 64;              // positions per KV page
 constexpr int CONV_RING = 8;              // conv history slots, indexed by position & 7
 constexpr int MAX_SPLITS = 128;           // attention split-K chunks per KV head (buffer sizing)
 constexpr int MAX_CHUNK_POS = 448;        // positions one attention task scans at most
-constexpr int MAX_LM_ROWS = 2048;         // LM-head rows one CTA can own (per-row scales staged in smem)
+constexpr int MAX_LM_ROWS = 1 << 20;      // LM-head rows one CTA can own (no per-CTA staging limits it)
 constexpr int MAX_BODY_ROWS = 64;         // rows of a layer GEMV one CTA can own
 constexpr int OPS_PER_LAYER = 5;
 constexpr int PROF_FIELDS = 6;          // enter, staged, done, published, ring-wait ns, spare
@@ -43,10 +43,10 @@ struct Qwen35_08B {
 };
 
 constexpr int SMEM_RING = NSTAGE * SLOT_BYTES;
-constexpr int SMEM_XS = 3584 * 4;                                  // GEMV input vector / mixer scratch
-constexpr int SMEM_SCALE = MAX_LM_ROWS * 4;
-constexpr int SMEM_MISC = 2048;
-constexpr int SMEM_BYTES = SMEM_RING + SMEM_XS + SMEM_SCALE + SMEM_MISC;
+constexpr int SMEM_XQ = 3 * 2 * 3584;                              // GEMV input planes (3 bf16 pieces of K = 3584) / mixer scratch
+constexpr int MAX_BLOCKS = 512;                                    // KV pages per sequence (max_seq <= 32768)
+constexpr int SMEM_MISC = 2 * NCW * 32 * 4 + MAX_BLOCKS * 4 + 1024;
+constexpr int SMEM_BYTES = SMEM_RING + SMEM_XQ + SMEM_MISC;
 
 // ---- device-side parameter block (one per engine, in constant memory) --------------------------
 struct LayerP {
@@ -89,7 +89,7 @@ struct Params {
     unsigned long long* mixl;
     unsigned long long* actl;
     unsigned long long* lml;
-    float* attn_part;
+    unsigned long long* attn_part;
     unsigned* attn_flag;
     const int* block_table;
     int* status;

@@ -33,17 +33,18 @@ enum { W_FULL = 1, W_EMPTY, W_X, W_PROJ, W_MIX, W_ACT, W_LM, W_PART, W_DRAIN };
 
 struct Smem {
     uint8_t* ring;
-    float* xs;          // GEMV input vector (permuted), or mixer scratch
-    float* scale_s;     // LM-head per-row scales of this CTA
-    float* out_s;       // raw row sums of a body GEMV [MAX_BODY_ROWS * 2]
-    float* red_s;       // [2][NCW] block-reduction scratch, alternating halves
+    uint8_t* xq;        // GEMV input as byte planes (int8 digits or bf16 pieces), or mixer scratch
+    float* part_s;      // [2][NCW][32] per-warp partial row sums of a ring chunk, alternating halves
+    int* bt_s;          // block table copy [max_seq / KV_BLOCK]
+    float* out_s;       // small per-op scratch (attention statistics)
+    float* red_s;       // [2][2 * NCW] block-reduction scratch, alternating halves
     float* xown;        // fp32 master copy of the residual rows this CTA owns
-    u64* best_s;        // [NCW] per-warp LM-head winners
+    u64* best_s;        // [NCW] block-reduction scratch for 64-bit keys
+    float* xscale_s;    // [1] power-of-two factor that undoes the fixed-point scaling of the staged input
     uint64_t* full;     // [NSTAGE]
     uint64_t* empty;    // [NSTAGE]
     volatile int* abort_flag;
     volatile int* quit_flag;
-    volatile int* tok_s;
 };
 
 struct Ctx {
@@ -149,140 +150,213 @@ __device__ __forceinline__ void ll_wait2(Ctx& c, const u64* p, uint32_t epoch, i
     b = __uint_as_float((uint32_t)w1);
 }
 
-// Sum over all consumer threads, in a fixed order (one barrier).
-__device__ __forceinline__ float consumer_sum(Ctx& c, float v) {
-    float* buf = c.sm.red_s + (c.red_n++ & 1) * NCW;
-    v = warp_sum(v);
-    if (c.lane == 0) buf[c.warp] = v;
-    consumer_sync();
-    float t = 0.f;
+// Wait for N word pairs at once: all loads are issued before any is checked, and only the pairs that
+// are not ready are loaded again, so a thread that needs several pairs pays one round trip, not N.
+template <int N>
+__device__ __forceinline__ void ll_wait_pairs(Ctx& c, const u64* const (&p)[N], const uint32_t (&e)[N], float (&v)[2 * N],
+                                              int where) {
+    u64 w[2 * N];
 #pragma unroll
-    for (int i = 0; i < NCW; i++) t += buf[i];
-    return t;
-}
-
-// ---- GEMV input vector layout --------------------------------------------------------------------
-// A lane reads one 16-byte piece of a weight row at a time: 16 int8 or 8 bf16 weights.  The matching
-// inputs are 4 (or 2) float4s.  Storing float4 number j of piece p at
-//     (p / 32) * 32 * PIECE + j * 128 + (p % 32) * 4
-// puts the j-th float4 of 32 consecutive pieces side by side, so a warp's loads are conflict-free.
-template <bool Q8>
-__device__ __forceinline__ int xs_index(int k) {
-    constexpr int PIECE = Q8 ? 16 : 8;
-    const int p = k / PIECE, r = k % PIECE;
-    return (p >> 5) * (32 * PIECE) + (r >> 2) * 128 + (p & 31) * 4 + (r & 3);
-}
-
-// Partial dot products of NR weight rows (16-byte pieces [p0, p0 + np) of each) with the staged input.
-template <bool Q8, int NR>
-__device__ __forceinline__ void dot_rows(const uint8_t* const (&rows)[NR], const float* xs, int p0, int np, int lane,
-                                         float (&acc)[NR]) {
-    constexpr int PIECE = Q8 ? 16 : 8;
-    float a0[NR], a1[NR];
+    for (int i = 0; i < N; i++)
+        if (p[i]) ll_load2(p[i], w[2 * i], w[2 * i + 1]);
+    Spin s;
+    while (true) {
+        bool ok = true;
 #pragma unroll
-    for (int r = 0; r < NR; r++) a0[r] = a1[r] = 0.f;
-#pragma unroll 2
-    for (int i = lane; i < np; i += 32) {
-        const int p = p0 + i;
-        const float* xb = xs + (p >> 5) * (32 * PIECE) + (p & 31) * 4;
-        uint4 w[NR];
-#pragma unroll
-        for (int r = 0; r < NR; r++) w[r] = *reinterpret_cast<const uint4*>(rows[r] + (size_t)p * 16);
-        if (Q8) {
-            const float4 x0 = *reinterpret_cast<const float4*>(xb);
-            const float4 x1 = *reinterpret_cast<const float4*>(xb + 128);
-            const float4 x2 = *reinterpret_cast<const float4*>(xb + 256);
-            const float4 x3 = *reinterpret_cast<const float4*>(xb + 384);
-#pragma unroll
-            for (int r = 0; r < NR; r++) {
-                a0[r] = fmaf(deq_u8<0>(w[r].x), x0.x, a0[r]);
-                a1[r] = fmaf(deq_u8<1>(w[r].x), x0.y, a1[r]);
-                a0[r] = fmaf(deq_u8<2>(w[r].x), x0.z, a0[r]);
-                a1[r] = fmaf(deq_u8<3>(w[r].x), x0.w, a1[r]);
-                a0[r] = fmaf(deq_u8<0>(w[r].y), x1.x, a0[r]);
-                a1[r] = fmaf(deq_u8<1>(w[r].y), x1.y, a1[r]);
-                a0[r] = fmaf(deq_u8<2>(w[r].y), x1.z, a0[r]);
-                a1[r] = fmaf(deq_u8<3>(w[r].y), x1.w, a1[r]);
-                a0[r] = fmaf(deq_u8<0>(w[r].z), x2.x, a0[r]);
-                a1[r] = fmaf(deq_u8<1>(w[r].z), x2.y, a1[r]);
-                a0[r] = fmaf(deq_u8<2>(w[r].z), x2.z, a0[r]);
-                a1[r] = fmaf(deq_u8<3>(w[r].z), x2.w, a1[r]);
-                a0[r] = fmaf(deq_u8<0>(w[r].w), x3.x, a0[r]);
-                a1[r] = fmaf(deq_u8<1>(w[r].w), x3.y, a1[r]);
-                a0[r] = fmaf(deq_u8<2>(w[r].w), x3.z, a0[r]);
-                a1[r] = fmaf(deq_u8<3>(w[r].w), x3.w, a1[r]);
+        for (int i = 0; i < N; i++)
+            if (p[i] && ((uint32_t)(w[2 * i] >> 32) != e[i] || (uint32_t)(w[2 * i + 1] >> 32) != e[i])) {
+                ok = false;
+                ll_load2(p[i], w[2 * i], w[2 * i + 1]);
             }
-        } else {
-            const float4 x0 = *reinterpret_cast<const float4*>(xb);
-            const float4 x1 = *reinterpret_cast<const float4*>(xb + 128);
-#pragma unroll
-            for (int r = 0; r < NR; r++) {
-                a0[r] = fmaf(bf_lo(w[r].x), x0.x, a0[r]);
-                a1[r] = fmaf(bf_hi(w[r].x), x0.y, a1[r]);
-                a0[r] = fmaf(bf_lo(w[r].y), x0.z, a0[r]);
-                a1[r] = fmaf(bf_hi(w[r].y), x0.w, a1[r]);
-                a0[r] = fmaf(bf_lo(w[r].z), x1.x, a0[r]);
-                a1[r] = fmaf(bf_hi(w[r].z), x1.y, a1[r]);
-                a0[r] = fmaf(bf_lo(w[r].w), x1.z, a0[r]);
-                a1[r] = fmaf(bf_hi(w[r].w), x1.w, a1[r]);
-            }
+        if (ok) break;
+        if (MK_SPIN_FAIL(c, s, where)) {
+            c.dead = true;
+            break;
         }
     }
 #pragma unroll
-    for (int r = 0; r < NR; r++) acc[r] = warp_sum(a0[r] + a1[r]);
+    for (int i = 0; i < N; i++) {
+        v[2 * i] = p[i] ? __uint_as_float((uint32_t)w[2 * i]) : 0.f;
+        v[2 * i + 1] = p[i] ? __uint_as_float((uint32_t)w[2 * i + 1]) : 0.f;
+    }
 }
 
-// Streams this CTA's rows [r0, r1) of a [rows, K] matrix out of the ring and hands every finished
-// (row, K-segment) sum to `sink(row, seg, sum)` on all lanes of the warp that computed it.
-//   KSPLIT  warps that share one row (each takes a contiguous K segment); used when a CTA owns few,
-//           long rows.  KSPLIT == 1 lets a warp take RPW rows at once and share the input loads.
-template <int K, bool Q8, int KSPLIT, int RPW, class Sink>
-__device__ __forceinline__ void gemv_stream(Ctx& c, int r0, int r1, Sink&& sink) {
-    constexpr int PIECE = Q8 ? 16 : 8;
-    constexpr int RB = Q8 ? K : 2 * K;          // row bytes
-    constexpr int RPC = SLOT_BYTES / RB;        // rows per ring chunk
-    constexpr int PPR = K / PIECE;              // pieces per row
-    constexpr int PPS = PPR / KSPLIT;           // pieces per segment
-    static_assert(PPR % KSPLIT == 0, "segments must be whole pieces");
-    static_assert(KSPLIT == 1 || RPW == 1, "row pairing only without K split");
-    static_assert(RPW == 1 || RPC % RPW == 0, "row groups must not straddle chunks");
-    for (int base = r0; base < r1; base += RPC) {
-        const int nr = min(RPC, r1 - base);
+// Sum and max over all consumer threads in one barrier, fixed order.
+__device__ __forceinline__ void consumer_sum_max(Ctx& c, float& sum, float& mx) {
+    float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);
+    sum = warp_sum(sum);
+    mx = warp_max(mx);
+    if (c.lane == 0) {
+        buf[c.warp] = sum;
+        buf[NCW + c.warp] = mx;
+    }
+    consumer_sync();
+    float t = 0.f, m = 0.f;
+#pragma unroll
+    for (int i = 0; i < NCW; i++) {
+        t += buf[i];
+        m = fmaxf(m, buf[NCW + i]);
+    }
+    sum = t;
+    mx = m;
+}
+
+// ---- GEMV on the tensor cores ---------------------------------------------------------------------
+// A weight row is cut into 64-byte k-blocks (64 int8 or 32 bf16 weights).  Rows are stored in groups
+// of up to 8, k-block major: block kb of every row of the group, then block kb + 1, ...  One 128-bit
+// load per lane therefore hands a warp an 8-row x 64-byte tile as the B operands of two MMAs
+// (lane = 4 * row + quarter), with no conversion and no bank conflict.
+//
+// The input vector is the A operand.  fp32 inputs are made exact for the tensor cores by splitting:
+//   int8 weights: x * 2^s rounded to a 28-bit integer, cut into four base-128 digits (int8 planes);
+//                 integer MMAs (s8 x s8 -> s32) are exact, the digits recombine in fp32;
+//   bf16 weights: x = p0 + p1 + p2 with three bf16 pieces (24 significant bits); bf16 MMAs with fp32
+//                 accumulation.
+// Plane m of the staged input is MMA row m, so one MMA handles all planes at once.  Each warp owns a
+// k-slice (k-blocks warp, warp + 16, ...) of every row of the chunk; per-warp partial sums meet in
+// shared memory and warp 0 finishes the rows after one barrier per chunk.
+template <bool Q8> struct Planes { static constexpr int N = Q8 ? 4 : 3; };
+
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Stage two consecutive inputs (elements k, k + 1) into the planes.  `scale` is the power of two that
+// maps the vector's largest magnitude below 2^27 (int8 path only).
+template <bool Q8>
+__device__ __forceinline__ void stage_pair(uint8_t* xq, int rb, int k, float v0, float v1, float scale) {
+    if (Q8) {
+        const int a = __float2int_rn(v0 * scale), b = __float2int_rn(v1 * scale);
+#pragma unroll
+        for (int d = 0; d < 4; d++) {
+            const int da = d < 3 ? ((a >> (7 * d)) & 127) : (a >> 21);
+            const int db = d < 3 ? ((b >> (7 * d)) & 127) : (b >> 21);
+            *reinterpret_cast<uint16_t*>(xq + d * rb + k) = (uint16_t)((da & 255) | ((db & 255) << 8));
+        }
+    } else {
+#pragma unroll
+        for (int d = 0; d < 3; d++) {
+            const __nv_bfloat16 pa = __float2bfloat16_rn(v0), pb = __float2bfloat16_rn(v1);
+            v0 -= __bfloat162float(pa);
+            v1 -= __bfloat162float(pb);
+            *reinterpret_cast<uint32_t*>(xq + d * rb + 2 * k) =
+                (uint32_t)__bfloat16_as_ushort(pa) | ((uint32_t)__bfloat16_as_ushort(pb) << 16);
+        }
+    }
+}
+
+// Fixed-point scale for a vector whose largest magnitude is `mx`: 2^(26 - exponent(mx)).
+__device__ __forceinline__ float fixed_scale(float mx) {
+    int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 127;
+    e = max(-100, min(100, e));
+    return __uint_as_float((uint32_t)(127 + 26 - e) << 23);
+}
+
+// Streams this CTA's rows [r0, r1) of a matrix with `rb`-byte rows out of the ring.  Two 8-row tiles
+// form the 16-row A operand of an MMA, the input planes are its B operand (column n = plane n), so
+// lane (g, t) ends up with rows g and g + 8 of the block for planes 2t and 2t + 1.  When a chunk's
+// rows are finished, every lane of warp 0 calls sink(lane, row, value, valid): lane i holds row
+// base + i of the chunk (value already multiplied by the row's scale and the input's scale).
+template <bool Q8, class Sink>
+__device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const float* __restrict__ row_scale,
+                                         Sink&& sink) {
+    const int rpc = SLOT_BYTES / rb;
+    const int nkb = rb >> 6;
+    const int g = c.lane >> 2, t = c.lane & 3;
+    const uint8_t* xrow = c.sm.xq + g * rb + t * 16;
+    const bool xlive = g < Planes<Q8>::N;
+    // per-row scales of the next four chunks, fetched ahead so that no chunk waits for DRAM
+    float sc0 = 1.f, sc1 = 1.f, sc2 = 1.f, sc3 = 1.f;
+    const bool scaler = row_scale != nullptr && c.warp == 0;
+    if (scaler) {
+        if (r0 + c.lane < r1) sc0 = row_scale[r0 + c.lane];
+        if (r0 + rpc + c.lane < r1) sc1 = row_scale[r0 + rpc + c.lane];
+        if (r0 + 2 * rpc + c.lane < r1) sc2 = row_scale[r0 + 2 * rpc + c.lane];
+        if (r0 + 3 * rpc + c.lane < r1) sc3 = row_scale[r0 + 3 * rpc + c.lane];
+    }
+    for (int base = r0; base < r1; base += rpc) {
+        const int nr = min(rpc, r1 - base);
         const uint32_t n = c.cons_n++;
         const int slot = (int)(n % NSTAGE);
+        const float rs = sc0;
+        sc0 = sc1; sc1 = sc2; sc2 = sc3;
+        if (scaler && base + 4 * rpc + c.lane < r1) sc3 = row_scale[base + 4 * rpc + c.lane];
         if (c.prof && c.tid == 0) {
-            const u64 t = globaltimer();
+            const u64 t0 = globaltimer();
             mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
-            c.wait_acc += globaltimer() - t;
+            c.wait_acc += globaltimer() - t0;
         } else {
             mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
         }
         const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
-        if (KSPLIT > 1) {
-            for (int item = c.warp; item < nr * KSPLIT; item += NCW) {
-                const int row = item / KSPLIT, seg = item % KSPLIT;
-                const uint8_t* const rows[1] = {buf + (size_t)row * RB};
-                float acc[1];
-                dot_rows<Q8, 1>(rows, c.sm.xs, seg * PPS, PPS, c.lane, acc);
-                sink(base + row, seg, acc[0]);
+        float* part = c.sm.part_s + ((n & 1) * NCW + c.warp) * 32;
+        for (int b0 = 0; b0 < nr; b0 += 16) {
+            const int n_lo = min(8, nr - b0), n_hi = max(0, min(8, nr - b0 - 8));
+            const uint8_t* t_lo = buf + (size_t)b0 * rb + g * 64 + t * 16;
+            const uint8_t* t_hi = buf + (size_t)(b0 + 8) * rb + g * 64 + t * 16;
+            const bool live_lo = g < n_lo, live_hi = g < n_hi;
+            int ci[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+            float cf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            int kb = c.warp;
+#pragma unroll 1
+            for (; kb < nkb; kb += 2 * NCW) {
+#pragma unroll
+                for (int u = 0; u < 2; u++) {        // two independent accumulator chains
+                    const int k2 = kb + u * NCW;
+                    if (k2 < nkb) {
+                        uint4 wl = make_uint4(0, 0, 0, 0), wh = wl, x = wl;
+                        if (live_lo) wl = *reinterpret_cast<const uint4*>(t_lo + (size_t)k2 * n_lo * 64);
+                        if (live_hi) wh = *reinterpret_cast<const uint4*>(t_hi + (size_t)k2 * n_hi * 64);
+                        if (xlive) x = *reinterpret_cast<const uint4*>(xrow + k2 * 64);
+                        if (Q8) {
+                            mma_s8(ci[u], wl.x, wh.x, wl.y, wh.y, x.x, x.y);
+                            mma_s8(ci[u], wl.z, wh.z, wl.w, wh.w, x.z, x.w);
+                        } else {
+                            mma_bf16(cf[u], wl.x, wh.x, wl.y, wh.y, x.x, x.y);
+                            mma_bf16(cf[u], wl.z, wh.z, wl.w, wh.w, x.z, x.w);
+                        }
+                    }
+                }
             }
-        } else {
-            const int nitems = (nr + RPW - 1) / RPW;
-            for (int item = c.warp; item < nitems; item += NCW) {
-                const uint8_t* rows[RPW];
-#pragma unroll
-                for (int r = 0; r < RPW; r++) rows[r] = buf + (size_t)(item * RPW + r) * RB;
-                float acc[RPW];
-                dot_rows<Q8, RPW>(rows, c.sm.xs, 0, PPR, c.lane, acc);
-#pragma unroll
-                for (int r = 0; r < RPW; r++)
-                    if (item * RPW + r < nr) sink(base + item * RPW + r, 0, acc[r]);
+            // planes -> value: this lane holds planes 2t, 2t + 1 of rows g (c0, c1) and g + 8 (c2, c3)
+            float v_lo, v_hi;
+            if (Q8) {
+                const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);       // 128^(2t)
+                const float pw1 = pw0 * 128.f;
+                v_lo = (float)(ci[0][0] + ci[1][0]) * pw0 + (float)(ci[0][1] + ci[1][1]) * pw1;
+                v_hi = (float)(ci[0][2] + ci[1][2]) * pw0 + (float)(ci[0][3] + ci[1][3]) * pw1;
+            } else {
+                v_lo = (cf[0][0] + cf[1][0]) + (cf[0][1] + cf[1][1]);
+                v_hi = (cf[0][2] + cf[1][2]) + (cf[0][3] + cf[1][3]);
+            }
+            v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
+            v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+            if (t == 0) {
+                part[b0 + g] = v_lo;
+                if (b0 + 8 + g < 32) part[b0 + 8 + g] = v_hi;
             }
         }
         __syncwarp();
         // A lane whose wait ran out never releases the slot: its copy may still be in flight, and the
         // producer must not aim a second copy at the same shared memory.
         if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
+        consumer_sync();
+        if (c.warp == 0) {
+            const float* pp = c.sm.part_s + (n & 1) * NCW * 32 + c.lane;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < NCW; w++) v += pp[w * 32];
+            sink(c.lane, base + c.lane, v * rs * *c.sm.xscale_s, c.lane < nr);
+        }
     }
 }
 
@@ -365,17 +439,37 @@ __device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
 }
 
 // ---- prologues ---------------------------------------------------------------------------------------
-// RMSNorm of the residual stream into the GEMV input vector.  `x` holds this thread's two elements
-// (2*tid, 2*tid+1).
+// RMSNorm of the residual stream into the GEMV input planes.  `x0`, `x1` are this thread's two
+// elements (2*tid, 2*tid+1).  One block reduction yields both the sum of squares and the largest
+// |x (1 + w)|, from which the fixed-point scale follows without a second pass.
 template <class S, bool Q8>
 __device__ __forceinline__ void stage_rmsnorm(Ctx& c, float x0, float x1, const float* __restrict__ w) {
     static_assert(S::HID == 2 * NCT, "two residual elements per consumer thread");
+    constexpr int RB = Q8 ? S::HID : 2 * S::HID;
     const int k = 2 * c.tid;
     const float2 g = *reinterpret_cast<const float2*>(w + k);
-    const float ss = consumer_sum(c, x0 * x0 + x1 * x1);
+    const float y0 = x0 * (1.0f + g.x), y1 = x1 * (1.0f + g.y);
+    float ss = x0 * x0 + x1 * x1, mx = fmaxf(fabsf(y0), fabsf(y1));
+    consumer_sum_max(c, ss, mx);
     const float inv = rsqrtf(ss * (1.0f / S::HID) + S::EPS);
-    c.sm.xs[xs_index<Q8>(k)] = x0 * inv * (1.0f + g.x);
-    c.sm.xs[xs_index<Q8>(k + 1)] = x1 * inv * (1.0f + g.y);
+    const float scale = Q8 ? fixed_scale(mx * inv) : 1.0f;
+    stage_pair<Q8>(c.sm.xq, RB, k, y0 * inv, y1 * inv, scale);
+    if (c.tid == 0) *c.sm.xscale_s = 1.0f / scale;
+    consumer_sync();
+}
+
+// For inputs that need no norm: the fixed-point scale from this thread's largest magnitude (one
+// block reduction on the int8 path, nothing on the bf16 path) ...
+template <bool Q8>
+__device__ __forceinline__ float block_scale(Ctx& c, float local_max) {
+    if (!Q8) return 1.0f;
+    float dummy = 0.f;
+    consumer_sum_max(c, dummy, local_max);
+    return fixed_scale(local_max);
+}
+// ... and the end of a staging phase: publish the inverse scale, make the planes visible.
+__device__ __forceinline__ void finish_stage(Ctx& c, float scale) {
+    if (c.tid == 0) *c.sm.xscale_s = 1.0f / scale;
     consumer_sync();
 }
 
@@ -386,8 +480,8 @@ __device__ __forceinline__ void load_embedding(const Params& P, int token, int t
     if (Q8) {
         const uint16_t b = *reinterpret_cast<const uint16_t*>(P.embed + (size_t)token * S::HID + k);
         const float sc = P.embed_scale[token];
-        x0 = (float)((int)(b & 0xff) - 128) * sc;
-        x1 = (float)((int)(b >> 8) - 128) * sc;
+        x0 = (float)(int)(signed char)(b & 0xff) * sc;
+        x1 = (float)(int)(signed char)(b >> 8) * sc;
     } else {
         const uint32_t b = *reinterpret_cast<const uint32_t*>(P.embed + ((size_t)token * S::HID + k) * 2);
         x0 = bf_lo(b);
@@ -405,7 +499,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     if (c.cta >= S::GDN_TASKS) return;
     const int h = c.cta / SL, j = c.cta % SL;
     const int vcol = j * S::GDN_SLICE + c.warp;
-    float* qkv_s = c.sm.xs;                       // [q 128 | k 128 | v 16 | b | a]
+    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);   // [q 128 | k 128 | v 16 | b | a]
     float* srow = L.state + ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
     const float4 st = *reinterpret_cast<const float4*>(srow);   // issued before the wait on purpose
     constexpr int NCH = 2 * S::LIN_DK + S::GDN_SLICE;           // 272 conv channels this task needs
@@ -415,17 +509,19 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
         else if (c.tid < 2 * S::LIN_DK) ch = S::LIN_QK + h * S::LIN_DK + (c.tid - S::LIN_DK);
         else ch = 2 * S::LIN_QK + h * S::LIN_DV + j * S::GDN_SLICE + (c.tid - 2 * S::LIN_DK);
         const float4 taps = *reinterpret_cast<const float4*>(L.conv_w + 4 * ch);
-        float* hist = L.conv_hist + (size_t)ch * CONV_RING;
-        const float h3 = __ldcg(hist + ((pos - 3) & (CONV_RING - 1)));   // written by another CTA: skip L1
-        const float h2 = __ldcg(hist + ((pos - 2) & (CONV_RING - 1)));
-        const float h1 = __ldcg(hist + ((pos - 1) & (CONV_RING - 1)));
+        // every task keeps its own history of the channels it convolves (q and k of the head are
+        // duplicated across the head's 8 tasks), so nothing here is shared between CTAs
+        float* hist = L.conv_hist + ((size_t)c.cta * NCH + c.tid) * CONV_RING;
+        const float h3 = hist[(pos - 3) & (CONV_RING - 1)];
+        const float h2 = hist[(pos - 2) & (CONV_RING - 1)];
+        const float h1 = hist[(pos - 1) & (CONV_RING - 1)];
         const float cur = ll_wait(c, P.projl + ch, e_proj, W_PROJ);
         float a = h3 * taps.x;
         a = fmaf(h2, taps.y, a);
         a = fmaf(h1, taps.z, a);
         a = fmaf(cur, taps.w, a);
         qkv_s[c.tid] = silu_f(a);
-        if (c.tid >= 2 * S::LIN_DK || j == 0) hist[pos & (CONV_RING - 1)] = cur;
+        hist[pos & (CONV_RING - 1)] = cur;
     } else if (c.tid < NCH + 2) {
         const int off = (c.tid == NCH ? S::B_OFF : S::A_OFF) + h;
         qkv_s[c.tid] = ll_wait(c, P.projl + off, e_proj, W_PROJ);
@@ -453,7 +549,6 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     *reinterpret_cast<float4*>(srow) = make_float4(s0, s1, s2, s3);
     const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
     prof_stamp(c, op, 2);
-    __threadfence();  // conv history of the q/k channels is read by sibling CTAs in the next steps
     if (c.lane == 0) ll_store(P.mixl + h * S::LIN_DV + vcol, e_out, o);
     consumer_sync();  // the scratch aliases the GEMV input vector that the next prologue writes
 }
@@ -492,12 +587,16 @@ __device__ __forceinline__ void store1(void* base, size_t elem, float v) {
 }
 
 // Split-K decode attention over the paged cache.  Task (g, s): KV head g, positions
-// [s * ch, min(n, (s + 1) * ch)), run by CTA s * NKV + g.  With one split the task publishes the
-// normalised output itself; otherwise it writes (acc, m, l) partials and raises a flag, and the
-// split-0 task of each KV head merges all partials in split order.
+// [s * ch, min(n, (s + 1) * ch)), run by CTA s * NKV + g.  Cached K and V rows of the task are
+// requested before the task waits for its query, so that only one memory round trip sits between
+// the projection and the scores.  With one split the task publishes the normalised output itself;
+// otherwise every task publishes (acc, m, l) partials as flag-in-data words and then merges a
+// 1/nsplit share of the head group's outputs from all partials, in a fixed order.
 template <class S, bool KVF32>
 __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
+    constexpr int NOUT = S::QPK * S::HD;        // outputs per KV head
+    constexpr int PFK = 1, PFV = 16;            // rows prefetched per warp (K) and per thread (V)
     const int n = pos + 1;
     const int max_splits = min(c.grid / S::NKV, MAX_SPLITS);
     const int ch = attn_chunk(n, max_splits);
@@ -505,36 +604,60 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     if (c.cta >= nsplit * S::NKV) return;
     const int g = c.cta % S::NKV, sp = c.cta / S::NKV;
     const int p0 = sp * ch, p1 = min(n, p0 + ch);
+    const int np = p1 - p0;
     const bool has_new = (p1 == n);
 
-    float* q_s = c.sm.xs;                       // [4][256] normalised, rotated, pre-scaled queries
+    float* q_s = reinterpret_cast<float*>(c.sm.xq);   // [4][256] normalised, rotated, pre-scaled queries
     float* knew_s = q_s + S::QPK * S::HD;       // [256]
     float* vnew_s = knew_s + S::HD;             // [256]
     float* sc_s = vnew_s + S::HD;               // [4][ch] scores, then probabilities
     float* stat_s = c.sm.out_s;                 // [4] m, [4] l
 
+    const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
+    auto kv_elem = [&](int p) -> size_t {
+        const int blk = c.sm.bt_s[p >> 6];
+        return ((size_t)blk * S::NKV + g) * kv_head_stride + (size_t)(p & (KV_BLOCK - 1)) * S::HD;
+    };
+    // -- 0. request cached rows early: K rows of this warp's positions, V elements of this thread's dim
+    const int d = c.tid & (S::HD - 1), hp = c.tid >> 8;
+    float kpre[PFK][8], vpre[PFV];
+#pragma unroll
+    for (int i = 0; i < PFK; i++) {
+        const int p = p0 + c.warp + i * NCW;
+#pragma unroll
+        for (int j = 0; j < 8; j++) kpre[i][j] = 0.f;
+        if (p < p1 && p != pos) load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kpre[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < PFV; i++) {
+        const int p = p0 + i;
+        vpre[i] = (p < p1 && p != pos) ? load1<KVF32>(L.v_cache, kv_elem(p) + d) : 0.f;
+    }
+
     // -- 1. q (4 heads), new k, new v from the projection words; per-head RMSNorm; partial RoPE
     {
         const int hh = c.warp >> 2, qd = c.warp & 3;        // head within group, 64-wide quarter
-        const int d = qd * 64 + 2 * c.lane;
-        const int qrow = (g * S::QPK + hh) * 2 * S::HD + d;
-        float a, b;
-        ll_wait2(c, P.projl + qrow, e_proj, W_PROJ, a, b);
-        float ka = 0.f, kb = 0.f, va = 0.f, vb = 0.f;
-        if (hh == 0) ll_wait2(c, P.projl + S::ATT_K_OFF + g * S::HD + d, e_proj, W_PROJ, ka, kb);
-        if (hh == 1) ll_wait2(c, P.projl + S::ATT_V_OFF + g * S::HD + d, e_proj, W_PROJ, va, vb);
-        float* buf = c.sm.red_s + (c.red_n++ & 1) * NCW;    // q sums
-        float* buf2 = reinterpret_cast<float*>(c.sm.best_s);   // k sums [4]; best_s is idle outside the LM head
+        const int dd = qd * 64 + 2 * c.lane;
+        const u64* const ptrs[2] = {P.projl + (g * S::QPK + hh) * 2 * S::HD + dd,
+                                    hh == 0 ? P.projl + S::ATT_K_OFF + g * S::HD + dd
+                                            : (hh == 1 ? P.projl + S::ATT_V_OFF + g * S::HD + dd : nullptr)};
+        const uint32_t eps[2] = {e_proj, e_proj};
+        float v4[4];
+        ll_wait_pairs<2>(c, ptrs, eps, v4, W_PROJ);
+        float a = v4[0], b = v4[1];
+        float ka = hh == 0 ? v4[2] : 0.f, kb = hh == 0 ? v4[3] : 0.f;
+        const float va = v4[2], vb = v4[3];
+        float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);      // q sums [16], k sums [4]
         const float sq = warp_sum(a * a + b * b);
         const float sk = warp_sum(ka * ka + kb * kb);
         if (c.lane == 0) {
             buf[c.warp] = sq;
-            if (hh == 0) buf2[qd] = sk;
+            if (hh == 0) buf[NCW + qd] = sk;
         }
         consumer_sync();
         const float qss = buf[hh * 4] + buf[hh * 4 + 1] + buf[hh * 4 + 2] + buf[hh * 4 + 3];
         const float qinv = rsqrtf(qss * (1.0f / S::HD) + S::EPS);
-        const float2 qw = *reinterpret_cast<const float2*>(L.q_norm + d);
+        const float2 qw = *reinterpret_cast<const float2*>(L.q_norm + dd);
         a = a * qinv * (1.0f + qw.x);
         b = b * qinv * (1.0f + qw.y);
         float cs0 = 1.f, sn0 = 0.f, cs1 = 1.f, sn1 = 0.f;
@@ -549,12 +672,12 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             if (c.lane < 16) { a = a * cs0 - pa * sn0; b = b * cs1 - pb * sn1; }
             else { a = a * cs0 + pa * sn0; b = b * cs1 + pb * sn1; }
         }
-        q_s[hh * S::HD + d] = a * 0.0625f;          // 1/sqrt(256), exact
-        q_s[hh * S::HD + d + 1] = b * 0.0625f;
+        q_s[hh * S::HD + dd] = a * 0.0625f;          // 1/sqrt(256), exact
+        q_s[hh * S::HD + dd + 1] = b * 0.0625f;
         if (hh == 0) {
-            const float kss = buf2[0] + buf2[1] + buf2[2] + buf2[3];
+            const float kss = buf[NCW] + buf[NCW + 1] + buf[NCW + 2] + buf[NCW + 3];
             const float kinv = rsqrtf(kss * (1.0f / S::HD) + S::EPS);
-            const float2 kw = *reinterpret_cast<const float2*>(L.k_norm + d);
+            const float2 kw = *reinterpret_cast<const float2*>(L.k_norm + dd);
             ka = ka * kinv * (1.0f + kw.x);
             kb = kb * kinv * (1.0f + kw.y);
             if (qd == 0) {
@@ -562,21 +685,16 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
                 if (c.lane < 16) { ka = ka * cs0 - pa * sn0; kb = kb * cs1 - pb * sn1; }
                 else { ka = ka * cs0 + pa * sn0; kb = kb * cs1 + pb * sn1; }
             }
-            knew_s[d] = round_kv<KVF32>(ka);
-            knew_s[d + 1] = round_kv<KVF32>(kb);
+            knew_s[dd] = round_kv<KVF32>(ka);
+            knew_s[dd + 1] = round_kv<KVF32>(kb);
         }
         if (hh == 1) {
-            vnew_s[d] = round_kv<KVF32>(va);
-            vnew_s[d + 1] = round_kv<KVF32>(vb);
+            vnew_s[dd] = round_kv<KVF32>(va);
+            vnew_s[dd + 1] = round_kv<KVF32>(vb);
         }
         consumer_sync();
         prof_stamp(c, op, 1);
     }
-    const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
-    auto kv_elem = [&](int p) -> size_t {
-        const int blk = P.block_table[p >> 6];
-        return ((size_t)blk * S::NKV + g) * kv_head_stride + (size_t)(p & (KV_BLOCK - 1)) * S::HD;
-    };
     // -- 2. append the new position (the task that owns it)
     if (has_new && c.tid < S::HD) {
         const size_t e = kv_elem(pos) + c.tid;
@@ -593,14 +711,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             q[hh][0] = x.x; q[hh][1] = x.y; q[hh][2] = x.z; q[hh][3] = x.w;
             q[hh][4] = y.x; q[hh][5] = y.y; q[hh][6] = y.z; q[hh][7] = y.w;
         }
-        for (int p = p0 + c.warp; p < p1; p += NCW) {
-            float kk[8];
-            if (p == pos) {
-#pragma unroll
-                for (int i = 0; i < 8; i++) kk[i] = knew_s[8 * c.lane + i];
-            } else {
-                load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kk);
-            }
+        auto score = [&](int p, const float (&kk)[8]) {
             float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -616,11 +727,31 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
                 sc_s[2 * ch + (p - p0)] = d2;
                 sc_s[3 * ch + (p - p0)] = d3;
             }
+        };
+#pragma unroll
+        for (int i = 0; i < PFK; i++) {
+            const int p = p0 + c.warp + i * NCW;
+            if (p < p1) {
+                if (p == pos) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) kpre[i][j] = knew_s[8 * c.lane + j];
+                }
+                score(p, kpre[i]);
+            }
+        }
+        for (int p = p0 + c.warp + PFK * NCW; p < p1; p += NCW) {
+            float kk[8];
+            if (p == pos) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) kk[j] = knew_s[8 * c.lane + j];
+            } else {
+                load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kk);
+            }
+            score(p, kk);
         }
     }
     consumer_sync();
     // -- 4. softmax statistics: warp hh < 4 handles head hh
-    const int np = p1 - p0;
     if (c.warp < S::QPK) {
         float* row = sc_s + c.warp * ch;
         float m = -INFINITY;
@@ -640,12 +771,19 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     }
     consumer_sync();
     // -- 5. weighted values: thread -> dim d, heads 2*hp and 2*hp+1
-    const int d = c.tid & (S::HD - 1), hp = c.tid >> 8;
     float acc0 = 0.f, acc1 = 0.f;
     {
         const float* pr0 = sc_s + (2 * hp) * ch;
         const float* pr1 = sc_s + (2 * hp + 1) * ch;
-        int i = 0;
+#pragma unroll
+        for (int i = 0; i < PFV; i++) {
+            if (i < np) {
+                const float v = (p0 + i == pos) ? vnew_s[d] : vpre[i];
+                acc0 = fmaf(pr0[i], v, acc0);
+                acc1 = fmaf(pr1[i], v, acc1);
+            }
+        }
+        int i = PFV;
         for (; i + 8 <= np; i += 8) {
             float v[8];
 #pragma unroll
@@ -669,52 +807,88 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     u64* out = P.mixl + (size_t)(g * S::QPK) * S::HD;
     prof_stamp(c, op, 2);
     if (nsplit == 1) {
-        __threadfence();  // the appended K/V row is read by other CTAs in later steps
         ll_store(out + (2 * hp) * S::HD + d, e_out, acc0 / stat_s[S::QPK + 2 * hp]);
         ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc1 / stat_s[S::QPK + 2 * hp + 1]);
-        consumer_sync();  // scratch aliases the GEMV input vector that the next prologue writes
+        // The appended K/V row is read by other CTAs from the next step on.  They get there only
+        // through words this CTA publishes after this fence, so the fence can sit off the critical path.
+        __threadfence();
+        consumer_sync();  // scratch aliases the GEMV input planes that the next prologue writes
         return;
     }
-    // -- 6. partials + flag; split 0 merges
-    float* part = P.attn_part + ((size_t)g * MAX_SPLITS + sp) * S::PART_STRIDE;
-    part[(2 * hp) * S::HD + d] = acc0;
-    part[(2 * hp + 1) * S::HD + d] = acc1;
-    if (c.tid < 2 * S::QPK) part[S::QPK * S::HD + c.tid] = stat_s[c.tid];
-    __threadfence();
-    consumer_sync();
-    unsigned* flags = P.attn_flag + (size_t)g * MAX_SPLITS;
-    if (c.tid == 0) st_relaxed_u32(flags + sp, e_out);
-    if (sp != 0) return;   // (the barrier above already fenced off the scratch reads)
-    for (int s2 = c.tid; s2 < nsplit; s2 += NCT) {
-        Spin s;
-        while (ld_relaxed_u32(flags + s2) != e_out) {
-            if (MK_SPIN_FAIL(c, s, W_PART)) {
+    // -- 6. partials as flag-in-data words: acc [4][256], then (m, l) per head
+    u64* part = P.attn_part + ((size_t)g * MAX_SPLITS + sp) * S::PART_STRIDE;
+    ll_store(part + (2 * hp) * S::HD + d, e_out, acc0);
+    ll_store(part + (2 * hp + 1) * S::HD + d, e_out, acc1);
+    if (c.tid < 2 * S::QPK) ll_store(part + NOUT + c.tid, e_out, stat_s[(c.tid & 1) * S::QPK + (c.tid >> 1)]);
+    // -- 7. merge this task's share of the outputs.  `tpo` threads share one output, each takes the
+    //       splits s = sub, sub + tpo, ...; a fixed shuffle tree combines them.
+    const int opc = (NOUT + nsplit - 1) / nsplit;           // outputs per task
+    int tpo = 1;
+    while (tpo < 32 && 2 * tpo * opc <= NCT && tpo < nsplit) tpo *= 2;
+    const int oi = c.tid / tpo, sub = c.tid % tpo;
+    const int o = sp * opc + oi;
+    const bool live = oi < opc && o < NOUT;
+    const int h = o / S::HD;
+    const u64* pg = P.attn_part + (size_t)g * MAX_SPLITS * S::PART_STRIDE;
+    constexpr int SPT = 4;                                   // splits per thread at most (MAX_SPLITS / 32)
+    float mv[SPT], lv[SPT], av[SPT];
+    {
+        u64 wa[SPT], wm[SPT], wl[SPT];
+#pragma unroll
+        for (int i = 0; i < SPT; i++) {
+            const int s2 = sub + i * tpo;
+            wa[i] = wm[i] = wl[i] = 0;
+            if (live && s2 < nsplit) {
+                const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
+                wa[i] = ll_load(ps + o);
+                ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
+            }
+        }
+        Spin spin;
+        while (true) {
+            bool ok = true;
+#pragma unroll
+            for (int i = 0; i < SPT; i++) {
+                const int s2 = sub + i * tpo;
+                if (live && s2 < nsplit) {
+                    const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
+                    if ((uint32_t)(wa[i] >> 32) != e_out) { ok = false; wa[i] = ll_load(ps + o); }
+                    if ((uint32_t)(wm[i] >> 32) != e_out || (uint32_t)(wl[i] >> 32) != e_out) {
+                        ok = false;
+                        ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
+                    }
+                }
+            }
+            if (ok) break;
+            if (MK_SPIN_FAIL(c, spin, W_PART)) {
                 c.dead = true;
                 break;
             }
         }
+#pragma unroll
+        for (int i = 0; i < SPT; i++) {
+            const bool have = live && sub + i * tpo < nsplit;
+            mv[i] = have ? __uint_as_float((uint32_t)wm[i]) : -INFINITY;
+            lv[i] = have ? __uint_as_float((uint32_t)wl[i]) : 0.f;
+            av[i] = have ? __uint_as_float((uint32_t)wa[i]) : 0.f;
+        }
     }
-    __threadfence();
-    consumer_sync();
-    const float* pg = P.attn_part + (size_t)g * MAX_SPLITS * S::PART_STRIDE;
-    float M0 = -INFINITY, M1 = -INFINITY;
-    for (int s2 = 0; s2 < nsplit; s2++) {
-        const float* ps = pg + (size_t)s2 * S::PART_STRIDE + S::QPK * S::HD;
-        M0 = fmaxf(M0, __ldcg(ps + 2 * hp));
-        M1 = fmaxf(M1, __ldcg(ps + 2 * hp + 1));
+    float M = fmaxf(fmaxf(mv[0], mv[1]), fmaxf(mv[2], mv[3]));
+    for (int x = 1; x < tpo; x *= 2) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
+    float Ls = 0.f, Os = 0.f;
+#pragma unroll
+    for (int i = 0; i < SPT; i++) {
+        const float w = mv[i] == -INFINITY ? 0.f : __expf(mv[i] - M);
+        Ls = fmaf(lv[i], w, Ls);
+        Os = fmaf(av[i], w, Os);
     }
-    float o0 = 0.f, o1 = 0.f, l0 = 0.f, l1 = 0.f;
-    for (int s2 = 0; s2 < nsplit; s2++) {
-        const float* pa = pg + (size_t)s2 * S::PART_STRIDE;
-        const float* ps = pa + S::QPK * S::HD;
-        const float w0 = __expf(__ldcg(ps + 2 * hp) - M0), w1 = __expf(__ldcg(ps + 2 * hp + 1) - M1);
-        l0 = fmaf(__ldcg(ps + S::QPK + 2 * hp), w0, l0);
-        l1 = fmaf(__ldcg(ps + S::QPK + 2 * hp + 1), w1, l1);
-        o0 = fmaf(__ldcg(pa + (2 * hp) * S::HD + d), w0, o0);
-        o1 = fmaf(__ldcg(pa + (2 * hp + 1) * S::HD + d), w1, o1);
+    for (int x = 1; x < tpo; x *= 2) {
+        Ls += __shfl_xor_sync(0xffffffffu, Ls, x);
+        Os += __shfl_xor_sync(0xffffffffu, Os, x);
     }
-    ll_store(out + (2 * hp) * S::HD + d, e_out, o0 / l0);
-    ll_store(out + (2 * hp + 1) * S::HD + d, e_out, o1 / l1);
+    if (live && sub == 0) ll_store(out + o, e_out, Os / Ls);
+    __threadfence();      // K/V append before anything this CTA publishes later (see above)
+    consumer_sync();      // scratch aliases the GEMV input planes that the next prologue writes
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------
@@ -728,17 +902,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     {
         uint8_t* p = smem_raw;
         c.sm.ring = p; p += SMEM_RING;
-        c.sm.xs = reinterpret_cast<float*>(p); p += SMEM_XS;
-        c.sm.scale_s = reinterpret_cast<float*>(p); p += SMEM_SCALE;
-        c.sm.out_s = reinterpret_cast<float*>(p); p += 2 * MAX_BODY_ROWS * 4;      // 512
-        c.sm.red_s = reinterpret_cast<float*>(p); p += 2 * NCW * 4;                // 128
+        c.sm.xq = p; p += SMEM_XQ;
+        c.sm.part_s = reinterpret_cast<float*>(p); p += 2 * NCW * 32 * 4;          // 4096
+        c.sm.bt_s = reinterpret_cast<int*>(p); p += MAX_BLOCKS * 4;                // 2048
+        c.sm.out_s = reinterpret_cast<float*>(p); p += 64;
+        c.sm.red_s = reinterpret_cast<float*>(p); p += 2 * 2 * NCW * 4;            // 256
         c.sm.xown = reinterpret_cast<float*>(p); p += 16 * 4;                      // 64
         c.sm.best_s = reinterpret_cast<u64*>(p); p += NCW * 8;                     // 128
         c.sm.full = reinterpret_cast<uint64_t*>(p); p += NSTAGE * 8;
         c.sm.empty = reinterpret_cast<uint64_t*>(p); p += NSTAGE * 8;
+        c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
-        c.sm.tok_s = reinterpret_cast<volatile int*>(p); p += 8;
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
@@ -752,9 +927,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         }
         *c.sm.abort_flag = 0;
         *c.sm.quit_flag = 0;
+        *c.sm.xscale_s = 1.0f;
         fence_barrier_init();
         fence_proxy_async();
     }
+    for (int i = c.tid; i < P.max_seq / KV_BLOCK; i += NTHREADS) c.sm.bt_s[i] = P.block_table[i];
     __syncthreads();
 
     if (c.warp == NCW) {
@@ -763,6 +940,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     }
 
     // ---------------- consumers ----------------
+    constexpr int WB = Q8 ? 1 : 2;                       // bytes per weight
     const int OPS = P.n_layers * OPS_PER_LAYER + 1;     // epochs per step
     int xr0, xr1;                                        // residual rows this CTA owns
     cta_rows(S::HID, 1, c.cta, c.grid, xr0, xr1);
@@ -822,137 +1000,119 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             const LayerP& L = P.layer[l];
             const uint32_t eA = e0 + l * OPS_PER_LAYER, eB = eA + 1, eC = eA + 2, eD = eA + 3, eE = eA + 4;
             const bool attn = L.kind != 0;
+            const int op0 = l * OPS_PER_LAYER;
             // ---- A: in-projection
             {
-                const int op = l * OPS_PER_LAYER;
-                prof_stamp(c, op, 0);
+                prof_stamp(c, op0, 0);
                 int r0, r1;
                 cta_rows(attn ? S::ATT_IN : S::GDN_IN, 1, c.cta, c.grid, r0, r1);
-                const int nrows = r1 - r0;
-                float sc = 1.f;
-                if (Q8 && c.tid < nrows) sc = L.s_in[r0 + c.tid];
                 if (l > 0) ll_wait2(c, P.xl + 2 * c.tid, eA - 1, W_X, x0, x1);
                 stage_rmsnorm<S, Q8>(c, x0, x1, L.in_norm);
-                prof_stamp(c, op, 1);
-                float* out_s = c.sm.out_s;
-                gemv_stream<S::HID, Q8, 1, Q8 ? 2 : 1>(c, r0, r1, [&](int row, int, float v) {
-                    if (c.lane == 0) out_s[row - r0] = v;
+                prof_stamp(c, op0, 1);
+                gemv_mma<Q8>(c, r0, r1, S::HID * WB, L.s_in, [&](int, int row, float v, bool ok) {
+                    if (ok) ll_store(P.projl + row, eA, v);
                 });
-                consumer_sync();
-                prof_stamp(c, op, 2);
-                if (c.tid < nrows) ll_store(P.projl + r0 + c.tid, eA, out_s[c.tid] * sc);
-                prof_stamp(c, op, 3);
+                prof_stamp(c, op0, 3);
             }
             // ---- B: mixer
-            prof_stamp(c, l * OPS_PER_LAYER + 1, 0);
-            if (attn) attn_op<S, KVF32>(c, P, L, pos, eA, eB, l * OPS_PER_LAYER + 1);
-            else gdn_op<S>(c, P, L, pos, eA, eB, l * OPS_PER_LAYER + 1);
-            prof_stamp(c, l * OPS_PER_LAYER + 1, 3);
+            prof_stamp(c, op0 + 1, 0);
+            if (attn) attn_op<S, KVF32>(c, P, L, pos, eA, eB, op0 + 1);
+            else gdn_op<S>(c, P, L, pos, eA, eB, op0 + 1);
+            prof_stamp(c, op0 + 1, 3);
             // ---- C: out-projection + residual
             {
-                const int op = l * OPS_PER_LAYER + 2;
+                const int op = op0 + 2;
                 prof_stamp(c, op, 0);
-                const int nrows = xr1 - xr0;
-                float sc = 1.f;
-                if (Q8 && c.tid < nrows) sc = L.s_out[xr0 + c.tid];
                 // each thread stages 4 consecutive mixer outputs; a warp covers 128 = one DeltaNet head
                 const int k = 4 * c.tid;
                 float m[4];
-                ll_wait2(c, P.mixl + k, eB, W_MIX, m[0], m[1]);
-                ll_wait2(c, P.mixl + k + 2, eB, W_MIX, m[2], m[3]);
-                if (attn) {
-                    const int head = k / S::HD, d = k % S::HD;
-                    float gt[4];
-                    const u64* gp = P.projl + head * 2 * S::HD + S::HD + d;
-                    ll_wait2(c, gp, eA, W_PROJ, gt[0], gt[1]);
-                    ll_wait2(c, gp + 2, eA, W_PROJ, gt[2], gt[3]);
+                {
+                    const u64* aux = attn ? P.projl + (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD)   // sigmoid gate
+                                          : P.projl + S::Z_OFF + k;                                    // z
+                    const u64* const ptrs[4] = {P.mixl + k, P.mixl + k + 2, aux, aux + 2};
+                    const uint32_t eps[4] = {eB, eB, eA, eA};
+                    float v[8];
+                    ll_wait_pairs<4>(c, ptrs, eps, v, W_MIX);
+                    if (attn) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) c.sm.xs[xs_index<Q8>(k + i)] = m[i] * sigmoid_f(gt[i]);
-                } else {
-                    float z[4];
-                    ll_wait2(c, P.projl + S::Z_OFF + k, eA, W_PROJ, z[0], z[1]);
-                    ll_wait2(c, P.projl + S::Z_OFF + k + 2, eA, W_PROJ, z[2], z[3]);
-                    const float ss = warp_sum(m[0] * m[0] + m[1] * m[1] + m[2] * m[2] + m[3] * m[3]);
-                    const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
-                    const float4 gw = *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
-                    c.sm.xs[xs_index<Q8>(k)] = m[0] * inv * gw.x * silu_f(z[0]);
-                    c.sm.xs[xs_index<Q8>(k + 1)] = m[1] * inv * gw.y * silu_f(z[1]);
-                    c.sm.xs[xs_index<Q8>(k + 2)] = m[2] * inv * gw.z * silu_f(z[2]);
-                    c.sm.xs[xs_index<Q8>(k + 3)] = m[3] * inv * gw.w * silu_f(z[3]);
+                        for (int i = 0; i < 4; i++) m[i] = v[i] * sigmoid_f(v[4 + i]);
+                    } else {
+                        const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
+                        const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
+                        const float4 gw = *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
+                        m[0] = v[0] * inv * gw.x * silu_f(v[4]);
+                        m[1] = v[1] * inv * gw.y * silu_f(v[5]);
+                        m[2] = v[2] * inv * gw.z * silu_f(v[6]);
+                        m[3] = v[3] * inv * gw.w * silu_f(v[7]);
+                    }
                 }
-                consumer_sync();
+                const float scale = block_scale<Q8>(c, fmaxf(fmaxf(fabsf(m[0]), fabsf(m[1])), fmaxf(fabsf(m[2]), fabsf(m[3]))));
+                stage_pair<Q8>(c.sm.xq, S::MIX * WB, k, m[0], m[1], scale);
+                stage_pair<Q8>(c.sm.xq, S::MIX * WB, k + 2, m[2], m[3], scale);
+                finish_stage(c, scale);
                 prof_stamp(c, op, 1);
-                float* out_s = c.sm.out_s;
-                gemv_stream<S::MIX, Q8, 2, 1>(c, xr0, xr1, [&](int row, int seg, float v) {
-                    if (c.lane == 0) out_s[(row - xr0) * 2 + seg] = v;
+                gemv_mma<Q8>(c, xr0, xr1, S::MIX * WB, L.s_out, [&](int, int row, float v, bool ok) {
+                    if (ok) {
+                        const float xn = c.sm.xown[row - xr0] + v;
+                        c.sm.xown[row - xr0] = xn;
+                        ll_store(P.xl + row, eC, xn);
+                    }
                 });
-                consumer_sync();
-                prof_stamp(c, op, 2);
-                if (c.tid < nrows) {
-                    const float y = (out_s[2 * c.tid] + out_s[2 * c.tid + 1]) * sc;
-                    const float xn = c.sm.xown[c.tid] + y;
-                    c.sm.xown[c.tid] = xn;
-                    ll_store(P.xl + xr0 + c.tid, eC, xn);
-                }
                 prof_stamp(c, op, 3);
             }
             // ---- D: gate/up + SwiGLU
             {
-                const int op = l * OPS_PER_LAYER + 3;
+                const int op = op0 + 3;
                 prof_stamp(c, op, 0);
                 int r0, r1;
                 cta_rows(2 * S::INTER, 2, c.cta, c.grid, r0, r1);
-                const int npairs = (r1 - r0) / 2;
-                float2 sc = make_float2(1.f, 1.f);
-                if (Q8 && c.tid < npairs) sc = *reinterpret_cast<const float2*>(L.s_gu + r0 + 2 * c.tid);
                 ll_wait2(c, P.xl + 2 * c.tid, eC, W_X, x0, x1);
                 stage_rmsnorm<S, Q8>(c, x0, x1, L.post_norm);
                 prof_stamp(c, op, 1);
-                float* out_s = c.sm.out_s;
-                gemv_stream<S::HID, Q8, 1, Q8 ? 2 : 1>(c, r0, r1, [&](int row, int, float v) {
-                    if (c.lane == 0) out_s[row - r0] = v;
+                gemv_mma<Q8>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, float v, bool ok) {
+                    // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane
+                    const float up = __shfl_down_sync(0xffffffffu, v, 1);
+                    if (ok && !(lane & 1)) ll_store(P.actl + (row >> 1), eD, silu_f(v) * up);
                 });
-                consumer_sync();
-                prof_stamp(c, op, 2);
-                if (c.tid < npairs) {
-                    const float gate = out_s[2 * c.tid] * sc.x, up = out_s[2 * c.tid + 1] * sc.y;
-                    ll_store(P.actl + r0 / 2 + c.tid, eD, silu_f(gate) * up);
-                }
                 prof_stamp(c, op, 3);
             }
             // ---- E: down-projection + residual
             {
-                const int op = l * OPS_PER_LAYER + 4;
+                const int op = op0 + 4;
                 prof_stamp(c, op, 0);
-                const int nrows = xr1 - xr0;
-                float sc = 1.f;
-                if (Q8 && c.tid < nrows) sc = L.s_down[xr0 + c.tid];
-                for (int k = 2 * c.tid; k < S::INTER; k += 2 * NCT) {
-                    float a, b;
-                    ll_wait2(c, P.actl + k, eD, W_ACT, a, b);
-                    c.sm.xs[xs_index<Q8>(k)] = a;
-                    c.sm.xs[xs_index<Q8>(k + 1)] = b;
-                }
-                consumer_sync();
-                prof_stamp(c, op, 1);
-                float* out_s = c.sm.out_s;
-                constexpr int KS = Q8 ? 2 : 4;   // bf16 rows are 7 KB: 4 per chunk, so 4 warps share a row
-                gemv_stream<S::INTER, Q8, KS, 1>(c, xr0, xr1, [&](int row, int seg, float v) {
-                    if (c.lane == 0) out_s[(row - xr0) * KS + seg] = v;
-                });
-                failed = consumer_any(c.dead);
-                prof_stamp(c, op, 2);
-                if (c.tid < nrows) {
-                    float y = 0.f;
+                float a[8];
+                float mx = 0.f;
+                {
+                    const u64* ptrs[4];
+                    const uint32_t eps[4] = {eD, eD, eD, eD};
 #pragma unroll
-                    for (int i = 0; i < KS; i++) y += out_s[KS * c.tid + i];
-                    y *= sc;
-                    const float xn = c.sm.xown[c.tid] + y;
-                    c.sm.xown[c.tid] = xn;
-                    ll_store(P.xl + xr0 + c.tid, eE, xn);
-                    if (A.resid_out && l == P.n_layers - 1) A.resid_out[(size_t)s * S::HID + xr0 + c.tid] = xn;
+                    for (int j = 0; j < 4; j++) {
+                        const int k = 2 * c.tid + j * 2 * NCT;
+                        ptrs[j] = k < S::INTER ? P.actl + k : nullptr;
+                    }
+                    ll_wait_pairs<4>(c, ptrs, eps, a, W_ACT);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) mx = fmaxf(mx, fabsf(a[j]));
                 }
+                const float scale = block_scale<Q8>(c, mx);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int k = 2 * c.tid + j * 2 * NCT;
+                    if (k < S::INTER) stage_pair<Q8>(c.sm.xq, S::INTER * WB, k, a[2 * j], a[2 * j + 1], scale);
+                }
+                finish_stage(c, scale);
+                prof_stamp(c, op, 1);
+                const bool last = l == P.n_layers - 1;
+                gemv_mma<Q8>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, float v, bool ok) {
+                    if (ok) {
+                        const float xn = c.sm.xown[row - xr0] + v;
+                        c.sm.xown[row - xr0] = xn;
+                        ll_store(P.xl + row, eE, xn);
+                        if (A.resid_out && last) A.resid_out[(size_t)s * S::HID + row] = xn;
+                    }
+                });
                 prof_stamp(c, op, 3);
+                failed = consumer_any(c.dead);
             }
             if (failed) break;
         }
@@ -962,18 +1122,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             const uint32_t eL = e0 + (uint32_t)OPS - 1;
             const int op = P.n_layers * OPS_PER_LAYER;
             prof_stamp(c, op, 0);
-            const int nrows = lr1 - lr0;
-            if (Q8) for (int i = c.tid; i < nrows; i += NCT) c.sm.scale_s[i] = P.lm_scale[lr0 + i];
             ll_wait2(c, P.xl + 2 * c.tid, eL - 1, W_X, x0, x1);
             stage_rmsnorm<S, Q8>(c, x0, x1, P.final_norm);
             prof_stamp(c, op, 1);
             u64 best = 0;
             float* logits = A.logits_out ? A.logits_out + (size_t)s * P.vocab : nullptr;
             const float invT = A.inv_temperature;
-            const float* scale_s = c.sm.scale_s;
-            gemv_stream<S::HID, Q8, 1, Q8 ? 2 : 1>(c, lr0, lr1, [&](int row, int, float v) {
-                if (Q8) v *= scale_s[row - lr0];
-                if (logits && c.lane == 0) logits[row] = v;
+            gemv_mma<Q8>(c, lr0, lr1, S::HID * WB, P.lm_scale, [&](int, int row, float v, bool ok) {
+                if (!ok) return;
+                if (logits) logits[row] = v;
                 float score = v;
                 if (invT != 0.f) {
                     const uint32_t hsh = mk_mix32(A.seed, (uint32_t)pos, (uint32_t)row);
@@ -983,17 +1140,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 const u64 key = score_key(score, row);
                 best = key > best ? key : best;
             });
-            if (c.lane == 0) c.sm.best_s[c.warp] = best;
-            failed = consumer_any(c.dead);
-            prof_stamp(c, op, 2);
-            if (c.tid == 0) {
-                u64 b = 0;
-                for (int i = 0; i < NCW; i++) b = c.sm.best_s[i] > b ? c.sm.best_s[i] : b;
-                ll_store_bits(P.lml + 2 * c.cta, eL, (uint32_t)(b >> 32));
-                ll_store_bits(P.lml + 2 * c.cta + 1, eL, (uint32_t)b);
+            if (c.warp == 0) {
+                best = warp_max_u64(best);
+                if (c.lane == 0) {
+                    ll_store_bits(P.lml + 2 * c.cta, eL, (uint32_t)(best >> 32));
+                    ll_store_bits(P.lml + 2 * c.cta + 1, eL, (uint32_t)best);
+                }
             }
             prof_stamp(c, op, 3);
-            consumer_sync();   // best_s is read by thread 0 above before anyone reuses it
+            failed = consumer_any(c.dead);
             if (failed) break;
         }
         steps_done = s + 1;

@@ -22,6 +22,7 @@ import torch
 
 from . import _lib
 from .config import Config
+from .pack import as_bytes, pack_rows
 from .quant import quantize_int8_rows
 
 # Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
@@ -66,6 +67,9 @@ class Megakernel:
         assert isinstance(cfg, Config) or hasattr(cfg, "layer_types")
         self._check_shape(cfg)
         self.KV_BLOCK = _lib.query("KV_BLOCK")
+        self.GDN_SLICE = 16                                  # value columns per recurrence task
+        self.GDN_TASKS = cfg.lin_heads * cfg.lin_v_dim // self.GDN_SLICE
+        self.TASK_CHANNELS = 2 * cfg.lin_k_dim + self.GDN_SLICE
         self.max_seq = (max_seq + self.KV_BLOCK - 1) // self.KV_BLOCK * self.KV_BLOCK
         self.grid = torch.cuda.get_device_properties(device).multi_processor_count
         self._keep = []   # every tensor whose address the kernel holds
@@ -80,13 +84,21 @@ class Megakernel:
 
         q8 = quant == "int8"
 
-        def mat(t):
-            """A GEMV weight in the kernel's format: (address, scale address)."""
+        slot_bytes = _lib.query("SLOT_BYTES")
+
+        def plain(t):
+            """A weight matrix in the kernel's element format, row-major: (tensor, scales or None)."""
             t = t.to(device)
             if q8:
                 q, s = quantize_int8_rows(t)
-                return keep(q), keep(s)
-            return keep(t.to(torch.bfloat16)), 0
+                return (q.to(torch.int16) - 128).to(torch.int8), s      # signed two's complement
+            return t.to(torch.bfloat16), None
+
+        def mat(t, unit=1):
+            """A GEMV weight in the kernel's tile layout: (address, scale address)."""
+            m, s = plain(t)
+            packed = pack_rows(as_bytes(m), unit, self.grid, slot_bytes)
+            return keep(packed), (keep(s) if s is not None else 0)
 
         kvt = torch.float32 if kv_dtype == "fp32" else torch.bfloat16
         n_blocks = self.max_seq // self.KV_BLOCK
@@ -99,7 +111,7 @@ class Megakernel:
             m = f"layers.{i}."
             rec = dict.fromkeys(F, 0)
             gu = torch.stack([w[m + "mlp.gate_proj.weight"], w[m + "mlp.up_proj.weight"]], dim=1).reshape(-1, cfg.hidden)
-            rec["w_gu"], rec["s_gu"] = mat(gu)
+            rec["w_gu"], rec["s_gu"] = mat(gu, unit=2)
             rec["w_down"], rec["s_down"] = mat(w[m + "mlp.down_proj.weight"])
             rec["in_norm"] = f32(w[m + "input_layernorm.weight"])
             rec["post_norm"] = f32(w[m + "post_attention_layernorm.weight"])
@@ -113,7 +125,7 @@ class Megakernel:
                 rec["A_log"] = f32(w[p + "A_log"])
                 rec["dt_bias"] = f32(w[p + "dt_bias"])
                 rec["gdn_norm"] = f32(w[p + "norm.weight"])
-                hist = zeros(cfg.conv_dim, ring)
+                hist = zeros(self.GDN_TASKS, self.TASK_CHANNELS, ring)   # per recurrence task
                 st = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)   # [head][v][k]: the oracle's transposed
                 bak = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)
                 self.conv_hist.append(hist)
@@ -143,18 +155,17 @@ class Megakernel:
         # flag-in-data activation buffers: (epoch << 32) | fp32 bits
         self.ll = [torch.zeros(n, **u64) for n in (cfg.hidden, proj_max, mix, cfg.intermediate, 2 * self.grid)]
         max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
-        self.attn_part = zeros(cfg.n_kv_heads * max_splits * part_stride)
+        self.attn_part = zeros(cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
         self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
         self.block_table = torch.arange(n_blocks, device=device, dtype=torch.int32)
         self.status = zeros(4, dtype=torch.int32)
 
         self.embed = w["embed_tokens.weight"].to(device)
         self.final_norm = w["norm.weight"].to(device)
-        embed_ptr, embed_scale = mat(self.embed)
-        if "lm_head.weight" in w:
-            lm_ptr, lm_scale = mat(w["lm_head.weight"])
-        else:
-            lm_ptr, lm_scale = embed_ptr, embed_scale
+        # lookups read a plain row-major table; the LM head streams the same rows in the tile layout
+        table, table_scale = plain(self.embed)
+        embed_ptr, embed_scale = keep(table), (keep(table_scale) if table_scale is not None else 0)
+        lm_ptr, lm_scale = mat(w["lm_head.weight"] if "lm_head.weight" in w else self.embed)
         g = dict.fromkeys(_lib.GLOBAL_FIELDS, 0)
         g.update(embed=embed_ptr, embed_scale=embed_scale, lm_head=lm_ptr, lm_scale=lm_scale,
                  final_norm=f32(self.final_norm), rope_cos=keep(cos), rope_sin=keep(sin),
@@ -167,7 +178,7 @@ class Megakernel:
 
         desc = _lib.ModelDesc(shape=_lib.MK_SHAPE_QWEN35_08B, n_layers=cfg.n_layers, vocab=cfg.vocab,
                               max_seq=self.max_seq, quant=_lib.MK_QUANT[quant], kv_dtype=_lib.MK_KV[kv_dtype],
-                              draft_vocab=0, device=device.index)
+                              draft_vocab=0, device=device.index, grid=self.grid)
         self._h = ctypes.c_void_p()
         _lib.check(self.lib.mk_create(ctypes.byref(desc), ctypes.byref(self._h)))
         lv, gv = _lib.i64_array(layer_vals), _lib.i64_array([g[f] for f in _lib.GLOBAL_FIELDS])
@@ -217,6 +228,7 @@ class Megakernel:
         for t in self.conv_hist + self.state + self.ll:
             t.zero_()
         self.attn_flag.zero_()
+        self.attn_part.zero_()
         self.status.zero_()
         self.epoch = 1   # the buffers are zero, so epoch 0 never looks ready
         self.pos = 0
@@ -323,6 +335,21 @@ class Megakernel:
         """Recurrent state of the i-th DeltaNet layer as [head][k][v] (the reference decoder's layout,
         `qwen_mk/reference.py:54`; the kernel stores [head][v][k])."""
         return self.state[i].transpose(1, 2).contiguous()
+
+    def conv_window(self, i):
+        """Last three conv inputs of the i-th DeltaNet layer as [conv_dim, 3], oldest first (the
+        reference decoder's `conv_hist`, `qwen_mk/reference.py:53,70-71`)."""
+        c, ring = self.cfg, self.conv_hist[i].shape[-1]
+        slots = [(self.pos - 3 + j) % ring for j in range(3)]
+        h = self.conv_hist[i][:, :, slots]                       # [task, channel, 3]
+        spt = c.lin_v_dim // self.GDN_SLICE                     # tasks per head
+        out = torch.empty(c.conv_dim, 3, device=self.device)
+        nqk = c.lin_heads * c.lin_k_dim
+        first = h[::spt]                                        # the head's first task holds its q and k
+        out[:nqk] = first[:, : c.lin_k_dim].reshape(nqk, 3)
+        out[nqk: 2 * nqk] = first[:, c.lin_k_dim: 2 * c.lin_k_dim].reshape(nqk, 3)
+        out[2 * nqk:] = h[:, 2 * c.lin_k_dim:].reshape(c.lin_heads * c.lin_v_dim, 3)
+        return out
 
     def kv_rows(self, i, n):
         """K, V of the i-th attention layer for positions [0, n) as [kv_head, n, head_dim] fp32."""

@@ -1,0 +1,82 @@
+"""Weight layout of the decode kernel's GEMV: row slices per CTA, 8-row groups, k-block major.
+
+The kernel gives CTA `c` of `grid` the contiguous rows `plan_rows(N, unit, c, grid)` of every
+matrix and streams them through shared memory in chunks of `slot_bytes // row_bytes` rows.  Inside a
+chunk, rows are taken in groups of up to 8, and a group is stored k-block major: the first 64 bytes
+(64 int8 or 32 bf16 weights) of each of its rows, then the second 64 bytes of each row, and so on.
+A warp's 128-bit loads then fetch an 8-row x 64-byte tile as one contiguous 512-byte run, laid out
+exactly as the tensor-core instruction wants its second operand.  The bytes of a CTA's slice stay
+one contiguous span, so a chunk is still a single bulk copy.
+
+The layout depends on the grid size (one CTA per SM), so weights are packed for the device they will
+run on.  The reference's packers are geometry-dependent in the same way
+(`common/mkcore/pack.py:25-109`); for the 0.8B CUDA kernel the reference needs no packing beyond the
+gate/up row interleave (`qwen3.5-0.8b/qwen_mk/engine.py:86,100`), which `engine.py` keeps.
+"""
+
+import torch
+
+KBLOCK = 64       # bytes of one row inside a tile
+GROUP = 8         # rows per tile
+
+
+def plan_rows(rows, unit, cta, grid):
+    """Rows [r0, r1) of a `rows`-row matrix owned by CTA `cta` (mirrors `mk_plan_rows` in the C ABI)."""
+    units = rows // unit
+    return (units * cta // grid) * unit, (units * (cta + 1) // grid) * unit
+
+
+def _groups(n_rows, rows_per_chunk):
+    """(start, size) of every row group of a slice of `n_rows` rows."""
+    out = []
+    for base in range(0, n_rows, rows_per_chunk):
+        nr = min(rows_per_chunk, n_rows - base)
+        for g0 in range(0, nr, GROUP):
+            out.append((base + g0, min(GROUP, nr - g0)))
+    return out
+
+
+def pack_rows(w, unit, grid, slot_bytes):
+    """[N, row_bytes] uint8 (row-major weights as bytes) -> same shape, kernel layout."""
+    assert w.dtype == torch.uint8 and w.dim() == 2
+    n, rb = w.shape
+    assert rb % KBLOCK == 0 and slot_bytes >= rb
+    rpc = slot_bytes // rb
+    out = torch.empty_like(w)
+    nkb = rb // KBLOCK
+    for c in range(grid):
+        r0, r1 = plan_rows(n, unit, c, grid)
+        if rpc % GROUP == 0:
+            # groups are the consecutive 8-row blocks of the slice, the last one possibly short
+            nfull = (r1 - r0) // GROUP
+            if nfull:
+                blk = w[r0: r0 + nfull * GROUP].view(nfull, GROUP, nkb, KBLOCK)
+                out[r0: r0 + nfull * GROUP] = blk.transpose(1, 2).reshape(nfull * GROUP, rb)
+            tail = r0 + nfull * GROUP
+            if tail < r1:
+                out[tail: r1] = w[tail: r1].view(r1 - tail, nkb, KBLOCK).transpose(0, 1).reshape(r1 - tail, rb)
+        else:
+            for g0, ng in _groups(r1 - r0, rpc):
+                a = r0 + g0
+                out[a: a + ng] = w[a: a + ng].view(ng, nkb, KBLOCK).transpose(0, 1).reshape(ng, rb)
+    return out
+
+
+def unpack_rows(p, unit, grid, slot_bytes):
+    """Inverse of `pack_rows` (tests, and reading a row back out of a packed matrix)."""
+    n, rb = p.shape
+    rpc = slot_bytes // rb
+    nkb = rb // KBLOCK
+    out = torch.empty_like(p)
+    for c in range(grid):
+        r0, r1 = plan_rows(n, unit, c, grid)
+        for g0, ng in _groups(r1 - r0, rpc):
+            a = r0 + g0
+            out[a: a + ng] = p[a: a + ng].reshape(nkb, ng, KBLOCK).transpose(0, 1).reshape(ng, rb)
+    return out
+
+
+def as_bytes(w):
+    """Row-major weight matrix (int8 or bf16) viewed as [N, row_bytes] uint8."""
+    w = w.contiguous()
+    return w.view(torch.uint8).view(w.shape[0], -1)

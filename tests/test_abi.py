@@ -47,7 +47,7 @@ def test_field_order_matches_header(lib_built):
 
 
 def test_struct_layouts(lib_built):
-    assert ctypes.sizeof(_lib.ModelDesc) == 32
+    assert ctypes.sizeof(_lib.ModelDesc) == 36
     a = _lib.LaunchArgs
     assert a.stop_ids.offset == 40 and a.prof_step.offset == 96 and a.pf_bytes.offset == 104
     assert a.spec.offset == 120 and a.spec_out.offset == 136 and ctypes.sizeof(a) == 152
@@ -65,7 +65,7 @@ def test_bad_arguments_are_refused_without_a_gpu(lib_built):
     lib = _lib.load()
     assert lib.mk_create(None, None) == _lib.MK_ERR_BADARG
     assert b"null" in lib.mk_last_error()
-    desc = _lib.ModelDesc(shape=77, n_layers=4, vocab=4096, max_seq=64, quant=0, kv_dtype=1, draft_vocab=0, device=0)
+    desc = _lib.ModelDesc(shape=77, n_layers=4, vocab=4096, max_seq=64, quant=0, kv_dtype=1, draft_vocab=0, device=0, grid=0)
     h = ctypes.c_void_p()
     assert lib.mk_create(ctypes.byref(desc), ctypes.byref(h)) == _lib.MK_ERR_UNSUPPORTED
     with pytest.raises(_lib.MkError):
