@@ -201,7 +201,7 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     const int grid = a->grid > 0 ? a->grid : e->desc.grid;
     if (grid != e->desc.grid) return fail(MK_ERR_BADARG, "mk_launch: grid %d, but the weights are packed for %d CTAs", grid, e->desc.grid);
     // per-CTA ownership limits of the kernel's shared-memory staging
-    if ((Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID)
+    if ((Qwen35_08B::GDN_IN + grid - 1) / grid > MAX_BODY_ROWS || (Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID)
         return fail(MK_ERR_BADARG, "mk_launch: grid %d too small or too large for this shape", grid);
     if (grid < Qwen35_08B::GDN_TASKS) return fail(MK_ERR_BADARG, "mk_launch: grid %d < %d DeltaNet tasks", grid, (int)Qwen35_08B::GDN_TASKS);
     if (attn_chunk(a->start_pos + a->n_steps, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)

@@ -19,7 +19,11 @@ constexpr int MAX_CHUNK_POS = 448;        // positions one attention task scans 
 constexpr int MAX_LM_ROWS = 1 << 20;      // LM-head rows one CTA can own (no per-CTA staging limits it)
 constexpr int MAX_BODY_ROWS = 64;         // rows of a layer GEMV one CTA can own
 constexpr int OPS_PER_LAYER = 5;
+#ifdef MK_TRACE
+constexpr int PROF_FIELDS = 12;         // + fine-grained marks of a trace build
+#else
 constexpr int PROF_FIELDS = 6;          // enter, staged, done, published, ring-wait ns, spare
+#endif
 constexpr int PROF_MAX_OPS = MAX_LAYERS * OPS_PER_LAYER + 8;
 constexpr int SPEC_T = 2;
 
@@ -45,7 +49,7 @@ struct Qwen35_08B {
 constexpr int SMEM_RING = NSTAGE * SLOT_BYTES;
 constexpr int SMEM_XQ = 3 * 2 * 3584;                              // GEMV input planes (3 bf16 pieces of K = 3584) / mixer scratch
 constexpr int MAX_BLOCKS = 512;                                    // KV pages per sequence (max_seq <= 32768)
-constexpr int SMEM_MISC = 2 * NCW * 32 * 4 + MAX_BLOCKS * 4 + 1024;
+constexpr int SMEM_MISC = 2 * NCW * 32 * 4 + MAX_BLOCKS * 4 + 2048 + 1024;   // partial sums, block table, row scales, small scratch
 constexpr int SMEM_BYTES = SMEM_RING + SMEM_XQ + SMEM_MISC;
 
 // ---- device-side parameter block (one per engine, in constant memory) --------------------------

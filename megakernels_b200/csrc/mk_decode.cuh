@@ -40,6 +40,7 @@ struct Smem {
     float* red_s;       // [2][2 * NCW] block-reduction scratch, alternating halves
     float* xown;        // fp32 master copy of the residual rows this CTA owns
     u64* best_s;        // [NCW] block-reduction scratch for 64-bit keys
+    float* scale_s;     // per-row scales: two 128-row buffers for layer GEMVs, then the streaming ring
     float* xscale_s;    // [1] power-of-two factor that undoes the fixed-point scaling of the staged input
     uint64_t* full;     // [NSTAGE]
     uint64_t* empty;    // [NSTAGE]
@@ -57,10 +58,13 @@ struct Ctx {
     bool dead;          // this thread saw a wait run out
     u64* prof;          // this CTA's timestamp rows for the step being profiled, or null
     u64 wait_acc;       // time consumer thread 0 spent waiting for ring chunks in the current op
+    int cur_op;         // op index being traced (trace builds)
+    uint32_t gemv_n;    // layer GEMVs run so far (selects the scale buffer)
 };
 
 // Per-op timestamps (enter, inputs staged, work done, outputs published), consumer thread 0 only.
 __device__ __forceinline__ void prof_stamp(Ctx& c, int op, int field) {
+    if (field == 0) c.cur_op = op;
     if (c.prof && c.tid == 0) {
         c.prof[(size_t)op * PROF_FIELDS + field] = globaltimer();
         if (field == 3) {
@@ -111,13 +115,22 @@ __device__ __forceinline__ void mbar_wait(Ctx& c, uint64_t* b, uint32_t parity, 
     }
 }
 
+#ifdef MK_TRACE
+#define MK_MARK(c, idx) do { if ((c).prof && (c).tid == 0) (c).prof[(size_t)(c).cur_op * PROF_FIELDS + (idx)] = globaltimer(); } while (0)
+#else
+#define MK_MARK(c, idx) do { } while (0)
+#endif
+
 // Pause between two polls of a word that is not ready.  Thousands of threads poll the same few
 // cache lines; without a pause their loads queue up in front of the store they are waiting for.
 #ifndef MK_POLL_SLEEP_NS
 #define MK_POLL_SLEEP_NS 0
 #endif
-__device__ __forceinline__ void poll_backoff() {
-    if (MK_POLL_SLEEP_NS > 0) __nanosleep(MK_POLL_SLEEP_NS);
+#ifndef MK_POLL_FREE_SPINS
+#define MK_POLL_FREE_SPINS 2
+#endif
+__device__ __forceinline__ void poll_backoff(uint32_t polls_so_far) {
+    if (MK_POLL_SLEEP_NS > 0 && polls_so_far >= MK_POLL_FREE_SPINS) __nanosleep(MK_POLL_SLEEP_NS);
 }
 
 // Wait until the word shows `epoch`; returns its fp32 payload.
@@ -129,7 +142,7 @@ __device__ __forceinline__ float ll_wait(Ctx& c, const u64* p, uint32_t epoch, i
             c.dead = true;
             break;
         }
-        poll_backoff();
+        poll_backoff(s.it);
         w = ll_load(p);
     }
     return __uint_as_float((uint32_t)w);
@@ -143,7 +156,7 @@ __device__ __forceinline__ void ll_wait2(Ctx& c, const u64* p, uint32_t epoch, i
             c.dead = true;
             break;
         }
-        poll_backoff();
+        poll_backoff(s.it);
         ll_load2(p, w0, w1);
     }
     a = __uint_as_float((uint32_t)w0);
@@ -173,6 +186,7 @@ __device__ __forceinline__ void ll_wait_pairs(Ctx& c, const u64* const (&p)[N], 
             c.dead = true;
             break;
         }
+        poll_backoff(s.it);
     }
 #pragma unroll
     for (int i = 0; i < N; i++) {
@@ -261,12 +275,83 @@ __device__ __forceinline__ float fixed_scale(float mx) {
     return __uint_as_float((uint32_t)(127 + 26 - e) << 23);
 }
 
+// Per-row scales travel through shared memory so that the warp that finishes rows never stalls on a
+// global load: `scale_prefetch` (called when an op is entered, long before its rows finish) fills the
+// first 128 rows; the streaming GEMV refills its 8-chunk ring four chunks ahead.
+constexpr int SCALE_BODY = 128;                 // rows per body-op buffer (two buffers, alternating)
+constexpr int SCALE_RING = 8 * 32;              // streaming ring: 8 chunks of up to 32 rows
+__device__ __forceinline__ void scale_prefetch(Ctx& c, const float* __restrict__ row_scale, int r0, int r1,
+                                               bool stream) {
+    if (!row_scale || c.warp != NCW - 1) return;
+    float* dst = stream ? c.sm.scale_s + 2 * SCALE_BODY : c.sm.scale_s + (c.gemv_n & 1) * SCALE_BODY;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = (r0 + c.lane + 32 * i < r1) ? row_scale[r0 + c.lane + 32 * i] : 1.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) dst[c.lane + 32 * i] = v[i];
+}
+
+// MMAs of one or two 16-row blocks (rows [b0, b0 + 32) of the chunk) over this warp's k-blocks.
+// Lane (g, t) returns, per block, the finished planes 2t and 2t + 1 of rows g and g + 8.
+template <bool Q8>
+__device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xrow, bool xlive, int rb, int nkb, int nr,
+                                           int b0, int warp, int g, int t, float (&v)[4]) {
+    int n8[4];
+    const uint8_t* tile[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {               // the four 8-row tiles of the two blocks
+        n8[q] = max(0, min(8, nr - b0 - 8 * q));
+        tile[q] = buf + (size_t)(b0 + 8 * q) * rb + g * 64 + t * 16;
+    }
+    int ci[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    float cf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 2
+    for (int kb = warp; kb < nkb; kb += NCW) {
+        uint4 w[4], x = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            w[q] = make_uint4(0, 0, 0, 0);
+            if (g < n8[q]) w[q] = *reinterpret_cast<const uint4*>(tile[q] + (size_t)kb * n8[q] * 64);
+        }
+        if (xlive) x = *reinterpret_cast<const uint4*>(xrow + kb * 64);
+#pragma unroll
+        for (int b = 0; b < 2; b++) {           // two independent accumulator chains
+            if (Q8) {
+                mma_s8(ci[b], w[2 * b].x, w[2 * b + 1].x, w[2 * b].y, w[2 * b + 1].y, x.x, x.y);
+                mma_s8(ci[b], w[2 * b].z, w[2 * b + 1].z, w[2 * b].w, w[2 * b + 1].w, x.z, x.w);
+            } else {
+                mma_bf16(cf[b], w[2 * b].x, w[2 * b + 1].x, w[2 * b].y, w[2 * b + 1].y, x.x, x.y);
+                mma_bf16(cf[b], w[2 * b].z, w[2 * b + 1].z, w[2 * b].w, w[2 * b + 1].w, x.z, x.w);
+            }
+        }
+    }
+    const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);       // 128^(2t) for the int8 digits
+    const float pw1 = pw0 * 128.f;
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+        float lo, hi;
+        if (Q8) {
+            lo = (float)ci[b][0] * pw0 + (float)ci[b][1] * pw1;
+            hi = (float)ci[b][2] * pw0 + (float)ci[b][3] * pw1;
+        } else {
+            lo = cf[b][0] + cf[b][1];
+            hi = cf[b][2] + cf[b][3];
+        }
+        v[2 * b] = lo + __shfl_xor_sync(0xffffffffu, lo, 1);
+        v[2 * b + 1] = hi + __shfl_xor_sync(0xffffffffu, hi, 1);
+    }
+}
+
 // Streams this CTA's rows [r0, r1) of a matrix with `rb`-byte rows out of the ring.  Two 8-row tiles
-// form the 16-row A operand of an MMA, the input planes are its B operand (column n = plane n), so
-// lane (g, t) ends up with rows g and g + 8 of the block for planes 2t and 2t + 1.  When a chunk's
-// rows are finished, every lane of warp 0 calls sink(lane, row, value, valid): lane i holds row
-// base + i of the chunk (value already multiplied by the row's scale and the input's scale).
-template <bool Q8, class Sink>
+// form the 16-row A operand of an MMA, the input planes are its B operand (column n = plane n).
+// Every warp owns a k-slice of all rows; per-warp partial sums meet in shared memory.
+//   STREAM = false  (layer GEMVs, at most 64 rows per CTA): one barrier after the last chunk, then
+//                   warps 0 and 1 finish the rows;
+//   STREAM = true   (LM head): one barrier per chunk, warp 0 finishes that chunk's rows while the
+//                   other warps move on.
+// A finishing warp calls sink(lane, row, value, valid) on all of its lanes; `value` already carries
+// the row's scale and the input's fixed-point scale.
+template <bool Q8, bool STREAM, class Sink>
 __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const float* __restrict__ row_scale,
                                          Sink&& sink) {
     const int rpc = SLOT_BYTES / rb;
@@ -274,22 +359,19 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
     const int g = c.lane >> 2, t = c.lane & 3;
     const uint8_t* xrow = c.sm.xq + g * rb + t * 16;
     const bool xlive = g < Planes<Q8>::N;
-    // per-row scales of the next four chunks, fetched ahead so that no chunk waits for DRAM
-    float sc0 = 1.f, sc1 = 1.f, sc2 = 1.f, sc3 = 1.f;
-    const bool scaler = row_scale != nullptr && c.warp == 0;
-    if (scaler) {
-        if (r0 + c.lane < r1) sc0 = row_scale[r0 + c.lane];
-        if (r0 + rpc + c.lane < r1) sc1 = row_scale[r0 + rpc + c.lane];
-        if (r0 + 2 * rpc + c.lane < r1) sc2 = row_scale[r0 + 2 * rpc + c.lane];
-        if (r0 + 3 * rpc + c.lane < r1) sc3 = row_scale[r0 + 3 * rpc + c.lane];
-    }
-    for (int base = r0; base < r1; base += rpc) {
+    const float* scales = STREAM ? c.sm.scale_s + 2 * SCALE_BODY : c.sm.scale_s + (c.gemv_n & 1) * SCALE_BODY;
+    c.gemv_n++;
+    float pend = 1.f;                            // scale fetched for the chunk four ahead (STREAM)
+    int chunk = 0;
+    for (int base = r0; base < r1; base += rpc, chunk++) {
         const int nr = min(rpc, r1 - base);
         const uint32_t n = c.cons_n++;
         const int slot = (int)(n % NSTAGE);
-        const float rs = sc0;
-        sc0 = sc1; sc1 = sc2; sc2 = sc3;
-        if (scaler && base + 4 * rpc + c.lane < r1) sc3 = row_scale[base + 4 * rpc + c.lane];
+        if (STREAM && row_scale && c.warp == NCW - 1) {
+            if (chunk > 0) c.sm.scale_s[2 * SCALE_BODY + ((chunk + 3) & 7) * 32 + c.lane] = pend;
+            const int r = base + 4 * rpc + c.lane;
+            pend = r < r1 ? row_scale[r] : 1.f;
+        }
         if (c.prof && c.tid == 0) {
             const u64 t0 = globaltimer();
             mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
@@ -298,64 +380,48 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
             mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
         }
         const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
-        float* part = c.sm.part_s + ((n & 1) * NCW + c.warp) * 32;
-        for (int b0 = 0; b0 < nr; b0 += 16) {
-            const int n_lo = min(8, nr - b0), n_hi = max(0, min(8, nr - b0 - 8));
-            const uint8_t* t_lo = buf + (size_t)b0 * rb + g * 64 + t * 16;
-            const uint8_t* t_hi = buf + (size_t)(b0 + 8) * rb + g * 64 + t * 16;
-            const bool live_lo = g < n_lo, live_hi = g < n_hi;
-            int ci[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-            float cf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-            int kb = c.warp;
-#pragma unroll 1
-            for (; kb < nkb; kb += 2 * NCW) {
-#pragma unroll
-                for (int u = 0; u < 2; u++) {        // two independent accumulator chains
-                    const int k2 = kb + u * NCW;
-                    if (k2 < nkb) {
-                        uint4 wl = make_uint4(0, 0, 0, 0), wh = wl, x = wl;
-                        if (live_lo) wl = *reinterpret_cast<const uint4*>(t_lo + (size_t)k2 * n_lo * 64);
-                        if (live_hi) wh = *reinterpret_cast<const uint4*>(t_hi + (size_t)k2 * n_hi * 64);
-                        if (xlive) x = *reinterpret_cast<const uint4*>(xrow + k2 * 64);
-                        if (Q8) {
-                            mma_s8(ci[u], wl.x, wh.x, wl.y, wh.y, x.x, x.y);
-                            mma_s8(ci[u], wl.z, wh.z, wl.w, wh.w, x.z, x.w);
-                        } else {
-                            mma_bf16(cf[u], wl.x, wh.x, wl.y, wh.y, x.x, x.y);
-                            mma_bf16(cf[u], wl.z, wh.z, wl.w, wh.w, x.z, x.w);
-                        }
-                    }
-                }
-            }
-            // planes -> value: this lane holds planes 2t, 2t + 1 of rows g (c0, c1) and g + 8 (c2, c3)
-            float v_lo, v_hi;
-            if (Q8) {
-                const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);       // 128^(2t)
-                const float pw1 = pw0 * 128.f;
-                v_lo = (float)(ci[0][0] + ci[1][0]) * pw0 + (float)(ci[0][1] + ci[1][1]) * pw1;
-                v_hi = (float)(ci[0][2] + ci[1][2]) * pw0 + (float)(ci[0][3] + ci[1][3]) * pw1;
-            } else {
-                v_lo = (cf[0][0] + cf[1][0]) + (cf[0][1] + cf[1][1]);
-                v_hi = (cf[0][2] + cf[1][2]) + (cf[0][3] + cf[1][3]);
-            }
-            v_lo += __shfl_xor_sync(0xffffffffu, v_lo, 1);
-            v_hi += __shfl_xor_sync(0xffffffffu, v_hi, 1);
+        // partial sums: [warp][row]; 64 rows per warp for layer GEMVs, two alternating 32-row halves when streaming
+        float* part = STREAM ? c.sm.part_s + ((n & 1) * NCW + c.warp) * 32
+                             : c.sm.part_s + c.warp * 64 + (base - r0);
+        if (base == r0) MK_MARK(c, 8);
+        for (int b0 = 0; b0 < nr; b0 += 32) {
+            float v[4];
+            mma_blocks<Q8>(buf, xrow, xlive, rb, nkb, nr, b0, c.warp, g, t, v);
             if (t == 0) {
-                part[b0 + g] = v_lo;
-                if (b0 + 8 + g < 32) part[b0 + 8 + g] = v_hi;
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+                    if (b0 + 8 * q + g < nr) part[b0 + 8 * q + g] = v[q];
             }
         }
         __syncwarp();
         // A lane whose wait ran out never releases the slot: its copy may still be in flight, and the
         // producer must not aim a second copy at the same shared memory.
         if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
+        if (STREAM) {
+            consumer_sync();
+            if (c.warp == 0) {
+                const float* pp = c.sm.part_s + (n & 1) * NCW * 32 + c.lane;
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < NCW; w++) v += pp[w * 32];
+                const float rs = row_scale ? scales[(chunk & 7) * 32 + c.lane] : 1.f;
+                sink(c.lane, base + c.lane, v * rs * *c.sm.xscale_s, c.lane < nr);
+            }
+        }
+    }
+    if (!STREAM) {
+        MK_MARK(c, 9);
         consumer_sync();
-        if (c.warp == 0) {
-            const float* pp = c.sm.part_s + (n & 1) * NCW * 32 + c.lane;
+        MK_MARK(c, 10);
+        if (c.warp < 2) {
+            const int idx = c.warp * 32 + c.lane;
+            const float* pp = c.sm.part_s + idx;
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < NCW; w++) v += pp[w * 32];
-            sink(c.lane, base + c.lane, v * rs * *c.sm.xscale_s, c.lane < nr);
+            for (int w = 0; w < NCW; w++) v += pp[w * 64];
+            const float rs = row_scale ? scales[idx] : 1.f;
+            sink(c.lane, r0 + idx, v * rs * *c.sm.xscale_s, idx < r1 - r0);
+            MK_MARK(c, 11);
         }
     }
 }
@@ -443,14 +509,15 @@ __device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
 // elements (2*tid, 2*tid+1).  One block reduction yields both the sum of squares and the largest
 // |x (1 + w)|, from which the fixed-point scale follows without a second pass.
 template <class S, bool Q8>
-__device__ __forceinline__ void stage_rmsnorm(Ctx& c, float x0, float x1, const float* __restrict__ w) {
+__device__ __forceinline__ void stage_rmsnorm(Ctx& c, float x0, float x1, float2 g) {
     static_assert(S::HID == 2 * NCT, "two residual elements per consumer thread");
     constexpr int RB = Q8 ? S::HID : 2 * S::HID;
     const int k = 2 * c.tid;
-    const float2 g = *reinterpret_cast<const float2*>(w + k);
     const float y0 = x0 * (1.0f + g.x), y1 = x1 * (1.0f + g.y);
     float ss = x0 * x0 + x1 * x1, mx = fmaxf(fabsf(y0), fabsf(y1));
+    MK_MARK(c, 6);
     consumer_sum_max(c, ss, mx);
+    MK_MARK(c, 7);
     const float inv = rsqrtf(ss * (1.0f / S::HID) + S::EPS);
     const float scale = Q8 ? fixed_scale(mx * inv) : 1.0f;
     stage_pair<Q8>(c.sm.xq, RB, k, y0 * inv, y1 * inv, scale);
@@ -502,6 +569,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     float* qkv_s = reinterpret_cast<float*>(c.sm.xq);   // [q 128 | k 128 | v 16 | b | a]
     float* srow = L.state + ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
     const float4 st = *reinterpret_cast<const float4*>(srow);   // issued before the wait on purpose
+    const float a_log = L.A_log[h], dt_bias = L.dt_bias[h];
     constexpr int NCH = 2 * S::LIN_DK + S::GDN_SLICE;           // 272 conv channels this task needs
     if (c.tid < NCH) {
         int ch;
@@ -537,7 +605,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     const float ks = 1.0f / fmaxf(sqrtf(kn), 1e-6f);
     const float vval = qkv_s[2 * S::LIN_DK + c.warp];
     const float beta = sigmoid_f(qkv_s[NCH]);
-    const float decay = expf(-expf(L.A_log[h]) * softplus_f(qkv_s[NCH + 1] + L.dt_bias[h]));
+    const float decay = expf(-expf(a_log) * softplus_f(qkv_s[NCH + 1] + dt_bias));
     const float kx = k4.x * ks, ky = k4.y * ks, kz = k4.z * ks, kw = k4.w * ks;
     float s0 = st.x * decay, s1 = st.y * decay, s2 = st.z * decay, s3 = st.w * decay;
     const float recalled = warp_sum(fmaf(s3, kw, fmaf(s2, kz, fmaf(s1, ky, s0 * kx))));
@@ -642,6 +710,17 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
                                     hh == 0 ? P.projl + S::ATT_K_OFF + g * S::HD + dd
                                             : (hh == 1 ? P.projl + S::ATT_V_OFF + g * S::HD + dd : nullptr)};
         const uint32_t eps[2] = {e_proj, e_proj};
+        // norm weights and rotation angles are requested before the wait
+        const float2 qw = *reinterpret_cast<const float2*>(L.q_norm + dd);
+        const float2 kw = hh == 0 ? *reinterpret_cast<const float2*>(L.k_norm + dd) : make_float2(0.f, 0.f);
+        float cs0 = 1.f, sn0 = 0.f, cs1 = 1.f, sn1 = 0.f;
+        if (qd == 0) {
+            const int i0 = (2 * c.lane) & 31;
+            cs0 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0];
+            sn0 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0];
+            cs1 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0 + 1];
+            sn1 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0 + 1];
+        }
         float v4[4];
         ll_wait_pairs<2>(c, ptrs, eps, v4, W_PROJ);
         float a = v4[0], b = v4[1];
@@ -657,16 +736,9 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         consumer_sync();
         const float qss = buf[hh * 4] + buf[hh * 4 + 1] + buf[hh * 4 + 2] + buf[hh * 4 + 3];
         const float qinv = rsqrtf(qss * (1.0f / S::HD) + S::EPS);
-        const float2 qw = *reinterpret_cast<const float2*>(L.q_norm + dd);
         a = a * qinv * (1.0f + qw.x);
         b = b * qinv * (1.0f + qw.y);
-        float cs0 = 1.f, sn0 = 0.f, cs1 = 1.f, sn1 = 0.f;
         if (qd == 0) {
-            const int i0 = (2 * c.lane) & 31;
-            cs0 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0];
-            sn0 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0];
-            cs1 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0 + 1];
-            sn1 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0 + 1];
             // dims [0,32) live in lanes 0..15, their partners [32,64) in lanes 16..31
             const float pa = __shfl_xor_sync(0xffffffffu, a, 16), pb = __shfl_xor_sync(0xffffffffu, b, 16);
             if (c.lane < 16) { a = a * cs0 - pa * sn0; b = b * cs1 - pb * sn1; }
@@ -677,7 +749,6 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         if (hh == 0) {
             const float kss = buf[NCW] + buf[NCW + 1] + buf[NCW + 2] + buf[NCW + 3];
             const float kinv = rsqrtf(kss * (1.0f / S::HD) + S::EPS);
-            const float2 kw = *reinterpret_cast<const float2*>(L.k_norm + dd);
             ka = ka * kinv * (1.0f + kw.x);
             kb = kb * kinv * (1.0f + kw.y);
             if (qd == 0) {
@@ -905,6 +976,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         c.sm.xq = p; p += SMEM_XQ;
         c.sm.part_s = reinterpret_cast<float*>(p); p += 2 * NCW * 32 * 4;          // 4096
         c.sm.bt_s = reinterpret_cast<int*>(p); p += MAX_BLOCKS * 4;                // 2048
+        c.sm.scale_s = reinterpret_cast<float*>(p); p += (2 * SCALE_BODY + SCALE_RING) * 4;   // 2048
         c.sm.out_s = reinterpret_cast<float*>(p); p += 64;
         c.sm.red_s = reinterpret_cast<float*>(p); p += 2 * 2 * NCW * 4;            // 256
         c.sm.xown = reinterpret_cast<float*>(p); p += 16 * 4;                      // 64
@@ -917,7 +989,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
-    c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr; c.wait_acc = 0;
+    c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr; c.wait_acc = 0; c.cur_op = 0; c.gemv_n = 0;
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
     if (c.tid == 0) {
@@ -1006,10 +1078,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 prof_stamp(c, op0, 0);
                 int r0, r1;
                 cta_rows(attn ? S::ATT_IN : S::GDN_IN, 1, c.cta, c.grid, r0, r1);
+                scale_prefetch(c, L.s_in, r0, r1, false);
+                // the norm weights are requested before the wait so that their latency hides behind it
+                const float2 nw = *reinterpret_cast<const float2*>(L.in_norm + 2 * c.tid);
                 if (l > 0) ll_wait2(c, P.xl + 2 * c.tid, eA - 1, W_X, x0, x1);
-                stage_rmsnorm<S, Q8>(c, x0, x1, L.in_norm);
+                stage_rmsnorm<S, Q8>(c, x0, x1, nw);
                 prof_stamp(c, op0, 1);
-                gemv_mma<Q8>(c, r0, r1, S::HID * WB, L.s_in, [&](int, int row, float v, bool ok) {
+                gemv_mma<Q8, false>(c, r0, r1, S::HID * WB, L.s_in, [&](int, int row, float v, bool ok) {
                     if (ok) ll_store(P.projl + row, eA, v);
                 });
                 prof_stamp(c, op0, 3);
@@ -1023,9 +1098,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             {
                 const int op = op0 + 2;
                 prof_stamp(c, op, 0);
+                scale_prefetch(c, L.s_out, xr0, xr1, false);
                 // each thread stages 4 consecutive mixer outputs; a warp covers 128 = one DeltaNet head
                 const int k = 4 * c.tid;
                 float m[4];
+                const float4 gw = attn ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                       : *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
                 {
                     const u64* aux = attn ? P.projl + (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD)   // sigmoid gate
                                           : P.projl + S::Z_OFF + k;                                    // z
@@ -1039,7 +1117,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                     } else {
                         const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
                         const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
-                        const float4 gw = *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
                         m[0] = v[0] * inv * gw.x * silu_f(v[4]);
                         m[1] = v[1] * inv * gw.y * silu_f(v[5]);
                         m[2] = v[2] * inv * gw.z * silu_f(v[6]);
@@ -1051,7 +1128,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 stage_pair<Q8>(c.sm.xq, S::MIX * WB, k + 2, m[2], m[3], scale);
                 finish_stage(c, scale);
                 prof_stamp(c, op, 1);
-                gemv_mma<Q8>(c, xr0, xr1, S::MIX * WB, L.s_out, [&](int, int row, float v, bool ok) {
+                gemv_mma<Q8, false>(c, xr0, xr1, S::MIX * WB, L.s_out, [&](int, int row, float v, bool ok) {
                     if (ok) {
                         const float xn = c.sm.xown[row - xr0] + v;
                         c.sm.xown[row - xr0] = xn;
@@ -1066,10 +1143,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 prof_stamp(c, op, 0);
                 int r0, r1;
                 cta_rows(2 * S::INTER, 2, c.cta, c.grid, r0, r1);
+                scale_prefetch(c, L.s_gu, r0, r1, false);
+                const float2 nw = *reinterpret_cast<const float2*>(L.post_norm + 2 * c.tid);
                 ll_wait2(c, P.xl + 2 * c.tid, eC, W_X, x0, x1);
-                stage_rmsnorm<S, Q8>(c, x0, x1, L.post_norm);
+                stage_rmsnorm<S, Q8>(c, x0, x1, nw);
                 prof_stamp(c, op, 1);
-                gemv_mma<Q8>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, float v, bool ok) {
+                gemv_mma<Q8, false>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, float v, bool ok) {
                     // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane
                     const float up = __shfl_down_sync(0xffffffffu, v, 1);
                     if (ok && !(lane & 1)) ll_store(P.actl + (row >> 1), eD, silu_f(v) * up);
@@ -1080,6 +1159,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             {
                 const int op = op0 + 4;
                 prof_stamp(c, op, 0);
+                scale_prefetch(c, L.s_down, xr0, xr1, false);
                 float a[8];
                 float mx = 0.f;
                 {
@@ -1103,7 +1183,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
                 finish_stage(c, scale);
                 prof_stamp(c, op, 1);
                 const bool last = l == P.n_layers - 1;
-                gemv_mma<Q8>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, float v, bool ok) {
+                gemv_mma<Q8, false>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, float v, bool ok) {
                     if (ok) {
                         const float xn = c.sm.xown[row - xr0] + v;
                         c.sm.xown[row - xr0] = xn;
@@ -1122,13 +1202,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             const uint32_t eL = e0 + (uint32_t)OPS - 1;
             const int op = P.n_layers * OPS_PER_LAYER;
             prof_stamp(c, op, 0);
+            scale_prefetch(c, P.lm_scale, lr0, lr1, true);
+            const float2 nw = *reinterpret_cast<const float2*>(P.final_norm + 2 * c.tid);
             ll_wait2(c, P.xl + 2 * c.tid, eL - 1, W_X, x0, x1);
-            stage_rmsnorm<S, Q8>(c, x0, x1, P.final_norm);
+            stage_rmsnorm<S, Q8>(c, x0, x1, nw);
             prof_stamp(c, op, 1);
             u64 best = 0;
             float* logits = A.logits_out ? A.logits_out + (size_t)s * P.vocab : nullptr;
             const float invT = A.inv_temperature;
-            gemv_mma<Q8>(c, lr0, lr1, S::HID * WB, P.lm_scale, [&](int, int row, float v, bool ok) {
+            gemv_mma<Q8, true>(c, lr0, lr1, S::HID * WB, P.lm_scale, [&](int, int row, float v, bool ok) {
                 if (!ok) return;
                 if (logits) logits[row] = v;
                 float score = v;
