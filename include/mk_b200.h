@@ -145,6 +145,27 @@ int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_layer_values, c
  * Asynchronous on `stream` (a cudaStream_t, 0 for the default stream). */
 int mk_launch(mk_engine* e, const mk_launch_args* args, void* stream);
 
+/* Same launch as mk_launch, for a host that cannot give the kernel freshly allocated scratch.
+ *
+ * No counterpart in the reference.  Some callers must not allocate device memory: a serving
+ * process whose memory pool has already claimed the whole device, a plug-in that is called at a
+ * point where the host forbids allocation, a real-time loop that may not take the allocator's
+ * lock.  For them the activation hand-off words of the kernel (the buffers a normal engine passes
+ * as MK_G_XL, MK_G_PROJL, MK_G_MIXL, MK_G_ACTL, MK_G_LML and MK_G_ATTN_PART) live in one array that
+ * is compiled into the library, MK_STATIC_SCRATCH_BYTES (3 MiB) per GPU that loads it, held until the
+ * process exits.  The caller still passes every input and output (weights, state, KV cache, status
+ * words, the launch arguments); this function calls no cudaMalloc / cudaFree and no allocating
+ * library routine.
+ *
+ *  - The first call on a device looks up the array's device address and caches it; make that first
+ *    call outside any stream capture.
+ *  - A grid or shape whose hand-off words do not fit the array is refused with MK_ERR_BADARG.
+ *  - Every call clears the array on `stream` before the kernel runs, because all calls (of all
+ *    engines) share it and it keeps what the last call wrote.  Two calls that overlap on the GPU
+ *    (different streams, or different engines at once) therefore race: serialise them. */
+#define MK_STATIC_SCRATCH_BYTES (3u << 20)
+int mk_launch_static(mk_engine* e, const mk_launch_args* args, void* stream);
+
 /* Replaces `watchdog_fired` (qwen3.5-0.8b/csrc/megakernel.cu:1284-1289): synchronises the device,
  * reads the status words of the last launch and returns MK_OK or MK_ERR_TIMEOUT.  Unlike the
  * reference, waits are bounded in every build, not only with -DMK_WATCHDOG. */

@@ -27,7 +27,7 @@ GLOBAL_FIELDS = ["embed", "embed_scale", "lm_head", "lm_scale", "final_norm", "r
 QUERIES = ["SMEM_BYTES", "N_THREADS", "CONV_RING", "KV_BLOCK", "MAX_SPLITS", "PART_STRIDE", "OPS_PER_LAYER",
            "PROF_MAX_OPS", "PROF_FIELDS", "SPEC_T", "MAX_LAYERS", "LAYER_FIELDS", "GLOBAL_FIELDS", "SLOT_BYTES",
            "STAGES", "MAX_LM_ROWS"]
-EXPORTS = ["mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_status", "mk_query", "mk_bw_probe",
+EXPORTS = ["mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_status", "mk_query", "mk_bw_probe",
            "mk_plan_rows", "mk_plan_attn_chunk", "mk_last_error"]
 
 
@@ -72,6 +72,7 @@ def load():
     lib.mk_set_params.argtypes = [ctypes.c_void_p, P(ctypes.c_int64), ctypes.c_int64, P(ctypes.c_int64),
                                   ctypes.c_int64, P(ctypes.c_int64), ctypes.c_int64]
     lib.mk_launch.argtypes = [ctypes.c_void_p, P(LaunchArgs), ctypes.c_void_p]
+    lib.mk_launch_static.argtypes = [ctypes.c_void_p, P(LaunchArgs), ctypes.c_void_p]
     lib.mk_status.argtypes = [ctypes.c_void_p, P(ctypes.c_int32)]
     lib.mk_query.argtypes = [ctypes.c_int]
     lib.mk_query.restype = ctypes.c_int64
@@ -81,7 +82,7 @@ def load():
     lib.mk_plan_attn_chunk.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.mk_plan_attn_chunk.restype = ctypes.c_int
     lib.mk_last_error.restype = ctypes.c_char_p
-    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_status", "mk_bw_probe", "mk_plan_rows"):
+    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_status", "mk_bw_probe", "mk_plan_rows"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib

@@ -17,6 +17,7 @@ struct mk_engine {
     int n_sm;
     bool params_set;
     Params host;
+    bool static_ready;   // mk_launch_static has written its parameter block for the current params
 };
 
 static thread_local char g_err[512] = "";
@@ -108,6 +109,7 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
     e->slot = slot;
     e->n_sm = n_sm;
     e->params_set = false;
+    e->static_ready = false;
     memset(&e->host, 0, sizeof e->host);
     *out = e;
     return MK_OK;
@@ -177,6 +179,7 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     MK_CUDA(cudaSetDevice(e->desc.device));
     MK_CUDA(cudaMemcpyToSymbol(c_params, &p, sizeof(Params), (size_t)e->slot * sizeof(Params), cudaMemcpyHostToDevice));
     e->params_set = true;
+    e->static_ready = false;
     return MK_OK;
 }
 
@@ -245,6 +248,109 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     void* kargs[] = {&slot, &A};
     MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, SMEM_BYTES,
                                         static_cast<cudaStream_t>(stream)));
+    return MK_OK;
+}
+
+// ---- launch without caller-provided scratch ---------------------------------------------------------
+// The hand-off words of the kernel in an array that is part of the library image.  In host code the
+// array's name is only a stand-in for the symbol: its device address comes from cudaGetSymbolAddress,
+// once per device, and is what the kernel's parameter block receives.
+static __device__ __align__(256) unsigned char g_static_scratch[MK_STATIC_SCRATCH_BYTES];
+static constexpr int MAX_DEVICES = 64;
+static unsigned char* g_static_addr[MAX_DEVICES] = {};
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* stream) {
+    if (!e || !a) return fail(MK_ERR_BADARG, "mk_launch_static: null argument");
+    if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch_static: mk_set_params has not succeeded on this engine");
+    if (a->spec) return fail(MK_ERR_UNSUPPORTED, "mk_launch_static: speculative cycles are not built into this library yet");
+    if (a->n_forced < 1 || a->n_steps < a->n_forced || !a->forced) return fail(MK_ERR_BADARG, "mk_launch_static: need 1 <= n_forced <= n_steps and a token list");
+    if (a->start_pos < 0 || (int64_t)a->start_pos + a->n_steps > e->desc.max_seq)
+        return fail(MK_ERR_BADARG, "mk_launch_static: sequence would exceed max_seq=%d", e->desc.max_seq);
+    if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch_static: lm_from out of range");
+    if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch_static: tokens_out / out_info missing");
+    if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch_static: stop ids missing");
+    const int grid = a->grid > 0 ? a->grid : e->desc.grid;
+    if (grid != e->desc.grid) return fail(MK_ERR_BADARG, "mk_launch_static: grid %d, but the weights are packed for %d CTAs", grid, e->desc.grid);
+    if ((Qwen35_08B::GDN_IN + grid - 1) / grid > MAX_BODY_ROWS || (Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID ||
+        grid < Qwen35_08B::GDN_TASKS)
+        return fail(MK_ERR_BADARG, "mk_launch_static: grid %d too small or too large for this shape", grid);
+    if (attn_chunk(a->start_pos + a->n_steps, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
+        return fail(MK_ERR_BADARG, "mk_launch_static: context of %d positions is too long for %d CTAs", a->start_pos + a->n_steps, grid);
+    const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1;
+    if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
+        return fail(MK_ERR_BADARG, "mk_launch_static: epoch counter exhausted or zero; reset the engine");
+    const int dev = e->desc.device;
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(MK_ERR_BADARG, "mk_launch_static: device ordinal %d", dev);
+
+    // layout of the hand-off words inside the array
+    typedef Qwen35_08B S;
+    size_t off = 0;
+    const size_t o_xl = off;    off = align256(off + sizeof(unsigned long long) * S::HID);
+    const size_t o_proj = off;  off = align256(off + sizeof(unsigned long long) * S::PROJ_MAX);
+    const size_t o_mix = off;   off = align256(off + sizeof(unsigned long long) * S::MIX);
+    const size_t o_act = off;   off = align256(off + sizeof(unsigned long long) * S::INTER);
+    const size_t o_lml = off;   off = align256(off + sizeof(unsigned long long) * 2 * (size_t)grid);
+    const size_t o_part = off;  off = align256(off + sizeof(unsigned long long) * (size_t)S::NKV * MAX_SPLITS * S::PART_STRIDE);
+    if (off > MK_STATIC_SCRATCH_BYTES)
+        return fail(MK_ERR_BADARG, "mk_launch_static: this shape and a grid of %d CTAs need %zu bytes of hand-off words, the built-in array holds %u",
+                    grid, off, (unsigned)MK_STATIC_SCRATCH_BYTES);
+
+    MK_CUDA(cudaSetDevice(dev));
+    if (!g_static_addr[dev]) {
+        // set-up, once per device, with that device current
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_static_addr[dev]) {
+            void* p = nullptr;
+            MK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+            if (!p) return fail(MK_ERR_CUDA, "mk_launch_static: the built-in array has no device address");
+            g_static_addr[dev] = static_cast<unsigned char*>(p);
+        }
+    }
+    unsigned char* base = g_static_addr[dev];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int pslot = MAX_ENGINES + e->slot;
+    if (!e->static_ready) {
+        Params p = e->host;
+        p.xl = reinterpret_cast<unsigned long long*>(base + o_xl);
+        p.projl = reinterpret_cast<unsigned long long*>(base + o_proj);
+        p.mixl = reinterpret_cast<unsigned long long*>(base + o_mix);
+        p.actl = reinterpret_cast<unsigned long long*>(base + o_act);
+        p.lml = reinterpret_cast<unsigned long long*>(base + o_lml);
+        p.attn_part = reinterpret_cast<unsigned long long*>(base + o_part);
+        MK_CUDA(cudaMemcpyToSymbol(c_params, &p, sizeof(Params), (size_t)pslot * sizeof(Params), cudaMemcpyHostToDevice));
+        e->static_ready = true;
+    }
+    // the array keeps the previous call's words (and their epochs): everything must start at zero
+    MK_CUDA(cudaMemsetAsync(base, 0, off, st));
+
+    Args A;
+    memset(&A, 0, sizeof A);
+    A.forced = as_ptr<const int*>(a->forced);
+    A.stop_ids = as_ptr<const int*>(a->stop_ids);
+    A.tokens_out = as_ptr<unsigned long long*>(a->tokens_out);
+    A.logits_out = as_ptr<float*>(a->logits_out);
+    A.resid_out = as_ptr<float*>(a->resid_out);
+    A.step_ts = as_ptr<unsigned long long*>(a->step_ts);
+    A.out_info = as_ptr<int*>(a->out_info);
+    A.prof = as_ptr<unsigned long long*>(a->prof);
+    A.pf_bytes = a->pf_bytes;
+    A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
+    A.n_forced = a->n_forced;
+    A.n_steps = a->n_steps;
+    A.lm_from = a->lm_from;
+    A.start_pos = a->start_pos;
+    A.epoch_base = a->epoch_base;
+    A.seed = a->seed;
+    A.inv_temperature = a->inv_temperature;
+    A.n_stop = a->n_stop;
+    A.prof_step = a->prof_step;
+    kernel_fn fn = pick_kernel(e->desc);
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    int slot = pslot;
+    void* kargs[] = {&slot, &A};
+    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, SMEM_BYTES, st));
     return MK_OK;
 }
 

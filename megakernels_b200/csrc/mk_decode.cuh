@@ -963,7 +963,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------
-__constant__ Params c_params[MAX_ENGINES];   // one parameter block per live engine handle
+__constant__ Params c_params[2 * MAX_ENGINES];   // per engine handle: its block, and the variant with built-in scratch
 
 template <class S, bool Q8, bool KVF32>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, const __grid_constant__ Args A) {
