@@ -32,8 +32,9 @@ METRIC = "decode tok/s at batch 1 (0.8B hybrid, int8 per-channel, 512-token prom
 PROMPT, GENERATE = 512, 512
 L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, per generated token, from the
-# ncu capture summarised in profiles/ (a 16-step launch, scaled by steps); None until captured.
-NCU_DRAM_BYTES_PER_TOKEN = None
+# ncu capture summarised in profiles/decode_kernel_int8_64prompt_16steps.md (a 16-step launch at a 64-token
+# context, scaled by steps; the KV part grows with context, the weight part does not).
+NCU_DRAM_BYTES_PER_TOKEN = (10.533937e9 + 337.758208e6) / 16
 
 
 def measured_peak_gbs():
