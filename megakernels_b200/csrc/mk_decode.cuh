@@ -195,6 +195,28 @@ __device__ __forceinline__ void ll_wait_pairs(Ctx& c, const u64* const (&p)[N], 
     }
 }
 
+// A CTA that had no part in the op it now waits for arrives early.  If all of its threads polled
+// right away, their loads would queue in front of the very stores they wait for.  Instead one warp
+// watches 32 words spread over the buffer, at a relaxed pace, and releases the CTA when all of them
+// show the epoch; the full poll that follows then finds (nearly) everything ready.
+__device__ __forceinline__ void gate_on_samples(Ctx& c, const u64* buf, int nwords, uint32_t epoch) {
+    if (c.warp == 0) {
+        const u64* p = buf + (size_t)c.lane * (nwords / 32) + (nwords / 64);
+        Spin s;
+        while (true) {
+            const bool ready = (uint32_t)(ll_load(p) >> 32) == epoch;
+            if (__all_sync(0xffffffffu, ready)) break;
+            const bool fail = MK_SPIN_FAIL(c, s, W_MIX);
+            if (__any_sync(0xffffffffu, fail)) {      // leave together: the vote above needs every lane
+                c.dead = true;
+                break;
+            }
+            __nanosleep(150);
+        }
+    }
+    consumer_sync();
+}
+
 // Sum and max over all consumer threads in one barrier, fixed order.
 __device__ __forceinline__ void consumer_sum_max(Ctx& c, float& sum, float& mx) {
     float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);
@@ -560,10 +582,10 @@ __device__ __forceinline__ void load_embedding(const Params& P, int token, int t
 // Task t < GDN_TASKS: head t / 8, value columns [16 * (t % 8), +16).  Warp w owns value column w of the
 // slice; a lane holds 4 consecutive key indices of that column's state row.
 template <class S>
-__device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
+__device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::GDN_SLICE == NCW && S::LIN_DK == 128, "one warp per value column, 4 keys per lane");
     constexpr int SL = S::LIN_DV / S::GDN_SLICE;  // slices per head
-    if (c.cta >= S::GDN_TASKS) return;
+    if (c.cta >= S::GDN_TASKS) return false;
     const int h = c.cta / SL, j = c.cta % SL;
     const int vcol = j * S::GDN_SLICE + c.warp;
     float* qkv_s = reinterpret_cast<float*>(c.sm.xq);   // [q 128 | k 128 | v 16 | b | a]
@@ -619,6 +641,7 @@ __device__ void gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     prof_stamp(c, op, 2);
     if (c.lane == 0) ll_store(P.mixl + h * S::LIN_DV + vcol, e_out, o);
     consumer_sync();  // the scratch aliases the GEMV input vector that the next prologue writes
+    return true;
 }
 
 // ---- attention ---------------------------------------------------------------------------------------
@@ -661,7 +684,7 @@ __device__ __forceinline__ void store1(void* base, size_t elem, float v) {
 // otherwise every task publishes (acc, m, l) partials as flag-in-data words and then merges a
 // 1/nsplit share of the head group's outputs from all partials, in a fixed order.
 template <class S, bool KVF32>
-__device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
+__device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
     constexpr int NOUT = S::QPK * S::HD;        // outputs per KV head
     constexpr int PFK = 1, PFV = 16;            // rows prefetched per warp (K) and per thread (V)
@@ -669,7 +692,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     const int max_splits = min(c.grid / S::NKV, MAX_SPLITS);
     const int ch = attn_chunk(n, max_splits);
     const int nsplit = (n + ch - 1) / ch;
-    if (c.cta >= nsplit * S::NKV) return;
+    if (c.cta >= nsplit * S::NKV) return false;
     const int g = c.cta % S::NKV, sp = c.cta / S::NKV;
     const int p0 = sp * ch, p1 = min(n, p0 + ch);
     const int np = p1 - p0;
@@ -884,7 +907,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         // through words this CTA publishes after this fence, so the fence can sit off the critical path.
         __threadfence();
         consumer_sync();  // scratch aliases the GEMV input planes that the next prologue writes
-        return;
+        return true;
     }
     // -- 6. partials as flag-in-data words: acc [4][256], then (m, l) per head
     u64* part = P.attn_part + ((size_t)g * MAX_SPLITS + sp) * S::PART_STRIDE;
@@ -960,6 +983,7 @@ __device__ void attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     if (live && sub == 0) ll_store(out + o, e_out, Os / Ls);
     __threadfence();      // K/V append before anything this CTA publishes later (see above)
     consumer_sync();      // scratch aliases the GEMV input planes that the next prologue writes
+    return true;
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------
@@ -1091,14 +1115,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
             }
             // ---- B: mixer
             prof_stamp(c, op0 + 1, 0);
-            if (attn) attn_op<S, KVF32>(c, P, L, pos, eA, eB, op0 + 1);
-            else gdn_op<S>(c, P, L, pos, eA, eB, op0 + 1);
+            const bool had_task = attn ? attn_op<S, KVF32>(c, P, L, pos, eA, eB, op0 + 1)
+                                       : gdn_op<S>(c, P, L, pos, eA, eB, op0 + 1);
             prof_stamp(c, op0 + 1, 3);
             // ---- C: out-projection + residual
             {
                 const int op = op0 + 2;
                 prof_stamp(c, op, 0);
                 scale_prefetch(c, L.s_out, xr0, xr1, false);
+                if (!had_task) gate_on_samples(c, P.mixl, S::MIX, eB);
                 // each thread stages 4 consecutive mixer outputs; a warp covers 128 = one DeltaNet head
                 const int k = 4 * c.tid;
                 float m[4];
