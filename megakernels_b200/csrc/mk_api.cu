@@ -139,7 +139,11 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
         fill_layer(p.layer[l], layers + (size_t)l * MK_LAYER_FIELDS);
         if (const char* why = check_layer(p.layer[l], q8)) return fail(MK_ERR_BADARG, "layer %d: %s", l, why);
     }
-    if (mtp) fill_layer(p.mtp, mtp);
+    if (mtp) {
+        fill_layer(p.mtp, mtp);
+        if (p.mtp.kind != 1) return fail(MK_ERR_BADARG, "MTP layer must be a gated-attention layer");
+        if (const char* why = check_layer(p.mtp, q8)) return fail(MK_ERR_BADARG, "MTP layer: %s", why);
+    }
     p.embed = as_ptr<const uint8_t*>(g[MK_G_EMBED]);
     p.embed_scale = as_ptr<const float*>(g[MK_G_EMBED_SCALE]);
     p.lm_head = as_ptr<const uint8_t*>(g[MK_G_LM_HEAD]);
@@ -184,22 +188,39 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
 }
 
 typedef void (*kernel_fn)(const int, const Args);
+static_assert(Geo<1>::SMEM == SMEM_BYTES && Geo<2>::SMEM == SMEM_BYTES, "one shared-memory size for both kernels");
 
-static kernel_fn pick_kernel(const mk_model_desc& d) {
+static kernel_fn pick_kernel(const mk_model_desc& d, bool spec = false) {
     const bool q8 = d.quant == MK_QUANT_INT8, f32 = d.kv_dtype == MK_KV_F32;
-    if (q8) return f32 ? decode_kernel<Qwen35_08B, true, true> : decode_kernel<Qwen35_08B, true, false>;
-    return f32 ? decode_kernel<Qwen35_08B, false, true> : decode_kernel<Qwen35_08B, false, false>;
+    if (spec) {
+        if (q8) return f32 ? decode_kernel<Qwen35_08B, true, true, 2> : decode_kernel<Qwen35_08B, true, false, 2>;
+        return f32 ? decode_kernel<Qwen35_08B, false, true, 2> : decode_kernel<Qwen35_08B, false, false, 2>;
+    }
+    if (q8) return f32 ? decode_kernel<Qwen35_08B, true, true, 1> : decode_kernel<Qwen35_08B, true, false, 1>;
+    return f32 ? decode_kernel<Qwen35_08B, false, true, 1> : decode_kernel<Qwen35_08B, false, false, 1>;
 }
 
 extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     if (!e || !a) return fail(MK_ERR_BADARG, "mk_launch: null argument");
     if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch: mk_set_params has not succeeded on this engine");
-    if (a->spec) return fail(MK_ERR_UNSUPPORTED, "mk_launch: speculative cycles are not built into this library yet");
-    if (a->n_forced < 1 || a->n_steps < a->n_forced || !a->forced) return fail(MK_ERR_BADARG, "mk_launch: need 1 <= n_forced <= n_steps and a token list");
-    if (a->start_pos < 0 || (int64_t)a->start_pos + a->n_steps > e->desc.max_seq)
-        return fail(MK_ERR_BADARG, "mk_launch: sequence would exceed max_seq=%d", e->desc.max_seq);
-    if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch: lm_from out of range");
-    if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch: tokens_out / out_info missing");
+    const bool spec = a->spec != 0;
+    if (spec) {
+        // n_steps counts cycles; a cycle feeds two positions and may emit two tokens
+        const Params& p = e->host;
+        if (e->desc.draft_vocab < 1 || !p.mtp_fc || !p.draft_head || !p.xml || !p.mtp.w_in || !p.mtp_norm_e || !p.mtp_norm_h || !p.mtp_norm)
+            return fail(MK_ERR_BADARG, "mk_launch: speculative cycles need the draft head's parameters (mk_set_params with an MTP record)");
+        if (a->n_steps < 1 || a->limit < 1 || !a->spec_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch: need n_steps >= 1 cycles, limit >= 1 and spec_out / out_info");
+        if (a->first_tok < 0 || a->first_tok >= e->desc.vocab || a->first_draft < 0 || a->first_draft >= e->desc.vocab)
+            return fail(MK_ERR_BADARG, "mk_launch: pending token or draft outside the vocabulary");
+        if (a->start_pos < 0 || (int64_t)a->start_pos + 2 * (int64_t)a->n_steps + 1 > e->desc.max_seq)
+            return fail(MK_ERR_BADARG, "mk_launch: sequence would exceed max_seq=%d", e->desc.max_seq);
+    } else {
+        if (a->n_forced < 1 || a->n_steps < a->n_forced || !a->forced) return fail(MK_ERR_BADARG, "mk_launch: need 1 <= n_forced <= n_steps and a token list");
+        if (a->start_pos < 0 || (int64_t)a->start_pos + a->n_steps > e->desc.max_seq)
+            return fail(MK_ERR_BADARG, "mk_launch: sequence would exceed max_seq=%d", e->desc.max_seq);
+        if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch: lm_from out of range");
+        if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch: tokens_out / out_info missing");
+    }
     if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch: stop ids missing");
     const int grid = a->grid > 0 ? a->grid : e->desc.grid;
     if (grid != e->desc.grid) return fail(MK_ERR_BADARG, "mk_launch: grid %d, but the weights are packed for %d CTAs", grid, e->desc.grid);
@@ -207,9 +228,10 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     if ((Qwen35_08B::GDN_IN + grid - 1) / grid > MAX_BODY_ROWS || (Qwen35_08B::HID + grid - 1) / grid > 16 || grid > Qwen35_08B::HID)
         return fail(MK_ERR_BADARG, "mk_launch: grid %d too small or too large for this shape", grid);
     if (grid < Qwen35_08B::GDN_TASKS) return fail(MK_ERR_BADARG, "mk_launch: grid %d < %d DeltaNet tasks", grid, (int)Qwen35_08B::GDN_TASKS);
-    if (attn_chunk(a->start_pos + a->n_steps, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
-        return fail(MK_ERR_BADARG, "mk_launch: context of %d positions is too long for %d CTAs", a->start_pos + a->n_steps, grid);
-    const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1;
+    const int last_pos = a->start_pos + (spec ? 2 * a->n_steps + 1 : a->n_steps);
+    if (attn_chunk(last_pos, grid / Qwen35_08B::NKV < MAX_SPLITS ? grid / Qwen35_08B::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
+        return fail(MK_ERR_BADARG, "mk_launch: context of %d positions is too long for %d CTAs", last_pos, grid);
+    const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1 + (spec ? 2 + OPS_PER_LAYER : 0);
     if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
         return fail(MK_ERR_BADARG, "mk_launch: epoch counter exhausted or zero; reset the engine");
 
@@ -242,7 +264,7 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     A.limit = a->limit;
 
     MK_CUDA(cudaSetDevice(e->desc.device));
-    kernel_fn fn = pick_kernel(e->desc);
+    kernel_fn fn = pick_kernel(e->desc, spec);
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     int slot = e->slot;
     void* kargs[] = {&slot, &A};
@@ -412,7 +434,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) bw_ring_kernel(const uint8_t* __r
                                                               unsigned* sink) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* ring = smem_raw;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + SMEM_RING);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (NSTAGE * SLOT_BYTES));
     uint64_t* empty = full + NSTAGE;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
@@ -479,7 +501,7 @@ extern "C" int mk_bw_probe(uint64_t src, int64_t bytes, int mode, uint64_t sink,
     if (mode == 0) {
         bw_plain_kernel<<<n_sm * 4, 512, 0, st>>>(as_ptr<const uint4*>(src), bytes / 16, as_ptr<unsigned*>(sink));
     } else if (mode == 1) {
-        const int smem = SMEM_RING + 2 * NSTAGE * 8;
+        const int smem = (NSTAGE * SLOT_BYTES) + 2 * NSTAGE * 8;
         MK_CUDA(cudaFuncSetAttribute(bw_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         bw_ring_kernel<<<n_sm, NTHREADS, smem, st>>>(as_ptr<const uint8_t*>(src), bytes, as_ptr<unsigned*>(sink));
     } else {

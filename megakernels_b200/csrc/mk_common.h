@@ -46,11 +46,8 @@ struct Qwen35_08B {
     static constexpr float EPS = 1e-6f;
 };
 
-constexpr int SMEM_RING = NSTAGE * SLOT_BYTES;
-constexpr int SMEM_XQ = 3 * 2 * 3584;                              // GEMV input planes (3 bf16 pieces of K = 3584) / mixer scratch
 constexpr int MAX_BLOCKS = 512;                                    // KV pages per sequence (max_seq <= 32768)
-constexpr int SMEM_MISC = 2 * NCW * 32 * 4 + MAX_BLOCKS * 4 + 2048 + 1024;   // partial sums, block table, row scales, small scratch
-constexpr int SMEM_BYTES = SMEM_RING + SMEM_XQ + SMEM_MISC;
+constexpr int SMEM_BYTES = NSTAGE * SLOT_BYTES + 3 * 2 * 3584 + NCW * 64 * 4 + MAX_BLOCKS * 4 + 2048 + 2048;   // == Geo<1>::SMEM == Geo<2>::SMEM
 
 // ---- device-side parameter block (one per engine, in constant memory) --------------------------
 struct LayerP {

@@ -34,16 +34,16 @@ enum { W_FULL = 1, W_EMPTY, W_X, W_PROJ, W_MIX, W_ACT, W_LM, W_PART, W_DRAIN };
 struct Smem {
     uint8_t* ring;
     uint8_t* xq;        // GEMV input as byte planes (int8 digits or bf16 pieces), or mixer scratch
-    float* part_s;      // [2][NCW][32] per-warp partial row sums of a ring chunk, alternating halves
+    float* part_s;      // per-warp partial row sums: [NCW][T][64], or two alternating [NCW][T][32] halves when streaming
     int* bt_s;          // block table copy [max_seq / KV_BLOCK]
     float* out_s;       // small per-op scratch (attention statistics)
-    float* red_s;       // [2][2 * NCW] block-reduction scratch, alternating halves
-    float* xown;        // fp32 master copy of the residual rows this CTA owns
+    float* red_s;       // block-reduction scratch, two alternating halves of up to 8 * NCW floats
+    float* xown;        // fp32 master copy of the residual rows this CTA owns, [T][16]
     u64* best_s;        // [NCW] block-reduction scratch for 64-bit keys
     float* scale_s;     // per-row scales: two 128-row buffers for layer GEMVs, then the streaming ring
-    float* xscale_s;    // [1] power-of-two factor that undoes the fixed-point scaling of the staged input
-    uint64_t* full;     // [NSTAGE]
-    uint64_t* empty;    // [NSTAGE]
+    float* xscale_s;    // [T] power-of-two factors that undo the fixed-point scaling of the staged inputs
+    uint64_t* full;     // [ring stages]
+    uint64_t* empty;    // [ring stages]
     volatile int* abort_flag;
     volatile int* quit_flag;
 };
@@ -217,40 +217,56 @@ __device__ __forceinline__ void gate_on_samples(Ctx& c, const u64* buf, int nwor
     consumer_sync();
 }
 
-// Sum and max over all consumer threads in one barrier, fixed order.
-__device__ __forceinline__ void consumer_sum_max(Ctx& c, float& sum, float& mx) {
-    float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);
-    sum = warp_sum(sum);
-    mx = warp_max(mx);
-    if (c.lane == 0) {
-        buf[c.warp] = sum;
-        buf[NCW + c.warp] = mx;
+// Geometry that depends on how many tokens one pass over the weights serves (1: plain decode,
+// 2: a speculative cycle).  Two tokens need twice the input planes, so the ring gives up a stage.
+template <int T> struct Geo {
+    static constexpr int NS = T == 1 ? 6 : 5;                       // ring stages
+    static constexpr int RING = NS * SLOT_BYTES;
+    static constexpr int XQ = (T == 1 ? 3 : 7) * 2 * 3584;          // input planes: bf16 pieces of K = 3584 are the largest
+    static constexpr int PART = NCW * T * 64 * 4;                   // per-warp partial sums
+    static constexpr int SMEM = RING + XQ + PART + MAX_BLOCKS * 4 + 2048 + 2048;
+};
+
+// Sums and maxima over all consumer threads in one barrier, fixed order; one pair per token.
+template <int T>
+__device__ __forceinline__ void consumer_sum_max(Ctx& c, float (&sum)[T], float (&mx)[T]) {
+    float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * T * NCW);
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+        const float a = warp_sum(sum[j]), b = warp_max(mx[j]);
+        if (c.lane == 0) {
+            buf[(2 * j) * NCW + c.warp] = a;
+            buf[(2 * j + 1) * NCW + c.warp] = b;
+        }
     }
     consumer_sync();
-    float t = 0.f, m = 0.f;
 #pragma unroll
-    for (int i = 0; i < NCW; i++) {
-        t += buf[i];
-        m = fmaxf(m, buf[NCW + i]);
+    for (int j = 0; j < T; j++) {
+        float t = 0.f, m = 0.f;
+#pragma unroll
+        for (int i = 0; i < NCW; i++) {
+            t += buf[(2 * j) * NCW + i];
+            m = fmaxf(m, buf[(2 * j + 1) * NCW + i]);
+        }
+        sum[j] = t;
+        mx[j] = m;
     }
-    sum = t;
-    mx = m;
 }
 
 // ---- GEMV on the tensor cores ---------------------------------------------------------------------
 // A weight row is cut into 64-byte k-blocks (64 int8 or 32 bf16 weights).  Rows are stored in groups
 // of up to 8, k-block major: block kb of every row of the group, then block kb + 1, ...  One 128-bit
-// load per lane therefore hands a warp an 8-row x 64-byte tile as the B operands of two MMAs
-// (lane = 4 * row + quarter), with no conversion and no bank conflict.
+// load per lane therefore hands a warp an 8-row x 64-byte tile in MMA operand order (lane = 4 * row +
+// quarter), with no conversion and no bank conflict.  Two tiles are the 16-row A operand.
 //
-// The input vector is the A operand.  fp32 inputs are made exact for the tensor cores by splitting:
+// The input vector is the B operand.  fp32 inputs are made exact for the tensor cores by splitting:
 //   int8 weights: x * 2^s rounded to a 28-bit integer, cut into four base-128 digits (int8 planes);
 //                 integer MMAs (s8 x s8 -> s32) are exact, the digits recombine in fp32;
 //   bf16 weights: x = p0 + p1 + p2 with three bf16 pieces (24 significant bits); bf16 MMAs with fp32
 //                 accumulation.
-// Plane m of the staged input is MMA row m, so one MMA handles all planes at once.  Each warp owns a
-// k-slice (k-blocks warp, warp + 16, ...) of every row of the chunk; per-warp partial sums meet in
-// shared memory and warp 0 finishes the rows after one barrier per chunk.
+// Plane 4 * token + piece of the staged input is MMA column 4 * token + piece, so one MMA serves every
+// plane of up to two tokens.  Each warp owns a k-slice (k-blocks warp, warp + 16, ...) of every row of
+// a chunk; per-warp partial sums meet in shared memory.
 template <bool Q8> struct Planes { static constexpr int N = Q8 ? 4 : 3; };
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -266,8 +282,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Stage two consecutive inputs (elements k, k + 1) into the planes.  `scale` is the power of two that
-// maps the vector's largest magnitude below 2^27 (int8 path only).
+// Stage two consecutive inputs (elements k, k + 1) of one token into its planes (`xq` points at the
+// token's first plane).  `scale` is the power of two that maps the vector's largest magnitude below
+// 2^27 (int8 path only).
 template <bool Q8>
 __device__ __forceinline__ void stage_pair(uint8_t* xq, int rb, int k, float v0, float v1, float scale) {
     if (Q8) {
@@ -314,7 +331,8 @@ __device__ __forceinline__ void scale_prefetch(Ctx& c, const float* __restrict__
 }
 
 // MMAs of one or two 16-row blocks (rows [b0, b0 + 32) of the chunk) over this warp's k-blocks.
-// Lane (g, t) returns, per block, the finished planes 2t and 2t + 1 of rows g and g + 8.
+// Lane (g, t) holds, per block, rows g and g + 8 for MMA columns 2t and 2t + 1, i.e. two planes of
+// token t / 2; after the exchange with lane t ^ 1 it holds that token's finished partial sums.
 template <bool Q8>
 __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xrow, bool xlive, int rb, int nkb, int nr,
                                            int b0, int warp, int g, int t, float (&v)[4]) {
@@ -347,7 +365,7 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
             }
         }
     }
-    const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);       // 128^(2t) for the int8 digits
+    const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);       // 128^(2 * (t & 1)) for the int8 digits
     const float pw1 = pw0 * 128.f;
 #pragma unroll
     for (int b = 0; b < 2; b++) {
@@ -364,23 +382,23 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
     }
 }
 
-// Streams this CTA's rows [r0, r1) of a matrix with `rb`-byte rows out of the ring.  Two 8-row tiles
-// form the 16-row A operand of an MMA, the input planes are its B operand (column n = plane n).
-// Every warp owns a k-slice of all rows; per-warp partial sums meet in shared memory.
+// Streams this CTA's rows [r0, r1) of a matrix with `rb`-byte rows out of the ring.
 //   STREAM = false  (layer GEMVs, at most 64 rows per CTA): one barrier after the last chunk, then
-//                   warps 0 and 1 finish the rows;
-//   STREAM = true   (LM head): one barrier per chunk, warp 0 finishes that chunk's rows while the
-//                   other warps move on.
-// A finishing warp calls sink(lane, row, value, valid) on all of its lanes; `value` already carries
-// the row's scale and the input's fixed-point scale.
-template <bool Q8, bool STREAM, class Sink>
+//                   warps 2 * token and 2 * token + 1 finish that token's rows;
+//   STREAM = true   (LM head, draft head): one barrier per chunk, warp `token` finishes that token's
+//                   rows of the chunk while the other warps move on.
+// A finishing warp calls sink(lane, row, token, value, valid) on all of its lanes; `value` already
+// carries the row's scale and the input's fixed-point scale.
+template <bool Q8, int T, bool STREAM, class Sink>
 __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const float* __restrict__ row_scale,
                                          Sink&& sink) {
+    constexpr int NS = Geo<T>::NS;
     const int rpc = SLOT_BYTES / rb;
     const int nkb = rb >> 6;
     const int g = c.lane >> 2, t = c.lane & 3;
-    const uint8_t* xrow = c.sm.xq + g * rb + t * 16;
-    const bool xlive = g < Planes<Q8>::N;
+    const uint8_t* xrow = c.sm.xq + g * rb + t * 16;                      // plane g = column g of the B operand
+    const bool xlive = (g >> 2) < T && (g & 3) < Planes<Q8>::N;
+    const int tok = t >> 1;                                               // token whose sums this lane ends up with
     const float* scales = STREAM ? c.sm.scale_s + 2 * SCALE_BODY : c.sm.scale_s + (c.gemv_n & 1) * SCALE_BODY;
     c.gemv_n++;
     float pend = 1.f;                            // scale fetched for the chunk four ahead (STREAM)
@@ -388,7 +406,7 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
     for (int base = r0; base < r1; base += rpc, chunk++) {
         const int nr = min(rpc, r1 - base);
         const uint32_t n = c.cons_n++;
-        const int slot = (int)(n % NSTAGE);
+        const int slot = (int)(n % NS);
         if (STREAM && row_scale && c.warp == NCW - 1) {
             if (chunk > 0) c.sm.scale_s[2 * SCALE_BODY + ((chunk + 3) & 7) * 32 + c.lane] = pend;
             const int r = base + 4 * rpc + c.lane;
@@ -396,20 +414,20 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
         }
         if (c.prof && c.tid == 0) {
             const u64 t0 = globaltimer();
-            mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
+            mbar_wait(c, &c.sm.full[slot], (n / NS) & 1, W_FULL);
             c.wait_acc += globaltimer() - t0;
         } else {
-            mbar_wait(c, &c.sm.full[slot], (n / NSTAGE) & 1, W_FULL);
+            mbar_wait(c, &c.sm.full[slot], (n / NS) & 1, W_FULL);
         }
         const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
-        // partial sums: [warp][row]; 64 rows per warp for layer GEMVs, two alternating 32-row halves when streaming
-        float* part = STREAM ? c.sm.part_s + ((n & 1) * NCW + c.warp) * 32
-                             : c.sm.part_s + c.warp * 64 + (base - r0);
+        // partial sums [warp][token][row]: 64 rows for layer GEMVs, two alternating 32-row halves when streaming
+        float* part = STREAM ? c.sm.part_s + (((n & 1) * NCW + c.warp) * T + tok) * 32
+                             : c.sm.part_s + (c.warp * T + tok) * 64 + (base - r0);
         if (base == r0) MK_MARK(c, 8);
         for (int b0 = 0; b0 < nr; b0 += 32) {
             float v[4];
             mma_blocks<Q8>(buf, xrow, xlive, rb, nkb, nr, b0, c.warp, g, t, v);
-            if (t == 0) {
+            if ((t & 1) == 0 && tok < T) {
 #pragma unroll
                 for (int q = 0; q < 4; q++)
                     if (b0 + 8 * q + g < nr) part[b0 + 8 * q + g] = v[q];
@@ -421,13 +439,13 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
         if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
         if (STREAM) {
             consumer_sync();
-            if (c.warp == 0) {
-                const float* pp = c.sm.part_s + (n & 1) * NCW * 32 + c.lane;
+            if (c.warp < T) {
+                const float* pp = c.sm.part_s + ((n & 1) * NCW * T + c.warp) * 32 + c.lane;
                 float v = 0.f;
 #pragma unroll
-                for (int w = 0; w < NCW; w++) v += pp[w * 32];
+                for (int w = 0; w < NCW; w++) v += pp[w * T * 32];
                 const float rs = row_scale ? scales[(chunk & 7) * 32 + c.lane] : 1.f;
-                sink(c.lane, base + c.lane, v * rs * *c.sm.xscale_s, c.lane < nr);
+                sink(c.lane, base + c.lane, c.warp, v * rs * c.sm.xscale_s[c.warp], c.lane < nr);
             }
         }
     }
@@ -435,20 +453,21 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
         MK_MARK(c, 9);
         consumer_sync();
         MK_MARK(c, 10);
-        if (c.warp < 2) {
-            const int idx = c.warp * 32 + c.lane;
-            const float* pp = c.sm.part_s + idx;
+        if (c.warp < 2 * T) {
+            const int tk = c.warp >> 1, idx = (c.warp & 1) * 32 + c.lane;
+            const float* pp = c.sm.part_s + tk * 64 + idx;
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < NCW; w++) v += pp[w * 64];
+            for (int w = 0; w < NCW; w++) v += pp[w * T * 64];
             const float rs = row_scale ? scales[idx] : 1.f;
-            sink(c.lane, r0 + idx, v * rs * *c.sm.xscale_s, idx < r1 - r0);
+            sink(c.lane, r0 + idx, tk, v * rs * c.sm.xscale_s[tk], idx < r1 - r0);
             MK_MARK(c, 11);
         }
     }
 }
 
 // ---- producer ----------------------------------------------------------------------------------------
+template <int NS>
 struct Producer {
     Ctx& c;
     u64 policy;
@@ -465,9 +484,9 @@ struct Producer {
         const int rpc = SLOT_BYTES / row_bytes;
         for (int base = r0; base < r1; base += rpc) {
             const int nr = min(rpc, r1 - base);
-            const int slot = (int)(n % NSTAGE);
-            if (n >= NSTAGE) {
-                const uint32_t par = ((n / NSTAGE) - 1) & 1;
+            const int slot = (int)(n % NS);
+            if (n >= NS) {
+                const uint32_t par = ((n / NS) - 1) & 1;
                 Spin s;
                 while (!mbar_try_wait(&c.sm.empty[slot], par)) {
                     if (*c.sm.quit_flag || MK_SPIN_FAIL(c, s, W_EMPTY)) {
@@ -490,11 +509,11 @@ struct Producer {
 
     // Before the CTA may exit, every copy that was issued must have landed.
     __device__ void drain() {
-        const uint32_t first = n > NSTAGE ? n - NSTAGE : 0;
+        const uint32_t first = n > NS ? n - NS : 0;
         for (uint32_t i = first; i < n; i++) {
             Spin s;
             s.t0 = 0;
-            while (!mbar_try_wait(&c.sm.full[i % NSTAGE], (i / NSTAGE) & 1)) {
+            while (!mbar_try_wait(&c.sm.full[i % NS], (i / NS) & 1)) {
                 // Not abortable by the shared flags: the copy is still writing shared memory.
                 if (((++s.it) & 1023u) == 0) {
                     const u64 now = globaltimer();
@@ -509,56 +528,86 @@ struct Producer {
     }
 };
 
-template <class S, bool Q8>
+// The weight stream of one pass: the four GEMVs of every layer, then the LM head when its output is
+// needed; a speculative cycle continues with the draft head's fusion projection, its decoder layer
+// and the draft vocabulary rows.  Consumers consume exactly this sequence.
+template <class S, bool Q8, int T>
 __device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
-    Producer pr(c);
+    Producer<Geo<T>::NS> pr(c);
     constexpr int WB = Q8 ? 1 : 2;  // bytes per weight
+    auto layer = [&](const LayerP& L) {
+        pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID * WB);
+        pr.stream(L.w_out, S::HID, 1, S::MIX * WB);
+        pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID * WB);
+        pr.stream(L.w_down, S::HID, 1, S::INTER * WB);
+    };
     for (int s = 0; s < A.n_steps && !pr.stop; s++) {
-        for (int l = 0; l < P.n_layers && !pr.stop; l++) {
-            const LayerP& L = P.layer[l];
-            pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID * WB);
-            pr.stream(L.w_out, S::HID, 1, S::MIX * WB);
-            pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID * WB);
-            pr.stream(L.w_down, S::HID, 1, S::INTER * WB);
+        for (int l = 0; l < P.n_layers && !pr.stop; l++) layer(P.layer[l]);
+        if (T == 2) {
+            pr.stream(P.lm_head, P.vocab, 1, S::HID * WB);
+            pr.stream(P.mtp_fc, S::HID, 1, 2 * S::HID * WB);
+            layer(P.mtp);
+            pr.stream(P.draft_head, P.draft_vocab, 1, S::HID * WB);
+        } else if (s >= A.lm_from) {
+            pr.stream(P.lm_head, P.vocab, 1, S::HID * WB);
         }
-        if (s >= A.lm_from) pr.stream(P.lm_head, P.vocab, 1, S::HID * WB);
     }
     pr.drain();
 }
 
 // ---- prologues ---------------------------------------------------------------------------------------
-// RMSNorm of the residual stream into the GEMV input planes.  `x0`, `x1` are this thread's two
-// elements (2*tid, 2*tid+1).  One block reduction yields both the sum of squares and the largest
-// |x (1 + w)|, from which the fixed-point scale follows without a second pass.
-template <class S, bool Q8>
-__device__ __forceinline__ void stage_rmsnorm(Ctx& c, float x0, float x1, float2 g) {
+// RMSNorm of T residual vectors into the GEMV input planes.  `x[j]` are this thread's two elements
+// (2*tid, 2*tid+1) of token j.  One block reduction yields, per token, the sum of squares and the
+// largest |x (1 + w)|, from which the fixed-point scale follows without a second pass.  `y` returns
+// the normalised values.
+template <class S, bool Q8, int T>
+__device__ __forceinline__ void stage_rmsnorm(Ctx& c, const float (&x)[T][2], float2 g, float (&y)[T][2]) {
     static_assert(S::HID == 2 * NCT, "two residual elements per consumer thread");
     constexpr int RB = Q8 ? S::HID : 2 * S::HID;
     const int k = 2 * c.tid;
-    const float y0 = x0 * (1.0f + g.x), y1 = x1 * (1.0f + g.y);
-    float ss = x0 * x0 + x1 * x1, mx = fmaxf(fabsf(y0), fabsf(y1));
+    float ss[T], mx[T];
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+        y[j][0] = x[j][0] * (1.0f + g.x);
+        y[j][1] = x[j][1] * (1.0f + g.y);
+        ss[j] = x[j][0] * x[j][0] + x[j][1] * x[j][1];
+        mx[j] = fmaxf(fabsf(y[j][0]), fabsf(y[j][1]));
+    }
     MK_MARK(c, 6);
-    consumer_sum_max(c, ss, mx);
+    consumer_sum_max<T>(c, ss, mx);
     MK_MARK(c, 7);
-    const float inv = rsqrtf(ss * (1.0f / S::HID) + S::EPS);
-    const float scale = Q8 ? fixed_scale(mx * inv) : 1.0f;
-    stage_pair<Q8>(c.sm.xq, RB, k, y0 * inv, y1 * inv, scale);
-    if (c.tid == 0) *c.sm.xscale_s = 1.0f / scale;
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+        const float inv = rsqrtf(ss[j] * (1.0f / S::HID) + S::EPS);
+        const float scale = Q8 ? fixed_scale(mx[j] * inv) : 1.0f;
+        y[j][0] *= inv;
+        y[j][1] *= inv;
+        stage_pair<Q8>(c.sm.xq + (size_t)(4 * j) * RB, RB, k, y[j][0], y[j][1], scale);
+        if (c.tid == 0) c.sm.xscale_s[j] = 1.0f / scale;
+    }
     consumer_sync();
 }
 
-// For inputs that need no norm: the fixed-point scale from this thread's largest magnitude (one
-// block reduction on the int8 path, nothing on the bf16 path) ...
-template <bool Q8>
-__device__ __forceinline__ float block_scale(Ctx& c, float local_max) {
-    if (!Q8) return 1.0f;
-    float dummy = 0.f;
-    consumer_sum_max(c, dummy, local_max);
-    return fixed_scale(local_max);
+// For inputs that need no norm: per-token fixed-point scales from this thread's largest magnitudes
+// (one block reduction on the int8 path, nothing on the bf16 path) ...
+template <bool Q8, int T>
+__device__ __forceinline__ void block_scale(Ctx& c, float (&mx)[T], float (&scale)[T]) {
+    if (Q8) {
+        float dummy[T];
+#pragma unroll
+        for (int j = 0; j < T; j++) dummy[j] = 0.f;
+        consumer_sum_max<T>(c, dummy, mx);
+    }
+#pragma unroll
+    for (int j = 0; j < T; j++) scale[j] = Q8 ? fixed_scale(mx[j]) : 1.0f;
 }
-// ... and the end of a staging phase: publish the inverse scale, make the planes visible.
-__device__ __forceinline__ void finish_stage(Ctx& c, float scale) {
-    if (c.tid == 0) *c.sm.xscale_s = 1.0f / scale;
+// ... and the end of a staging phase: publish the inverse scales, make the planes visible.
+template <int T>
+__device__ __forceinline__ void finish_stage(Ctx& c, const float (&scale)[T]) {
+    if (c.tid == 0) {
+#pragma unroll
+        for (int j = 0; j < T; j++) c.sm.xscale_s[j] = 1.0f / scale[j];
+    }
     consumer_sync();
 }
 
@@ -580,19 +629,24 @@ __device__ __forceinline__ void load_embedding(const Params& P, int token, int t
 
 // ---- Gated DeltaNet recurrence ------------------------------------------------------------------------
 // Task t < GDN_TASKS: head t / 8, value columns [16 * (t % 8), +16).  Warp w owns value column w of the
-// slice; a lane holds 4 consecutive key indices of that column's state row.
-template <class S>
-__device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
+// slice; a lane holds 4 consecutive key indices of that column's state row.  With two tokens the task
+// runs them one after the other: the state after the first token goes to `state_bak`, the state after
+// the second to `state`, and `from_bak` says which of the two the previous cycle left valid.
+template <class S, int T>
+__device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op,
+                       bool from_bak) {
     static_assert(S::GDN_SLICE == NCW && S::LIN_DK == 128, "one warp per value column, 4 keys per lane");
     constexpr int SL = S::LIN_DV / S::GDN_SLICE;  // slices per head
     if (c.cta >= S::GDN_TASKS) return false;
     const int h = c.cta / SL, j = c.cta % SL;
     const int vcol = j * S::GDN_SLICE + c.warp;
-    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);   // [q 128 | k 128 | v 16 | b | a]
-    float* srow = L.state + ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
-    const float4 st = *reinterpret_cast<const float4*>(srow);   // issued before the wait on purpose
-    const float a_log = L.A_log[h], dt_bias = L.dt_bias[h];
     constexpr int NCH = 2 * S::LIN_DK + S::GDN_SLICE;           // 272 conv channels this task needs
+    constexpr int QS = NCH + 8;                                 // per-token stride of the scratch
+    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);           // per token: [q 128 | k 128 | v 16 | b | a]
+    const size_t soff = ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
+    const float* sin = (T == 2 && from_bak) ? L.state_bak + soff : L.state + soff;
+    const float4 st = *reinterpret_cast<const float4*>(sin);    // issued before the wait on purpose
+    const float a_log = L.A_log[h], dt_bias = L.dt_bias[h];
     if (c.tid < NCH) {
         int ch;
         if (c.tid < S::LIN_DK) ch = h * S::LIN_DK + c.tid;
@@ -602,53 +656,92 @@ __device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
         // every task keeps its own history of the channels it convolves (q and k of the head are
         // duplicated across the head's 8 tasks), so nothing here is shared between CTAs
         float* hist = L.conv_hist + ((size_t)c.cta * NCH + c.tid) * CONV_RING;
-        const float h3 = hist[(pos - 3) & (CONV_RING - 1)];
-        const float h2 = hist[(pos - 2) & (CONV_RING - 1)];
-        const float h1 = hist[(pos - 1) & (CONV_RING - 1)];
-        const float cur = ll_wait(c, P.projl + ch, e_proj, W_PROJ);
-        float a = h3 * taps.x;
-        a = fmaf(h2, taps.y, a);
-        a = fmaf(h1, taps.z, a);
-        a = fmaf(cur, taps.w, a);
-        qkv_s[c.tid] = silu_f(a);
-        hist[pos & (CONV_RING - 1)] = cur;
+        float h3 = hist[(pos - 3) & (CONV_RING - 1)];
+        float h2 = hist[(pos - 2) & (CONV_RING - 1)];
+        float h1 = hist[(pos - 1) & (CONV_RING - 1)];
+        float cur[T];
+        if (T == 1) {
+            cur[0] = ll_wait(c, P.projl + ch, e_proj, W_PROJ);
+        } else {
+            Spin s;
+            u64 w0 = ll_load(P.projl + ch), w1 = ll_load(P.projl + S::PROJ_MAX + ch);
+            while ((uint32_t)(w0 >> 32) != e_proj || (uint32_t)(w1 >> 32) != e_proj) {
+                if (MK_SPIN_FAIL(c, s, W_PROJ)) {
+                    c.dead = true;
+                    break;
+                }
+                if ((uint32_t)(w0 >> 32) != e_proj) w0 = ll_load(P.projl + ch);
+                if ((uint32_t)(w1 >> 32) != e_proj) w1 = ll_load(P.projl + S::PROJ_MAX + ch);
+            }
+            cur[0] = __uint_as_float((uint32_t)w0);
+            cur[T - 1] = __uint_as_float((uint32_t)w1);
+        }
+#pragma unroll
+        for (int tk = 0; tk < T; tk++) {
+            float a = h3 * taps.x;
+            a = fmaf(h2, taps.y, a);
+            a = fmaf(h1, taps.z, a);
+            a = fmaf(cur[tk], taps.w, a);
+            qkv_s[tk * QS + c.tid] = silu_f(a);
+            hist[(pos + tk) & (CONV_RING - 1)] = cur[tk];
+            h3 = h2; h2 = h1; h1 = cur[tk];
+        }
     } else if (c.tid < NCH + 2) {
         const int off = (c.tid == NCH ? S::B_OFF : S::A_OFF) + h;
-        qkv_s[c.tid] = ll_wait(c, P.projl + off, e_proj, W_PROJ);
+#pragma unroll
+        for (int tk = 0; tk < T; tk++)
+            qkv_s[tk * QS + c.tid] = ll_wait(c, P.projl + (size_t)tk * S::PROJ_MAX + off, e_proj, W_PROJ);
     }
     consumer_sync();
     prof_stamp(c, op, 1);
-    const float4 q4 = *reinterpret_cast<const float4*>(qkv_s + 4 * c.lane);
-    const float4 k4 = *reinterpret_cast<const float4*>(qkv_s + S::LIN_DK + 4 * c.lane);
-    const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
-    const float kn = warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w);
-    // x / max(|x|, 1e-6), and the 1/sqrt(dk) query scale
-    const float qs = 0.08838834764831845f / fmaxf(sqrtf(qn), 1e-6f);
-    const float ks = 1.0f / fmaxf(sqrtf(kn), 1e-6f);
-    const float vval = qkv_s[2 * S::LIN_DK + c.warp];
-    const float beta = sigmoid_f(qkv_s[NCH]);
-    const float decay = expf(-expf(a_log) * softplus_f(qkv_s[NCH + 1] + dt_bias));
-    const float kx = k4.x * ks, ky = k4.y * ks, kz = k4.z * ks, kw = k4.w * ks;
-    float s0 = st.x * decay, s1 = st.y * decay, s2 = st.z * decay, s3 = st.w * decay;
-    const float recalled = warp_sum(fmaf(s3, kw, fmaf(s2, kz, fmaf(s1, ky, s0 * kx))));
-    const float delta = (vval - recalled) * beta;
-    s0 = fmaf(kx, delta, s0);
-    s1 = fmaf(ky, delta, s1);
-    s2 = fmaf(kz, delta, s2);
-    s3 = fmaf(kw, delta, s3);
-    *reinterpret_cast<float4*>(srow) = make_float4(s0, s1, s2, s3);
-    const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
+    float s0 = st.x, s1 = st.y, s2 = st.z, s3 = st.w;
+#pragma unroll
+    for (int tk = 0; tk < T; tk++) {
+        const float* qs_ = qkv_s + tk * QS;
+        const float4 q4 = *reinterpret_cast<const float4*>(qs_ + 4 * c.lane);
+        const float4 k4 = *reinterpret_cast<const float4*>(qs_ + S::LIN_DK + 4 * c.lane);
+        const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
+        const float kn = warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w);
+        // x / max(|x|, 1e-6), and the 1/sqrt(dk) query scale
+        const float qs = 0.08838834764831845f / fmaxf(sqrtf(qn), 1e-6f);
+        const float ks = 1.0f / fmaxf(sqrtf(kn), 1e-6f);
+        const float vval = qs_[2 * S::LIN_DK + c.warp];
+        const float beta = sigmoid_f(qs_[NCH]);
+        const float decay = expf(-expf(a_log) * softplus_f(qs_[NCH + 1] + dt_bias));
+        const float kx = k4.x * ks, ky = k4.y * ks, kz = k4.z * ks, kw = k4.w * ks;
+        s0 *= decay; s1 *= decay; s2 *= decay; s3 *= decay;
+        const float recalled = warp_sum(fmaf(s3, kw, fmaf(s2, kz, fmaf(s1, ky, s0 * kx))));
+        const float delta = (vval - recalled) * beta;
+        s0 = fmaf(kx, delta, s0);
+        s1 = fmaf(ky, delta, s1);
+        s2 = fmaf(kz, delta, s2);
+        s3 = fmaf(kw, delta, s3);
+        float* sout = (T == 2 && tk == 0) ? L.state_bak + soff : L.state + soff;
+        *reinterpret_cast<float4*>(sout) = make_float4(s0, s1, s2, s3);
+        const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
+        if (c.lane == 0) ll_store(P.mixl + (size_t)tk * S::MIX + h * S::LIN_DV + vcol, e_out, o);
+    }
     prof_stamp(c, op, 2);
-    if (c.lane == 0) ll_store(P.mixl + h * S::LIN_DV + vcol, e_out, o);
     consumer_sync();  // the scratch aliases the GEMV input vector that the next prologue writes
     return true;
 }
 
-// ---- attention ---------------------------------------------------------------------------------------
-template <bool F32> struct KvT;
-template <> struct KvT<true> { typedef float type; };
-template <> struct KvT<false> { typedef __nv_bfloat16 type; };
+// After a launch that ends on a rejected draft the valid DeltaNet state sits in `state_bak`: copy
+// this task's rows back so that the host (and the next plain launch) finds it in `state`.
+template <class S>
+__device__ void gdn_restore_state(Ctx& c, const Params& P) {
+    constexpr int SL = S::LIN_DV / S::GDN_SLICE;
+    if (c.cta >= S::GDN_TASKS) return;
+    const int h = c.cta / SL, j = c.cta % SL;
+    const size_t soff = ((size_t)(h * S::LIN_DV + j * S::GDN_SLICE + c.warp) * S::LIN_DK) + 4 * c.lane;
+    for (int l = 0; l < P.n_layers; l++) {
+        const LayerP& L = P.layer[l];
+        if (L.kind != 0) continue;
+        *reinterpret_cast<float4*>(L.state + soff) = *reinterpret_cast<const float4*>(L.state_bak + soff);
+    }
+}
 
+// ---- attention ---------------------------------------------------------------------------------------
 template <bool F32>
 __device__ __forceinline__ void load8(const void* base, size_t elem, float (&v)[8]) {
     if (F32) {
@@ -677,18 +770,19 @@ __device__ __forceinline__ void store1(void* base, size_t elem, float v) {
     else ((__nv_bfloat16*)base)[elem] = __float2bfloat16(v);
 }
 
-// Split-K decode attention over the paged cache.  Task (g, s): KV head g, positions
-// [s * ch, min(n, (s + 1) * ch)), run by CTA s * NKV + g.  Cached K and V rows of the task are
-// requested before the task waits for its query, so that only one memory round trip sits between
-// the projection and the scores.  With one split the task publishes the normalised output itself;
+// Split-K decode attention over the paged cache, for T consecutive positions pos .. pos + T - 1 of one
+// sequence.  Task (g, s): KV head g, positions [s * ch, min(n, (s + 1) * ch)) with n = pos + T, run by
+// CTA s * NKV + g.  Token j sees positions up to pos + j.  Cached K and V rows of the task are requested
+// before the task waits for its queries, so that only one memory round trip sits between the
+// projection and the scores.  With one split the task publishes the normalised outputs itself;
 // otherwise every task publishes (acc, m, l) partials as flag-in-data words and then merges a
 // 1/nsplit share of the head group's outputs from all partials, in a fixed order.
-template <class S, bool KVF32>
+template <class S, bool KVF32, int T>
 __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
-    constexpr int NOUT = S::QPK * S::HD;        // outputs per KV head
-    constexpr int PFK = 1, PFV = 16;            // rows prefetched per warp (K) and per thread (V)
-    const int n = pos + 1;
+    constexpr int NOUT = S::QPK * S::HD;        // outputs per KV head and token
+    constexpr int PFV = 16;                     // V rows requested early per thread
+    const int n = pos + T;
     const int max_splits = min(c.grid / S::NKV, MAX_SPLITS);
     const int ch = attn_chunk(n, max_splits);
     const int nsplit = (n + ch - 1) / ch;
@@ -696,148 +790,151 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     const int g = c.cta % S::NKV, sp = c.cta / S::NKV;
     const int p0 = sp * ch, p1 = min(n, p0 + ch);
     const int np = p1 - p0;
-    const bool has_new = (p1 == n);
 
-    float* q_s = reinterpret_cast<float*>(c.sm.xq);   // [4][256] normalised, rotated, pre-scaled queries
-    float* knew_s = q_s + S::QPK * S::HD;       // [256]
-    float* vnew_s = knew_s + S::HD;             // [256]
-    float* sc_s = vnew_s + S::HD;               // [4][ch] scores, then probabilities
-    float* stat_s = c.sm.out_s;                 // [4] m, [4] l
+    float* q_s = reinterpret_cast<float*>(c.sm.xq);       // [T][4][256] normalised, rotated, pre-scaled queries
+    float* knew_s = q_s + T * S::QPK * S::HD;             // [T][256] rows of positions pos .. pos + T - 1
+    float* vnew_s = knew_s + T * S::HD;                   // [T][256]
+    float* sc_s = vnew_s + T * S::HD;                     // [T][4][ch] scores, then probabilities
+    float* stat_s = c.sm.out_s;                           // [T][ m[4], l[4] ]
 
     const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
     auto kv_elem = [&](int p) -> size_t {
         const int blk = c.sm.bt_s[p >> 6];
         return ((size_t)blk * S::NKV + g) * kv_head_stride + (size_t)(p & (KV_BLOCK - 1)) * S::HD;
     };
-    // -- 0. request cached rows early: K rows of this warp's positions, V elements of this thread's dim
+    // -- 0. request cached rows early: the K row of this warp's first position, V elements of this thread's dim
     const int d = c.tid & (S::HD - 1), hp = c.tid >> 8;
-    float kpre[PFK][8], vpre[PFV];
+    float kpre[8], vpre[PFV];
+    {
+        const int p = p0 + c.warp;
 #pragma unroll
-    for (int i = 0; i < PFK; i++) {
-        const int p = p0 + c.warp + i * NCW;
-#pragma unroll
-        for (int j = 0; j < 8; j++) kpre[i][j] = 0.f;
-        if (p < p1 && p != pos) load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kpre[i]);
+        for (int i = 0; i < 8; i++) kpre[i] = 0.f;
+        if (p < p1 && p < pos) load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kpre);
     }
 #pragma unroll
     for (int i = 0; i < PFV; i++) {
         const int p = p0 + i;
-        vpre[i] = (p < p1 && p != pos) ? load1<KVF32>(L.v_cache, kv_elem(p) + d) : 0.f;
+        vpre[i] = (p < p1 && p < pos) ? load1<KVF32>(L.v_cache, kv_elem(p) + d) : 0.f;
     }
 
-    // -- 1. q (4 heads), new k, new v from the projection words; per-head RMSNorm; partial RoPE
+    // -- 1. q (4 heads), new k, new v of every token from the projection words; per-head RMSNorm; partial RoPE
     {
         const int hh = c.warp >> 2, qd = c.warp & 3;        // head within group, 64-wide quarter
         const int dd = qd * 64 + 2 * c.lane;
-        const u64* const ptrs[2] = {P.projl + (g * S::QPK + hh) * 2 * S::HD + dd,
-                                    hh == 0 ? P.projl + S::ATT_K_OFF + g * S::HD + dd
-                                            : (hh == 1 ? P.projl + S::ATT_V_OFF + g * S::HD + dd : nullptr)};
-        const uint32_t eps[2] = {e_proj, e_proj};
-        // norm weights and rotation angles are requested before the wait
+        // norm weights are requested before the wait
         const float2 qw = *reinterpret_cast<const float2*>(L.q_norm + dd);
         const float2 kw = hh == 0 ? *reinterpret_cast<const float2*>(L.k_norm + dd) : make_float2(0.f, 0.f);
-        float cs0 = 1.f, sn0 = 0.f, cs1 = 1.f, sn1 = 0.f;
-        if (qd == 0) {
-            const int i0 = (2 * c.lane) & 31;
-            cs0 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0];
-            sn0 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0];
-            cs1 = P.rope_cos[(size_t)pos * (S::ROT / 2) + i0 + 1];
-            sn1 = P.rope_sin[(size_t)pos * (S::ROT / 2) + i0 + 1];
+        const u64* ptrs[2 * T];
+        uint32_t eps[2 * T];
+#pragma unroll
+        for (int tk = 0; tk < T; tk++) {
+            const u64* pj = P.projl + (size_t)tk * S::PROJ_MAX;
+            ptrs[2 * tk] = pj + (g * S::QPK + hh) * 2 * S::HD + dd;
+            ptrs[2 * tk + 1] = hh == 0 ? pj + S::ATT_K_OFF + g * S::HD + dd
+                                       : (hh == 1 ? pj + S::ATT_V_OFF + g * S::HD + dd : nullptr);
+            eps[2 * tk] = eps[2 * tk + 1] = e_proj;
         }
-        float v4[4];
-        ll_wait_pairs<2>(c, ptrs, eps, v4, W_PROJ);
-        float a = v4[0], b = v4[1];
-        float ka = hh == 0 ? v4[2] : 0.f, kb = hh == 0 ? v4[3] : 0.f;
-        const float va = v4[2], vb = v4[3];
-        float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);      // q sums [16], k sums [4]
-        const float sq = warp_sum(a * a + b * b);
-        const float sk = warp_sum(ka * ka + kb * kb);
-        if (c.lane == 0) {
-            buf[c.warp] = sq;
-            if (hh == 0) buf[NCW + qd] = sk;
+        float v4[4 * T];
+        ll_wait_pairs<2 * T>(c, ptrs, eps, v4, W_PROJ);
+        float* buf = c.sm.red_s + (c.red_n++ & 1) * (2 * T * NCW);      // per token: q sums [16], k sums [4]
+#pragma unroll
+        for (int tk = 0; tk < T; tk++) {
+            const float a = v4[4 * tk], b = v4[4 * tk + 1];
+            const float ka = hh == 0 ? v4[4 * tk + 2] : 0.f, kb = hh == 0 ? v4[4 * tk + 3] : 0.f;
+            const float sq = warp_sum(a * a + b * b);
+            const float sk = warp_sum(ka * ka + kb * kb);
+            if (c.lane == 0) {
+                buf[tk * 2 * NCW + c.warp] = sq;
+                if (hh == 0) buf[tk * 2 * NCW + NCW + qd] = sk;
+            }
         }
         consumer_sync();
-        const float qss = buf[hh * 4] + buf[hh * 4 + 1] + buf[hh * 4 + 2] + buf[hh * 4 + 3];
-        const float qinv = rsqrtf(qss * (1.0f / S::HD) + S::EPS);
-        a = a * qinv * (1.0f + qw.x);
-        b = b * qinv * (1.0f + qw.y);
-        if (qd == 0) {
-            // dims [0,32) live in lanes 0..15, their partners [32,64) in lanes 16..31
-            const float pa = __shfl_xor_sync(0xffffffffu, a, 16), pb = __shfl_xor_sync(0xffffffffu, b, 16);
-            if (c.lane < 16) { a = a * cs0 - pa * sn0; b = b * cs1 - pb * sn1; }
-            else { a = a * cs0 + pa * sn0; b = b * cs1 + pb * sn1; }
-        }
-        q_s[hh * S::HD + dd] = a * 0.0625f;          // 1/sqrt(256), exact
-        q_s[hh * S::HD + dd + 1] = b * 0.0625f;
-        if (hh == 0) {
-            const float kss = buf[NCW] + buf[NCW + 1] + buf[NCW + 2] + buf[NCW + 3];
-            const float kinv = rsqrtf(kss * (1.0f / S::HD) + S::EPS);
-            ka = ka * kinv * (1.0f + kw.x);
-            kb = kb * kinv * (1.0f + kw.y);
+#pragma unroll
+        for (int tk = 0; tk < T; tk++) {
+            float a = v4[4 * tk], b = v4[4 * tk + 1];
+            float ka = hh == 0 ? v4[4 * tk + 2] : 0.f, kb = hh == 0 ? v4[4 * tk + 3] : 0.f;
+            const float va = v4[4 * tk + 2], vb = v4[4 * tk + 3];
+            const float* bq = buf + tk * 2 * NCW;
+            const float qss = bq[hh * 4] + bq[hh * 4 + 1] + bq[hh * 4 + 2] + bq[hh * 4 + 3];
+            const float qinv = rsqrtf(qss * (1.0f / S::HD) + S::EPS);
+            a = a * qinv * (1.0f + qw.x);
+            b = b * qinv * (1.0f + qw.y);
+            float cs0 = 1.f, sn0 = 0.f, cs1 = 1.f, sn1 = 0.f;
             if (qd == 0) {
-                const float pa = __shfl_xor_sync(0xffffffffu, ka, 16), pb = __shfl_xor_sync(0xffffffffu, kb, 16);
-                if (c.lane < 16) { ka = ka * cs0 - pa * sn0; kb = kb * cs1 - pb * sn1; }
-                else { ka = ka * cs0 + pa * sn0; kb = kb * cs1 + pb * sn1; }
+                const int i0 = (2 * c.lane) & 31;
+                const size_t ro = (size_t)(pos + tk) * (S::ROT / 2) + i0;
+                cs0 = P.rope_cos[ro]; sn0 = P.rope_sin[ro]; cs1 = P.rope_cos[ro + 1]; sn1 = P.rope_sin[ro + 1];
+                // dims [0,32) live in lanes 0..15, their partners [32,64) in lanes 16..31
+                const float pa = __shfl_xor_sync(0xffffffffu, a, 16), pb = __shfl_xor_sync(0xffffffffu, b, 16);
+                if (c.lane < 16) { a = a * cs0 - pa * sn0; b = b * cs1 - pb * sn1; }
+                else { a = a * cs0 + pa * sn0; b = b * cs1 + pb * sn1; }
             }
-            knew_s[dd] = round_kv<KVF32>(ka);
-            knew_s[dd + 1] = round_kv<KVF32>(kb);
-        }
-        if (hh == 1) {
-            vnew_s[dd] = round_kv<KVF32>(va);
-            vnew_s[dd + 1] = round_kv<KVF32>(vb);
+            float* qt = q_s + (tk * S::QPK + hh) * S::HD;
+            qt[dd] = a * 0.0625f;          // 1/sqrt(256), exact
+            qt[dd + 1] = b * 0.0625f;
+            if (hh == 0) {
+                const float kss = bq[NCW] + bq[NCW + 1] + bq[NCW + 2] + bq[NCW + 3];
+                const float kinv = rsqrtf(kss * (1.0f / S::HD) + S::EPS);
+                ka = ka * kinv * (1.0f + kw.x);
+                kb = kb * kinv * (1.0f + kw.y);
+                if (qd == 0) {
+                    const float pa = __shfl_xor_sync(0xffffffffu, ka, 16), pb = __shfl_xor_sync(0xffffffffu, kb, 16);
+                    if (c.lane < 16) { ka = ka * cs0 - pa * sn0; kb = kb * cs1 - pb * sn1; }
+                    else { ka = ka * cs0 + pa * sn0; kb = kb * cs1 + pb * sn1; }
+                }
+                knew_s[tk * S::HD + dd] = round_kv<KVF32>(ka);
+                knew_s[tk * S::HD + dd + 1] = round_kv<KVF32>(kb);
+            }
+            if (hh == 1) {
+                vnew_s[tk * S::HD + dd] = round_kv<KVF32>(va);
+                vnew_s[tk * S::HD + dd + 1] = round_kv<KVF32>(vb);
+            }
         }
         consumer_sync();
         prof_stamp(c, op, 1);
     }
-    // -- 2. append the new position (the task that owns it)
-    if (has_new && c.tid < S::HD) {
-        const size_t e = kv_elem(pos) + c.tid;
-        store1<KVF32>(L.k_cache, e, knew_s[c.tid]);
-        store1<KVF32>(L.v_cache, e, vnew_s[c.tid]);
-    }
-    // -- 3. scores: one warp per position, 8 dims per lane
-    {
-        float q[S::QPK][8];
+    // -- 2. append the new positions (the tasks that own them)
 #pragma unroll
-        for (int hh = 0; hh < S::QPK; hh++) {
-            const float4 x = *reinterpret_cast<const float4*>(q_s + hh * S::HD + 8 * c.lane);
-            const float4 y = *reinterpret_cast<const float4*>(q_s + hh * S::HD + 8 * c.lane + 4);
-            q[hh][0] = x.x; q[hh][1] = x.y; q[hh][2] = x.z; q[hh][3] = x.w;
-            q[hh][4] = y.x; q[hh][5] = y.y; q[hh][6] = y.z; q[hh][7] = y.w;
+    for (int tk = 0; tk < T; tk++) {
+        const int pn = pos + tk;
+        if (pn >= p0 && pn < p1 && c.tid < S::HD) {
+            const size_t e = kv_elem(pn) + c.tid;
+            store1<KVF32>(L.k_cache, e, knew_s[tk * S::HD + c.tid]);
+            store1<KVF32>(L.v_cache, e, vnew_s[tk * S::HD + c.tid]);
         }
+    }
+    // -- 3. scores: one warp per position, 8 dims per lane; token j ignores positions after pos + j
+    {
         auto score = [&](int p, const float (&kk)[8]) {
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                d0 = fmaf(q[0][i], kk[i], d0);
-                d1 = fmaf(q[1][i], kk[i], d1);
-                d2 = fmaf(q[2][i], kk[i], d2);
-                d3 = fmaf(q[3][i], kk[i], d3);
-            }
-            d0 = warp_sum(d0); d1 = warp_sum(d1); d2 = warp_sum(d2); d3 = warp_sum(d3);
-            if (c.lane == 0) {
-                sc_s[0 * ch + (p - p0)] = d0;
-                sc_s[1 * ch + (p - p0)] = d1;
-                sc_s[2 * ch + (p - p0)] = d2;
-                sc_s[3 * ch + (p - p0)] = d3;
+            for (int tk = 0; tk < T; tk++) {
+                float dsum[S::QPK];
+#pragma unroll
+                for (int hh = 0; hh < S::QPK; hh++) {
+                    const float* qt = q_s + (tk * S::QPK + hh) * S::HD + 8 * c.lane;
+                    const float4 x = *reinterpret_cast<const float4*>(qt);
+                    const float4 y = *reinterpret_cast<const float4*>(qt + 4);
+                    float a = x.x * kk[0];
+                    a = fmaf(x.y, kk[1], a); a = fmaf(x.z, kk[2], a); a = fmaf(x.w, kk[3], a);
+                    a = fmaf(y.x, kk[4], a); a = fmaf(y.y, kk[5], a); a = fmaf(y.z, kk[6], a); a = fmaf(y.w, kk[7], a);
+                    dsum[hh] = warp_sum(a);
+                }
+                if (c.lane == 0) {
+                    const bool seen = p <= pos + tk;
+#pragma unroll
+                    for (int hh = 0; hh < S::QPK; hh++)
+                        sc_s[(tk * S::QPK + hh) * ch + (p - p0)] = seen ? dsum[hh] : -INFINITY;
+                }
             }
         };
-#pragma unroll
-        for (int i = 0; i < PFK; i++) {
-            const int p = p0 + c.warp + i * NCW;
-            if (p < p1) {
-                if (p == pos) {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) kpre[i][j] = knew_s[8 * c.lane + j];
-                }
-                score(p, kpre[i]);
-            }
-        }
-        for (int p = p0 + c.warp + PFK * NCW; p < p1; p += NCW) {
+        for (int p = p0 + c.warp; p < p1; p += NCW) {
             float kk[8];
-            if (p == pos) {
+            if (p >= pos) {
 #pragma unroll
-                for (int j = 0; j < 8; j++) kk[j] = knew_s[8 * c.lane + j];
+                for (int i = 0; i < 8; i++) kk[i] = knew_s[(p - pos) * S::HD + 8 * c.lane + i];
+            } else if (p == p0 + c.warp) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) kk[i] = kpre[i];
             } else {
                 load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kk);
             }
@@ -845,36 +942,42 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         }
     }
     consumer_sync();
-    // -- 4. softmax statistics: warp hh < 4 handles head hh
-    if (c.warp < S::QPK) {
+    // -- 4. softmax statistics: warp w < 4T handles (token w / 4, head w % 4)
+    if (c.warp < T * S::QPK) {
         float* row = sc_s + c.warp * ch;
         float m = -INFINITY;
         for (int i = c.lane; i < np; i += 32) m = fmaxf(m, row[i]);
         m = warp_max(m);
         float l = 0.f;
         for (int i = c.lane; i < np; i += 32) {
-            const float e = __expf(row[i] - m);
+            const float e = m == -INFINITY ? 0.f : __expf(row[i] - m);
             row[i] = e;
             l += e;
         }
         l = warp_sum(l);
         if (c.lane == 0) {
-            stat_s[c.warp] = m;
-            stat_s[S::QPK + c.warp] = l;
+            stat_s[(c.warp >> 2) * 8 + (c.warp & 3)] = m;
+            stat_s[(c.warp >> 2) * 8 + S::QPK + (c.warp & 3)] = l;
         }
     }
     consumer_sync();
-    // -- 5. weighted values: thread -> dim d, heads 2*hp and 2*hp+1
-    float acc0 = 0.f, acc1 = 0.f;
+    // -- 5. weighted values: thread -> dim d, heads 2*hp and 2*hp+1, every token
+    float acc[T][2];
+#pragma unroll
+    for (int tk = 0; tk < T; tk++) acc[tk][0] = acc[tk][1] = 0.f;
     {
-        const float* pr0 = sc_s + (2 * hp) * ch;
-        const float* pr1 = sc_s + (2 * hp + 1) * ch;
+        auto accumulate = [&](int i, float v) {
+#pragma unroll
+            for (int tk = 0; tk < T; tk++) {
+                acc[tk][0] = fmaf(sc_s[(tk * S::QPK + 2 * hp) * ch + i], v, acc[tk][0]);
+                acc[tk][1] = fmaf(sc_s[(tk * S::QPK + 2 * hp + 1) * ch + i], v, acc[tk][1]);
+            }
+        };
 #pragma unroll
         for (int i = 0; i < PFV; i++) {
             if (i < np) {
-                const float v = (p0 + i == pos) ? vnew_s[d] : vpre[i];
-                acc0 = fmaf(pr0[i], v, acc0);
-                acc1 = fmaf(pr1[i], v, acc1);
+                const int p = p0 + i;
+                accumulate(i, p >= pos ? vnew_s[(p - pos) * S::HD + d] : vpre[i]);
             }
         }
         int i = PFV;
@@ -883,130 +986,325 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
 #pragma unroll
             for (int u = 0; u < 8; u++) {
                 const int p = p0 + i + u;
-                v[u] = (p == pos) ? vnew_s[d] : load1<KVF32>(L.v_cache, kv_elem(p) + d);
+                v[u] = p >= pos ? vnew_s[(p - pos) * S::HD + d] : load1<KVF32>(L.v_cache, kv_elem(p) + d);
             }
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                acc0 = fmaf(pr0[i + u], v[u], acc0);
-                acc1 = fmaf(pr1[i + u], v[u], acc1);
-            }
+            for (int u = 0; u < 8; u++) accumulate(i + u, v[u]);
         }
         for (; i < np; i++) {
             const int p = p0 + i;
-            const float v = (p == pos) ? vnew_s[d] : load1<KVF32>(L.v_cache, kv_elem(p) + d);
-            acc0 = fmaf(pr0[i], v, acc0);
-            acc1 = fmaf(pr1[i], v, acc1);
+            accumulate(i, p >= pos ? vnew_s[(p - pos) * S::HD + d] : load1<KVF32>(L.v_cache, kv_elem(p) + d));
         }
     }
-    u64* out = P.mixl + (size_t)(g * S::QPK) * S::HD;
     prof_stamp(c, op, 2);
     if (nsplit == 1) {
-        ll_store(out + (2 * hp) * S::HD + d, e_out, acc0 / stat_s[S::QPK + 2 * hp]);
-        ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc1 / stat_s[S::QPK + 2 * hp + 1]);
-        // The appended K/V row is read by other CTAs from the next step on.  They get there only
+#pragma unroll
+        for (int tk = 0; tk < T; tk++) {
+            u64* out = P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
+            ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
+            ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
+        }
+        // The appended K/V rows are read by other CTAs from the next step on.  They get there only
         // through words this CTA publishes after this fence, so the fence can sit off the critical path.
         __threadfence();
         consumer_sync();  // scratch aliases the GEMV input planes that the next prologue writes
         return true;
     }
-    // -- 6. partials as flag-in-data words: acc [4][256], then (m, l) per head
-    u64* part = P.attn_part + ((size_t)g * MAX_SPLITS + sp) * S::PART_STRIDE;
-    ll_store(part + (2 * hp) * S::HD + d, e_out, acc0);
-    ll_store(part + (2 * hp + 1) * S::HD + d, e_out, acc1);
-    if (c.tid < 2 * S::QPK) ll_store(part + NOUT + c.tid, e_out, stat_s[(c.tid & 1) * S::QPK + (c.tid >> 1)]);
+    // -- 6. partials as flag-in-data words: per token acc [4][256], then (m, l) per head
+#pragma unroll
+    for (int tk = 0; tk < T; tk++) {
+        u64* part = P.attn_part + (((size_t)tk * S::NKV + g) * MAX_SPLITS + sp) * S::PART_STRIDE;
+        ll_store(part + (2 * hp) * S::HD + d, e_out, acc[tk][0]);
+        ll_store(part + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1]);
+        if (c.tid < 2 * S::QPK) ll_store(part + NOUT + c.tid, e_out, stat_s[tk * 8 + (c.tid & 1) * S::QPK + (c.tid >> 1)]);
+    }
     // -- 7. merge this task's share of the outputs.  `tpo` threads share one output, each takes the
     //       splits s = sub, sub + tpo, ...; a fixed shuffle tree combines them.
-    const int opc = (NOUT + nsplit - 1) / nsplit;           // outputs per task
+    const int opc = (NOUT + nsplit - 1) / nsplit;           // outputs per task and token
     int tpo = 1;
     while (tpo < 32 && 2 * tpo * opc <= NCT && tpo < nsplit) tpo *= 2;
     const int oi = c.tid / tpo, sub = c.tid % tpo;
     const int o = sp * opc + oi;
     const bool live = oi < opc && o < NOUT;
     const int h = o / S::HD;
-    const u64* pg = P.attn_part + (size_t)g * MAX_SPLITS * S::PART_STRIDE;
     constexpr int SPT = 4;                                   // splits per thread at most (MAX_SPLITS / 32)
-    float mv[SPT], lv[SPT], av[SPT];
-    {
-        u64 wa[SPT], wm[SPT], wl[SPT];
 #pragma unroll
-        for (int i = 0; i < SPT; i++) {
-            const int s2 = sub + i * tpo;
-            wa[i] = wm[i] = wl[i] = 0;
-            if (live && s2 < nsplit) {
-                const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
-                wa[i] = ll_load(ps + o);
-                ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
-            }
-        }
-        Spin spin;
-        while (true) {
-            bool ok = true;
+    for (int tk = 0; tk < T; tk++) {
+        const u64* pg = P.attn_part + ((size_t)tk * S::NKV + g) * MAX_SPLITS * S::PART_STRIDE;
+        float mv[SPT], lv[SPT], av[SPT];
+        {
+            u64 wa[SPT], wm[SPT], wl[SPT];
 #pragma unroll
             for (int i = 0; i < SPT; i++) {
                 const int s2 = sub + i * tpo;
+                wa[i] = wm[i] = wl[i] = 0;
                 if (live && s2 < nsplit) {
                     const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
-                    if ((uint32_t)(wa[i] >> 32) != e_out) { ok = false; wa[i] = ll_load(ps + o); }
-                    if ((uint32_t)(wm[i] >> 32) != e_out || (uint32_t)(wl[i] >> 32) != e_out) {
-                        ok = false;
-                        ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
-                    }
+                    wa[i] = ll_load(ps + o);
+                    ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
                 }
             }
-            if (ok) break;
-            if (MK_SPIN_FAIL(c, spin, W_PART)) {
-                c.dead = true;
-                break;
+            Spin spin;
+            while (true) {
+                bool ok = true;
+#pragma unroll
+                for (int i = 0; i < SPT; i++) {
+                    const int s2 = sub + i * tpo;
+                    if (live && s2 < nsplit) {
+                        const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
+                        if ((uint32_t)(wa[i] >> 32) != e_out) { ok = false; wa[i] = ll_load(ps + o); }
+                        if ((uint32_t)(wm[i] >> 32) != e_out || (uint32_t)(wl[i] >> 32) != e_out) {
+                            ok = false;
+                            ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
+                        }
+                    }
+                }
+                if (ok) break;
+                if (MK_SPIN_FAIL(c, spin, W_PART)) {
+                    c.dead = true;
+                    break;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < SPT; i++) {
+                const bool have = live && sub + i * tpo < nsplit;
+                mv[i] = have ? __uint_as_float((uint32_t)wm[i]) : -INFINITY;
+                lv[i] = have ? __uint_as_float((uint32_t)wl[i]) : 0.f;
+                av[i] = have ? __uint_as_float((uint32_t)wa[i]) : 0.f;
             }
         }
+        float M = fmaxf(fmaxf(mv[0], mv[1]), fmaxf(mv[2], mv[3]));
+        for (int x = 1; x < tpo; x *= 2) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
+        float Ls = 0.f, Os = 0.f;
 #pragma unroll
         for (int i = 0; i < SPT; i++) {
-            const bool have = live && sub + i * tpo < nsplit;
-            mv[i] = have ? __uint_as_float((uint32_t)wm[i]) : -INFINITY;
-            lv[i] = have ? __uint_as_float((uint32_t)wl[i]) : 0.f;
-            av[i] = have ? __uint_as_float((uint32_t)wa[i]) : 0.f;
+            const float w = mv[i] == -INFINITY ? 0.f : __expf(mv[i] - M);
+            Ls = fmaf(lv[i], w, Ls);
+            Os = fmaf(av[i], w, Os);
         }
+        for (int x = 1; x < tpo; x *= 2) {
+            Ls += __shfl_xor_sync(0xffffffffu, Ls, x);
+            Os += __shfl_xor_sync(0xffffffffu, Os, x);
+        }
+        if (live && sub == 0) ll_store(P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD + o, e_out, Os / Ls);
     }
-    float M = fmaxf(fmaxf(mv[0], mv[1]), fmaxf(mv[2], mv[3]));
-    for (int x = 1; x < tpo; x *= 2) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, x));
-    float Ls = 0.f, Os = 0.f;
-#pragma unroll
-    for (int i = 0; i < SPT; i++) {
-        const float w = mv[i] == -INFINITY ? 0.f : __expf(mv[i] - M);
-        Ls = fmaf(lv[i], w, Ls);
-        Os = fmaf(av[i], w, Os);
-    }
-    for (int x = 1; x < tpo; x *= 2) {
-        Ls += __shfl_xor_sync(0xffffffffu, Ls, x);
-        Os += __shfl_xor_sync(0xffffffffu, Os, x);
-    }
-    if (live && sub == 0) ll_store(out + o, e_out, Os / Ls);
     __threadfence();      // K/V append before anything this CTA publishes later (see above)
     consumer_sync();      // scratch aliases the GEMV input planes that the next prologue writes
     return true;
 }
 
+// ---- one decoder layer -----------------------------------------------------------------------------------
+// Runs ops A..E of layer `L` for T tokens at positions pos .. pos + T - 1 on the residual stream `xbuf`
+// (words [T][HID]).  `x` holds this thread's residual elements when `x_in_regs` (first layer: they come
+// from the embedding lookup), otherwise they are awaited at epoch eA - 1.  Returns true if a wait ran out.
+template <class S, bool Q8, bool KVF32, int T>
+__device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP& L, u64* xbuf, uint32_t eA, int op0,
+                                          int pos, float (&x)[T][2], bool x_in_regs, bool from_bak, int xr0, int xr1,
+                                          float* resid_out) {
+    constexpr int WB = Q8 ? 1 : 2;                       // bytes per weight
+    const uint32_t eB = eA + 1, eC = eA + 2, eD = eA + 3, eE = eA + 4;
+    const bool attn = L.kind != 0;
+    float y[T][2];
+    // ---- A: in-projection
+    {
+        prof_stamp(c, op0, 0);
+        int r0, r1;
+        cta_rows(attn ? S::ATT_IN : S::GDN_IN, 1, c.cta, c.grid, r0, r1);
+        scale_prefetch(c, L.s_in, r0, r1, false);
+        // the norm weights are requested before the wait so that their latency hides behind it
+        const float2 nw = *reinterpret_cast<const float2*>(L.in_norm + 2 * c.tid);
+        if (!x_in_regs) {
+            const u64* ptrs[T];
+            uint32_t eps[T];
+            float v[2 * T];
+#pragma unroll
+            for (int j = 0; j < T; j++) { ptrs[j] = xbuf + (size_t)j * S::HID + 2 * c.tid; eps[j] = eA - 1; }
+            ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
+#pragma unroll
+            for (int j = 0; j < T; j++) { x[j][0] = v[2 * j]; x[j][1] = v[2 * j + 1]; }
+        }
+        stage_rmsnorm<S, Q8, T>(c, x, nw, y);
+        prof_stamp(c, op0, 1);
+        gemv_mma<Q8, T, false>(c, r0, r1, S::HID * WB, L.s_in, [&](int, int row, int tk, float v, bool ok) {
+            if (ok) ll_store(P.projl + (size_t)tk * S::PROJ_MAX + row, eA, v);
+        });
+        prof_stamp(c, op0, 3);
+    }
+    // ---- B: mixer
+    prof_stamp(c, op0 + 1, 0);
+    const bool had_task = attn ? attn_op<S, KVF32, T>(c, P, L, pos, eA, eB, op0 + 1)
+                               : gdn_op<S, T>(c, P, L, pos, eA, eB, op0 + 1, from_bak);
+    prof_stamp(c, op0 + 1, 3);
+    // ---- C: out-projection + residual
+    {
+        const int op = op0 + 2;
+        prof_stamp(c, op, 0);
+        scale_prefetch(c, L.s_out, xr0, xr1, false);
+        if (!had_task) gate_on_samples(c, P.mixl + (size_t)(T - 1) * S::MIX, S::MIX, eB);
+        // each thread stages 4 consecutive mixer outputs; a warp covers 128 = one DeltaNet head
+        const int k = 4 * c.tid;
+        float m[T][4];
+        const float4 gw = attn ? make_float4(0.f, 0.f, 0.f, 0.f)
+                               : *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
+        {
+            const u64* ptrs[4 * T];
+            uint32_t eps[4 * T];
+            float v[8 * T];
+#pragma unroll
+            for (int j = 0; j < T; j++) {
+                const u64* pj = P.projl + (size_t)j * S::PROJ_MAX;
+                const u64* aux = attn ? pj + (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD)   // sigmoid gate
+                                      : pj + S::Z_OFF + k;                                    // z
+                ptrs[4 * j] = P.mixl + (size_t)j * S::MIX + k;
+                ptrs[4 * j + 1] = ptrs[4 * j] + 2;
+                ptrs[4 * j + 2] = aux;
+                ptrs[4 * j + 3] = aux + 2;
+                eps[4 * j] = eps[4 * j + 1] = eB;
+                eps[4 * j + 2] = eps[4 * j + 3] = eA;
+            }
+            ll_wait_pairs<4 * T>(c, ptrs, eps, v, W_MIX);
+#pragma unroll
+            for (int j = 0; j < T; j++) {
+                const float* vj = v + 8 * j;
+                if (attn) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) m[j][i] = vj[i] * sigmoid_f(vj[4 + i]);
+                } else {
+                    const float ss = warp_sum(vj[0] * vj[0] + vj[1] * vj[1] + vj[2] * vj[2] + vj[3] * vj[3]);
+                    const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
+                    m[j][0] = vj[0] * inv * gw.x * silu_f(vj[4]);
+                    m[j][1] = vj[1] * inv * gw.y * silu_f(vj[5]);
+                    m[j][2] = vj[2] * inv * gw.z * silu_f(vj[6]);
+                    m[j][3] = vj[3] * inv * gw.w * silu_f(vj[7]);
+                }
+            }
+        }
+        float mx[T], scale[T];
+#pragma unroll
+        for (int j = 0; j < T; j++) mx[j] = fmaxf(fmaxf(fabsf(m[j][0]), fabsf(m[j][1])), fmaxf(fabsf(m[j][2]), fabsf(m[j][3])));
+        block_scale<Q8, T>(c, mx, scale);
+#pragma unroll
+        for (int j = 0; j < T; j++) {
+            uint8_t* xq = c.sm.xq + (size_t)(4 * j) * (S::MIX * WB);
+            stage_pair<Q8>(xq, S::MIX * WB, k, m[j][0], m[j][1], scale[j]);
+            stage_pair<Q8>(xq, S::MIX * WB, k + 2, m[j][2], m[j][3], scale[j]);
+        }
+        finish_stage<T>(c, scale);
+        prof_stamp(c, op, 1);
+        gemv_mma<Q8, T, false>(c, xr0, xr1, S::MIX * WB, L.s_out, [&](int, int row, int tk, float v, bool ok) {
+            if (ok) {
+                const float xn = c.sm.xown[tk * 16 + row - xr0] + v;
+                c.sm.xown[tk * 16 + row - xr0] = xn;
+                ll_store(xbuf + (size_t)tk * S::HID + row, eC, xn);
+            }
+        });
+        prof_stamp(c, op, 3);
+    }
+    // ---- D: gate/up + SwiGLU
+    {
+        const int op = op0 + 3;
+        prof_stamp(c, op, 0);
+        int r0, r1;
+        cta_rows(2 * S::INTER, 2, c.cta, c.grid, r0, r1);
+        scale_prefetch(c, L.s_gu, r0, r1, false);
+        const float2 nw = *reinterpret_cast<const float2*>(L.post_norm + 2 * c.tid);
+        {
+            const u64* ptrs[T];
+            uint32_t eps[T];
+            float v[2 * T];
+#pragma unroll
+            for (int j = 0; j < T; j++) { ptrs[j] = xbuf + (size_t)j * S::HID + 2 * c.tid; eps[j] = eC; }
+            ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
+#pragma unroll
+            for (int j = 0; j < T; j++) { x[j][0] = v[2 * j]; x[j][1] = v[2 * j + 1]; }
+        }
+        stage_rmsnorm<S, Q8, T>(c, x, nw, y);
+        prof_stamp(c, op, 1);
+        gemv_mma<Q8, T, false>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, int tk, float v, bool ok) {
+            // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane
+            const float up = __shfl_down_sync(0xffffffffu, v, 1);
+            if (ok && !(lane & 1)) ll_store(P.actl + (size_t)tk * S::INTER + (row >> 1), eD, silu_f(v) * up);
+        });
+        prof_stamp(c, op, 3);
+    }
+    // ---- E: down-projection + residual
+    bool failed;
+    {
+        const int op = op0 + 4;
+        prof_stamp(c, op, 0);
+        scale_prefetch(c, L.s_down, xr0, xr1, false);
+        float a[T][8];
+        float mx[T], scale[T];
+        {
+            const u64* ptrs[4 * T];
+            uint32_t eps[4 * T];
+            float v[8 * T];
+#pragma unroll
+            for (int j = 0; j < T; j++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int k = 2 * c.tid + i * 2 * NCT;
+                    ptrs[4 * j + i] = k < S::INTER ? P.actl + (size_t)j * S::INTER + k : nullptr;
+                    eps[4 * j + i] = eD;
+                }
+            ll_wait_pairs<4 * T>(c, ptrs, eps, v, W_ACT);
+#pragma unroll
+            for (int j = 0; j < T; j++) {
+                mx[j] = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    a[j][i] = v[8 * j + i];
+                    mx[j] = fmaxf(mx[j], fabsf(a[j][i]));
+                }
+            }
+        }
+        block_scale<Q8, T>(c, mx, scale);
+#pragma unroll
+        for (int j = 0; j < T; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int k = 2 * c.tid + i * 2 * NCT;
+                if (k < S::INTER)
+                    stage_pair<Q8>(c.sm.xq + (size_t)(4 * j) * (S::INTER * WB), S::INTER * WB, k, a[j][2 * i], a[j][2 * i + 1], scale[j]);
+            }
+        finish_stage<T>(c, scale);
+        prof_stamp(c, op, 1);
+        gemv_mma<Q8, T, false>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, int tk, float v, bool ok) {
+            if (ok) {
+                const float xn = c.sm.xown[tk * 16 + row - xr0] + v;
+                c.sm.xown[tk * 16 + row - xr0] = xn;
+                ll_store(xbuf + (size_t)tk * S::HID + row, eE, xn);
+                if (resid_out) resid_out[(size_t)tk * S::HID + row] = xn;
+            }
+        });
+        prof_stamp(c, op, 3);
+        failed = consumer_any(c.dead);
+    }
+    return failed;
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------
 __constant__ Params c_params[2 * MAX_ENGINES];   // per engine handle: its block, and the variant with built-in scratch
 
-template <class S, bool Q8, bool KVF32>
+template <class S, bool Q8, bool KVF32, int T>
 __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, const __grid_constant__ Args A) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
+    constexpr int NS = Geo<T>::NS;
     const Params& P = c_params[pslot];
     Ctx c;
     {
         uint8_t* p = smem_raw;
-        c.sm.ring = p; p += SMEM_RING;
-        c.sm.xq = p; p += SMEM_XQ;
-        c.sm.part_s = reinterpret_cast<float*>(p); p += 2 * NCW * 32 * 4;          // 4096
+        c.sm.ring = p; p += Geo<T>::RING;
+        c.sm.xq = p; p += Geo<T>::XQ;
+        c.sm.part_s = reinterpret_cast<float*>(p); p += Geo<T>::PART;
         c.sm.bt_s = reinterpret_cast<int*>(p); p += MAX_BLOCKS * 4;                // 2048
         c.sm.scale_s = reinterpret_cast<float*>(p); p += (2 * SCALE_BODY + SCALE_RING) * 4;   // 2048
-        c.sm.out_s = reinterpret_cast<float*>(p); p += 64;
-        c.sm.red_s = reinterpret_cast<float*>(p); p += 2 * 2 * NCW * 4;            // 256
-        c.sm.xown = reinterpret_cast<float*>(p); p += 16 * 4;                      // 64
+        c.sm.out_s = reinterpret_cast<float*>(p); p += 64;                         // [T][8] attention statistics
+        c.sm.red_s = reinterpret_cast<float*>(p); p += 2 * 8 * NCW * 4;            // 1024
+        c.sm.xown = reinterpret_cast<float*>(p); p += 2 * 16 * 4;                  // 128
         c.sm.best_s = reinterpret_cast<u64*>(p); p += NCW * 8;                     // 128
-        c.sm.full = reinterpret_cast<uint64_t*>(p); p += NSTAGE * 8;
-        c.sm.empty = reinterpret_cast<uint64_t*>(p); p += NSTAGE * 8;
+        c.sm.full = reinterpret_cast<uint64_t*>(p); p += 6 * 8;
+        c.sm.empty = reinterpret_cast<uint64_t*>(p); p += 6 * 8;
         c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
@@ -1017,13 +1315,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
     if (c.tid == 0) {
-        for (int i = 0; i < NSTAGE; i++) {
+        for (int i = 0; i < NS; i++) {
             mbar_init(&c.sm.full[i], 1);
             mbar_init(&c.sm.empty[i], NCW);
         }
         *c.sm.abort_flag = 0;
         *c.sm.quit_flag = 0;
-        *c.sm.xscale_s = 1.0f;
+        c.sm.xscale_s[0] = c.sm.xscale_s[1] = 1.0f;
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -1031,27 +1329,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
     __syncthreads();
 
     if (c.warp == NCW) {
-        if (c.lane == 0) producer_main<S, Q8>(c, P, A);
+        if (c.lane == 0) producer_main<S, Q8, T>(c, P, A);
         return;
     }
 
     // ---------------- consumers ----------------
     constexpr int WB = Q8 ? 1 : 2;                       // bytes per weight
-    const int OPS = P.n_layers * OPS_PER_LAYER + 1;     // epochs per step
+    const int NL5 = P.n_layers * OPS_PER_LAYER;
     int xr0, xr1;                                        // residual rows this CTA owns
     cta_rows(S::HID, 1, c.cta, c.grid, xr0, xr1);
     int lr0, lr1;                                        // LM-head rows this CTA owns
     cta_rows(P.vocab, 1, c.cta, c.grid, lr0, lr1);
-    int steps_done = 0;
-    bool stopped = false;
-    u64 last_key = 0;
 
-    // Reduce every CTA's LM-head winner of the step whose LM epoch is `e`.
-    auto reduce_token = [&](uint32_t e) -> u64 {
+    // Reduce every CTA's winner stored in `slot` ([grid][2] words) at epoch `e`.
+    auto reduce_key = [&](const u64* slot, uint32_t e) -> u64 {
         u64 key = 0;
         for (int i = c.tid; i < c.grid; i += NCT) {
-            const float hi = ll_wait(c, P.lml + 2 * i, e, W_LM);
-            const float lo = ll_wait(c, P.lml + 2 * i + 1, e, W_LM);
+            const float hi = ll_wait(c, slot + 2 * i, e, W_LM);
+            const float lo = ll_wait(c, slot + 2 * i + 1, e, W_LM);
             const u64 k = ((u64)__float_as_uint(hi) << 32) | __float_as_uint(lo);
             key = k > key ? k : key;
         }
@@ -1061,217 +1356,264 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         u64 best = 0;
 #pragma unroll
         for (int i = 0; i < NCW; i++) best = c.sm.best_s[i] > best ? c.sm.best_s[i] : best;
-        consumer_sync();   // best_s is reused by the next LM head
+        consumer_sync();   // best_s is reused by the next reduction
         return best;
     };
-
-    for (int s = 0; s < A.n_steps; s++) {
-        const uint32_t e0 = A.epoch_base + (uint32_t)s * (uint32_t)OPS;   // epoch of layer 0's op A
-        const int pos = A.start_pos + s;
-        c.prof = (A.prof && s == A.prof_step) ? A.prof + (size_t)c.cta * PROF_MAX_OPS * PROF_FIELDS : nullptr;
-        if (c.cta == 0 && c.tid == 0 && A.step_ts) A.step_ts[s] = globaltimer();
-        int token;
-        if (s < A.n_forced) {
-            token = A.forced[s];
-        } else {
-            last_key = reduce_token(e0 - 1);             // previous step's LM-head epoch
-            token = key_index(last_key);
-            if (c.cta == 0 && c.tid == 0) A.tokens_out[s - 1] = last_key;
-            bool is_stop = false;
-            for (int i = 0; i < A.n_stop; i++) is_stop |= (A.stop_ids[i] == token);
-            if (is_stop) {
-                stopped = true;
-                break;
+    auto is_stop = [&](int token) {
+        bool st = false;
+        for (int i = 0; i < A.n_stop; i++) st |= (A.stop_ids[i] == token);
+        return st;
+    };
+    // Embedding of `token` into this thread's residual elements and the owned master copy of token slot j.
+    auto embed = [&](int token, int j, float (&xj)[2]) {
+        if (token < 0 || token >= P.vocab) token = 0;    // only reachable after a failed wait
+        load_embedding<S, Q8>(P, token, c.tid, xj[0], xj[1]);
+        if (2 * c.tid >= xr0 && 2 * c.tid < xr1) c.sm.xown[j * 16 + 2 * c.tid - xr0] = xj[0];
+        if (2 * c.tid + 1 >= xr0 && 2 * c.tid + 1 < xr1) c.sm.xown[j * 16 + 2 * c.tid + 1 - xr0] = xj[1];
+    };
+    // LM head over this CTA's vocabulary rows for T tokens: final RMSNorm, GEMV, optional logits dump,
+    // per-CTA best key per token published at epoch eL.  `hn` returns the normalised hidden state.
+    auto lm_head = [&](uint32_t eL, int op, int pos, float* logits, float (&x)[T][2], float (&hn)[T][2]) -> bool {
+        prof_stamp(c, op, 0);
+        scale_prefetch(c, P.lm_scale, lr0, lr1, true);
+        const float2 nw = *reinterpret_cast<const float2*>(P.final_norm + 2 * c.tid);
+        {
+            const u64* ptrs[T];
+            uint32_t eps[T];
+            float v[2 * T];
+#pragma unroll
+            for (int j = 0; j < T; j++) { ptrs[j] = P.xl + (size_t)j * S::HID + 2 * c.tid; eps[j] = eL - 1; }
+            ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
+#pragma unroll
+            for (int j = 0; j < T; j++) { x[j][0] = v[2 * j]; x[j][1] = v[2 * j + 1]; }
+        }
+        stage_rmsnorm<S, Q8, T>(c, x, nw, hn);
+        prof_stamp(c, op, 1);
+        u64 best = 0;                                    // warp j tracks token j
+        const float invT = A.inv_temperature;
+        gemv_mma<Q8, T, true>(c, lr0, lr1, S::HID * WB, P.lm_scale, [&](int, int row, int tk, float v, bool ok) {
+            if (!ok) return;
+            if (logits) logits[(size_t)tk * P.vocab + row] = v;
+            float score = v;
+            if (invT != 0.f) {
+                const uint32_t hsh = mk_mix32(A.seed, (uint32_t)(pos + tk), (uint32_t)row);
+                const float u = ((float)(hsh >> 8) + 0.5f) * (1.0f / 16777216.0f);
+                score = v * invT - __logf(-__logf(u));
+            }
+            const u64 key = score_key(score, row);
+            best = key > best ? key : best;
+        });
+        if (c.warp < T) {
+            best = warp_max_u64(best);
+            if (c.lane == 0) {
+                u64* slot = P.lml + ((size_t)c.warp * c.grid + c.cta) * 2;
+                ll_store_bits(slot, eL, (uint32_t)(best >> 32));
+                ll_store_bits(slot + 1, eL, (uint32_t)best);
             }
         }
-        if (token < 0 || token >= P.vocab) token = 0;    // only reachable after a failed wait
+        prof_stamp(c, op, 3);
+        return consumer_any(c.dead);
+    };
 
-        float x0, x1;                                    // residual elements 2*tid, 2*tid+1
-        load_embedding<S, Q8>(P, token, c.tid, x0, x1);
-        if (2 * c.tid >= xr0 && 2 * c.tid < xr1) c.sm.xown[2 * c.tid - xr0] = x0;
-        if (2 * c.tid + 1 >= xr0 && 2 * c.tid + 1 < xr1) c.sm.xown[2 * c.tid + 1 - xr0] = x1;
-
-        bool failed = false;
-        for (int l = 0; l < P.n_layers; l++) {
-            const LayerP& L = P.layer[l];
-            const uint32_t eA = e0 + l * OPS_PER_LAYER, eB = eA + 1, eC = eA + 2, eD = eA + 3, eE = eA + 4;
-            const bool attn = L.kind != 0;
-            const int op0 = l * OPS_PER_LAYER;
-            // ---- A: in-projection
-            {
-                prof_stamp(c, op0, 0);
-                int r0, r1;
-                cta_rows(attn ? S::ATT_IN : S::GDN_IN, 1, c.cta, c.grid, r0, r1);
-                scale_prefetch(c, L.s_in, r0, r1, false);
-                // the norm weights are requested before the wait so that their latency hides behind it
-                const float2 nw = *reinterpret_cast<const float2*>(L.in_norm + 2 * c.tid);
-                if (l > 0) ll_wait2(c, P.xl + 2 * c.tid, eA - 1, W_X, x0, x1);
-                stage_rmsnorm<S, Q8>(c, x0, x1, nw);
-                prof_stamp(c, op0, 1);
-                gemv_mma<Q8, false>(c, r0, r1, S::HID * WB, L.s_in, [&](int, int row, float v, bool ok) {
-                    if (ok) ll_store(P.projl + row, eA, v);
-                });
-                prof_stamp(c, op0, 3);
-            }
-            // ---- B: mixer
-            prof_stamp(c, op0 + 1, 0);
-            const bool had_task = attn ? attn_op<S, KVF32>(c, P, L, pos, eA, eB, op0 + 1)
-                                       : gdn_op<S>(c, P, L, pos, eA, eB, op0 + 1);
-            prof_stamp(c, op0 + 1, 3);
-            // ---- C: out-projection + residual
-            {
-                const int op = op0 + 2;
-                prof_stamp(c, op, 0);
-                scale_prefetch(c, L.s_out, xr0, xr1, false);
-                if (!had_task) gate_on_samples(c, P.mixl, S::MIX, eB);
-                // each thread stages 4 consecutive mixer outputs; a warp covers 128 = one DeltaNet head
-                const int k = 4 * c.tid;
-                float m[4];
-                const float4 gw = attn ? make_float4(0.f, 0.f, 0.f, 0.f)
-                                       : *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
-                {
-                    const u64* aux = attn ? P.projl + (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD)   // sigmoid gate
-                                          : P.projl + S::Z_OFF + k;                                    // z
-                    const u64* const ptrs[4] = {P.mixl + k, P.mixl + k + 2, aux, aux + 2};
-                    const uint32_t eps[4] = {eB, eB, eA, eA};
-                    float v[8];
-                    ll_wait_pairs<4>(c, ptrs, eps, v, W_MIX);
-                    if (attn) {
-#pragma unroll
-                        for (int i = 0; i < 4; i++) m[i] = v[i] * sigmoid_f(v[4 + i]);
-                    } else {
-                        const float ss = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
-                        const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
-                        m[0] = v[0] * inv * gw.x * silu_f(v[4]);
-                        m[1] = v[1] * inv * gw.y * silu_f(v[5]);
-                        m[2] = v[2] * inv * gw.z * silu_f(v[6]);
-                        m[3] = v[3] * inv * gw.w * silu_f(v[7]);
-                    }
+    if constexpr (T == 1) {
+        // ---------------- plain decoding: one token per pass ----------------
+        const int OPS = NL5 + 1;                         // epochs per step
+        int steps_done = 0;
+        bool stopped = false;
+        u64 last_key = 0;
+        for (int s = 0; s < A.n_steps; s++) {
+            const uint32_t e0 = A.epoch_base + (uint32_t)s * (uint32_t)OPS;   // epoch of layer 0's op A
+            const int pos = A.start_pos + s;
+            c.prof = (A.prof && s == A.prof_step) ? A.prof + (size_t)c.cta * PROF_MAX_OPS * PROF_FIELDS : nullptr;
+            if (c.cta == 0 && c.tid == 0 && A.step_ts) A.step_ts[s] = globaltimer();
+            int token;
+            if (s < A.n_forced) {
+                token = A.forced[s];
+            } else {
+                last_key = reduce_key(P.lml, e0 - 1);        // previous step's LM-head epoch
+                token = key_index(last_key);
+                if (c.cta == 0 && c.tid == 0) A.tokens_out[s - 1] = last_key;
+                if (is_stop(token)) {
+                    stopped = true;
+                    break;
                 }
-                const float scale = block_scale<Q8>(c, fmaxf(fmaxf(fabsf(m[0]), fabsf(m[1])), fmaxf(fabsf(m[2]), fabsf(m[3]))));
-                stage_pair<Q8>(c.sm.xq, S::MIX * WB, k, m[0], m[1], scale);
-                stage_pair<Q8>(c.sm.xq, S::MIX * WB, k + 2, m[2], m[3], scale);
-                finish_stage(c, scale);
+            }
+            float x[T][2], hn[T][2];
+            embed(token, 0, x[0]);
+            bool failed = false;
+            for (int l = 0; l < P.n_layers && !failed; l++)
+                failed = run_layer<S, Q8, KVF32, T>(c, P, P.layer[l], P.xl, e0 + l * OPS_PER_LAYER, l * OPS_PER_LAYER, pos, x,
+                                                    l == 0, false, xr0, xr1,
+                                                    (A.resid_out && l == P.n_layers - 1) ? A.resid_out + (size_t)s * S::HID : nullptr);
+            if (failed) break;
+            if (s >= A.lm_from) {
+                float* logits = A.logits_out ? A.logits_out + (size_t)s * P.vocab : nullptr;
+                if (lm_head(e0 + (uint32_t)OPS - 1, NL5, pos, logits, x, hn)) break;
+            }
+            steps_done = s + 1;
+        }
+        // The prediction of the last step that ran (if it ran the LM head and nothing stopped us).
+        if (!stopped && steps_done == A.n_steps && A.n_steps > 0 && A.n_steps - 1 >= A.lm_from) {
+            const uint32_t eL = A.epoch_base + (uint32_t)A.n_steps * (uint32_t)OPS - 1;
+            last_key = reduce_key(P.lml, eL);
+            if (c.cta == 0 && c.tid == 0) A.tokens_out[A.n_steps - 1] = last_key;
+        }
+        if (c.tid == 0) *c.sm.quit_flag = 1;
+        if (c.cta == 0 && c.tid == 0) {
+            if (A.step_ts) A.step_ts[steps_done] = globaltimer();
+            A.out_info[0] = steps_done;
+            A.out_info[1] = (int)(A.epoch_base + (uint32_t)steps_done * (uint32_t)OPS);
+            A.out_info[2] = A.start_pos + steps_done;
+        }
+    } else {
+        // ---------------- speculative cycles: the pending token and a draft per pass ----------------
+        // A cycle verifies [pending, draft] in one pass, emits the model's token after `pending` and,
+        // if that token equals the draft, also the token after the draft.  The draft head then runs on
+        // both positions (its own KV cache needs every position) and proposes the next draft from the
+        // last accepted position.  Epochs per cycle: layers, LM head, fusion projection, draft layer
+        // (5 ops), draft vocabulary head.
+        const int OPSC = NL5 + 1 + 1 + OPS_PER_LAYER + 1;
+        int pos = A.start_pos, emitted = 0, cyc = 0;
+        int next_tok = A.first_tok, draft = A.first_draft;
+        bool from_bak = false, done = false, failed = false;
+        u64* draft_slot = P.lml + (size_t)T * c.grid * 2;
+        for (;; cyc++) {
+            const uint32_t e0 = A.epoch_base + (uint32_t)cyc * (uint32_t)OPSC;
+            c.prof = (A.prof && cyc == A.prof_step) ? A.prof + (size_t)c.cta * PROF_MAX_OPS * PROF_FIELDS : nullptr;
+            if (cyc > 0) {          // the previous cycle's draft
+                const int row = key_index(reduce_key(draft_slot, e0 - 1));
+                draft = (P.draft_ids && row >= 0 && row < P.draft_vocab) ? P.draft_ids[row] : row;
+                if (done || failed || cyc == A.n_steps) break;
+            } else if (A.n_steps == 0) {
+                break;
+            }
+            if (c.cta == 0 && c.tid == 0 && A.step_ts) A.step_ts[cyc] = globaltimer();
+            const int tok[2] = {next_tok, draft};
+            float x[T][2], hn[T][2];
+#pragma unroll
+            for (int j = 0; j < T; j++) embed(tok[j], j, x[j]);
+            for (int l = 0; l < P.n_layers && !failed; l++)
+                failed = run_layer<S, Q8, KVF32, T>(c, P, P.layer[l], P.xl, e0 + l * OPS_PER_LAYER, l * OPS_PER_LAYER, pos, x,
+                                                    l == 0, from_bak, xr0, xr1, nullptr);
+            if (failed) { cyc++; break; }
+            const uint32_t eL = e0 + NL5;
+            float* logits = A.logits_out ? A.logits_out + (size_t)cyc * T * P.vocab : nullptr;
+            if (lm_head(eL, NL5, pos, logits, x, hn)) { failed = true; cyc++; break; }
+            // verify
+            int yv[2];
+            yv[0] = key_index(reduce_key(P.lml, eL));
+            yv[1] = key_index(reduce_key(P.lml + (size_t)c.grid * 2, eL));
+            const bool stop0 = is_stop(yv[0]);
+            const int n_new = (yv[0] == tok[1] && !stop0 && emitted + 2 <= A.limit) ? 2 : 1;
+            if (c.cta == 0 && c.tid == 0) {
+                A.spec_out[emitted] = yv[0];
+                if (n_new == 2) A.spec_out[emitted + 1] = yv[1];
+                if (A.cycle_out) { A.cycle_out[2 * cyc] = n_new; A.cycle_out[2 * cyc + 1] = tok[1]; }
+            }
+            emitted += n_new;
+            done = stop0 || (n_new == 2 && is_stop(yv[1])) || emitted >= A.limit;
+            next_tok = yv[n_new - 1];
+            from_bak = n_new == 1;
+
+            // ---- draft head, op 1: u_j = fc([norm_e(embed(y_j)) | norm_h(h_j)])
+            const uint32_t eF = eL + 1;
+            {
+                const int op = NL5 + 1;
+                prof_stamp(c, op, 0);
+                scale_prefetch(c, P.mtp_fc_scale, xr0, xr1, false);
+                const float2 we = *reinterpret_cast<const float2*>(P.mtp_norm_e + 2 * c.tid);
+                const float2 wh = *reinterpret_cast<const float2*>(P.mtp_norm_h + 2 * c.tid);
+                float ev[T][2], ye[T][2], yh[T][2];
+                float ss[2 * T], mx[2 * T];
+#pragma unroll
+                for (int j = 0; j < T; j++) {
+                    int t2 = yv[j];
+                    if (t2 < 0 || t2 >= P.vocab) t2 = 0;
+                    load_embedding<S, Q8>(P, t2, c.tid, ev[j][0], ev[j][1]);
+                    ye[j][0] = ev[j][0] * (1.0f + we.x); ye[j][1] = ev[j][1] * (1.0f + we.y);
+                    yh[j][0] = hn[j][0] * (1.0f + wh.x); yh[j][1] = hn[j][1] * (1.0f + wh.y);
+                    ss[2 * j] = ev[j][0] * ev[j][0] + ev[j][1] * ev[j][1];
+                    ss[2 * j + 1] = hn[j][0] * hn[j][0] + hn[j][1] * hn[j][1];
+                    mx[2 * j] = fmaxf(fabsf(ye[j][0]), fabsf(ye[j][1]));
+                    mx[2 * j + 1] = fmaxf(fabsf(yh[j][0]), fabsf(yh[j][1]));
+                }
+                consumer_sum_max<2 * T>(c, ss, mx);
+                constexpr int RB = 2 * S::HID * WB;
+#pragma unroll
+                for (int j = 0; j < T; j++) {
+                    const float inv_e = rsqrtf(ss[2 * j] * (1.0f / S::HID) + S::EPS);
+                    const float inv_h = rsqrtf(ss[2 * j + 1] * (1.0f / S::HID) + S::EPS);
+                    const float scale = Q8 ? fixed_scale(fmaxf(mx[2 * j] * inv_e, mx[2 * j + 1] * inv_h)) : 1.0f;
+                    uint8_t* xq = c.sm.xq + (size_t)(4 * j) * RB;
+                    stage_pair<Q8>(xq, RB, 2 * c.tid, ye[j][0] * inv_e, ye[j][1] * inv_e, scale);
+                    stage_pair<Q8>(xq, RB, S::HID + 2 * c.tid, yh[j][0] * inv_h, yh[j][1] * inv_h, scale);
+                    if (c.tid == 0) c.sm.xscale_s[j] = 1.0f / scale;
+                }
+                consumer_sync();
                 prof_stamp(c, op, 1);
-                gemv_mma<Q8, false>(c, xr0, xr1, S::MIX * WB, L.s_out, [&](int, int row, float v, bool ok) {
+                gemv_mma<Q8, T, false>(c, xr0, xr1, RB, P.mtp_fc_scale, [&](int, int row, int tk, float v, bool ok) {
                     if (ok) {
-                        const float xn = c.sm.xown[row - xr0] + v;
-                        c.sm.xown[row - xr0] = xn;
-                        ll_store(P.xl + row, eC, xn);
+                        c.sm.xown[tk * 16 + row - xr0] = v;
+                        ll_store(P.xml + (size_t)tk * S::HID + row, eF, v);
                     }
                 });
                 prof_stamp(c, op, 3);
             }
-            // ---- D: gate/up + SwiGLU
+            // ---- draft head, ops 2..6: its decoder layer on positions pos, pos + 1 (own KV cache)
+            failed = run_layer<S, Q8, KVF32, T>(c, P, P.mtp, P.xml, eF + 1, NL5 + 2, pos, x, false, false, xr0, xr1, nullptr);
+            if (failed) { cyc++; break; }
+            // ---- draft head, op 7: greedy choice over the draft vocabulary at the last accepted position
             {
-                const int op = op0 + 3;
+                const uint32_t eV = eF + 1 + OPS_PER_LAYER;
+                const int op = NL5 + 2 + OPS_PER_LAYER;
                 prof_stamp(c, op, 0);
-                int r0, r1;
-                cta_rows(2 * S::INTER, 2, c.cta, c.grid, r0, r1);
-                scale_prefetch(c, L.s_gu, r0, r1, false);
-                const float2 nw = *reinterpret_cast<const float2*>(L.post_norm + 2 * c.tid);
-                ll_wait2(c, P.xl + 2 * c.tid, eC, W_X, x0, x1);
-                stage_rmsnorm<S, Q8>(c, x0, x1, nw);
-                prof_stamp(c, op, 1);
-                gemv_mma<Q8, false>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, float v, bool ok) {
-                    // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane
-                    const float up = __shfl_down_sync(0xffffffffu, v, 1);
-                    if (ok && !(lane & 1)) ll_store(P.actl + (row >> 1), eD, silu_f(v) * up);
-                });
-                prof_stamp(c, op, 3);
-            }
-            // ---- E: down-projection + residual
-            {
-                const int op = op0 + 4;
-                prof_stamp(c, op, 0);
-                scale_prefetch(c, L.s_down, xr0, xr1, false);
-                float a[8];
-                float mx = 0.f;
+                int dr0, dr1;
+                cta_rows(P.draft_vocab, 1, c.cta, c.grid, dr0, dr1);
+                scale_prefetch(c, P.draft_scale, dr0, dr1, true);
+                const float2 nw = *reinterpret_cast<const float2*>(P.mtp_norm + 2 * c.tid);
+                float u[T][2], un[T][2];
                 {
-                    const u64* ptrs[4];
-                    const uint32_t eps[4] = {eD, eD, eD, eD};
+                    const u64* ptrs[T];
+                    uint32_t eps[T];
+                    float v[2 * T];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const int k = 2 * c.tid + j * 2 * NCT;
-                        ptrs[j] = k < S::INTER ? P.actl + k : nullptr;
-                    }
-                    ll_wait_pairs<4>(c, ptrs, eps, a, W_ACT);
+                    for (int j = 0; j < T; j++) { ptrs[j] = P.xml + (size_t)j * S::HID + 2 * c.tid; eps[j] = eV - 1; }
+                    ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) mx = fmaxf(mx, fabsf(a[j]));
+                    for (int j = 0; j < T; j++) { u[j][0] = v[2 * j]; u[j][1] = v[2 * j + 1]; }
                 }
-                const float scale = block_scale<Q8>(c, mx);
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int k = 2 * c.tid + j * 2 * NCT;
-                    if (k < S::INTER) stage_pair<Q8>(c.sm.xq, S::INTER * WB, k, a[2 * j], a[2 * j + 1], scale);
-                }
-                finish_stage(c, scale);
+                stage_rmsnorm<S, Q8, T>(c, u, nw, un);
                 prof_stamp(c, op, 1);
-                const bool last = l == P.n_layers - 1;
-                gemv_mma<Q8, false>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, float v, bool ok) {
-                    if (ok) {
-                        const float xn = c.sm.xown[row - xr0] + v;
-                        c.sm.xown[row - xr0] = xn;
-                        ll_store(P.xl + row, eE, xn);
-                        if (A.resid_out && last) A.resid_out[(size_t)s * S::HID + row] = xn;
-                    }
+                u64 best = 0;
+                const int want = n_new - 1;              // token slot whose draft counts
+                gemv_mma<Q8, T, true>(c, dr0, dr1, S::HID * WB, P.draft_scale, [&](int, int row, int tk, float v, bool ok) {
+                    if (!ok || tk != want) return;
+                    const u64 key = score_key(v, row);
+                    best = key > best ? key : best;
                 });
+                if (c.warp < T) {
+                    best = warp_max_u64(best);
+                    if (c.warp == want && c.lane == 0) {
+                        ll_store_bits(draft_slot + 2 * c.cta, eV, (uint32_t)(best >> 32));
+                        ll_store_bits(draft_slot + 2 * c.cta + 1, eV, (uint32_t)best);
+                    }
+                }
                 prof_stamp(c, op, 3);
                 failed = consumer_any(c.dead);
             }
-            if (failed) break;
+            pos += n_new;
         }
-        if (failed) break;
-        // ---- LM head
-        if (s >= A.lm_from) {
-            const uint32_t eL = e0 + (uint32_t)OPS - 1;
-            const int op = P.n_layers * OPS_PER_LAYER;
-            prof_stamp(c, op, 0);
-            scale_prefetch(c, P.lm_scale, lr0, lr1, true);
-            const float2 nw = *reinterpret_cast<const float2*>(P.final_norm + 2 * c.tid);
-            ll_wait2(c, P.xl + 2 * c.tid, eL - 1, W_X, x0, x1);
-            stage_rmsnorm<S, Q8>(c, x0, x1, nw);
-            prof_stamp(c, op, 1);
-            u64 best = 0;
-            float* logits = A.logits_out ? A.logits_out + (size_t)s * P.vocab : nullptr;
-            const float invT = A.inv_temperature;
-            gemv_mma<Q8, true>(c, lr0, lr1, S::HID * WB, P.lm_scale, [&](int, int row, float v, bool ok) {
-                if (!ok) return;
-                if (logits) logits[row] = v;
-                float score = v;
-                if (invT != 0.f) {
-                    const uint32_t hsh = mk_mix32(A.seed, (uint32_t)pos, (uint32_t)row);
-                    const float u = ((float)(hsh >> 8) + 0.5f) * (1.0f / 16777216.0f);
-                    score = v * invT - __logf(-__logf(u));
-                }
-                const u64 key = score_key(score, row);
-                best = key > best ? key : best;
-            });
-            if (c.warp == 0) {
-                best = warp_max_u64(best);
-                if (c.lane == 0) {
-                    ll_store_bits(P.lml + 2 * c.cta, eL, (uint32_t)(best >> 32));
-                    ll_store_bits(P.lml + 2 * c.cta + 1, eL, (uint32_t)best);
-                }
-            }
-            prof_stamp(c, op, 3);
-            failed = consumer_any(c.dead);
-            if (failed) break;
+        if (c.tid == 0) *c.sm.quit_flag = 1;
+        if (from_bak && !failed) gdn_restore_state<S>(c, P);
+        if (c.cta == 0 && c.tid == 0) {
+            if (A.step_ts) A.step_ts[cyc] = globaltimer();
+            A.out_info[0] = emitted;
+            A.out_info[1] = (int)(A.epoch_base + (uint32_t)cyc * (uint32_t)OPSC);
+            A.out_info[2] = pos;
+            A.out_info[3] = next_tok;
+            A.out_info[4] = draft;
+            A.out_info[5] = cyc;
         }
-        steps_done = s + 1;
-    }
-    // The prediction of the last step that ran (if it ran the LM head and nothing stopped us).
-    if (!stopped && steps_done == A.n_steps && A.n_steps > 0 && A.n_steps - 1 >= A.lm_from) {
-        const uint32_t eL = A.epoch_base + (uint32_t)A.n_steps * (uint32_t)OPS - 1;
-        last_key = reduce_token(eL);
-        if (c.cta == 0 && c.tid == 0) A.tokens_out[A.n_steps - 1] = last_key;
-    }
-    if (c.tid == 0) *c.sm.quit_flag = 1;
-    if (c.cta == 0 && c.tid == 0) {
-        if (A.step_ts) A.step_ts[steps_done] = globaltimer();
-        A.out_info[0] = steps_done;
-        A.out_info[1] = (int)(A.epoch_base + (uint32_t)steps_done * (uint32_t)OPS);
-        A.out_info[2] = A.start_pos + steps_done;
     }
 }
 

@@ -21,9 +21,10 @@ import os
 import torch
 
 from . import _lib
+from . import mtp as mtp_mod
 from .config import Config
 from .pack import as_bytes, pack_rows
-from .quant import quantize_int8_rows
+from .quant import is_gemv_weight, quantize_int8_rows, roundtrip_int8_rows
 
 # Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
 # of the per-launch output buffers.
@@ -41,13 +42,13 @@ def rope_tables(cfg, max_seq, device):
 
 class Megakernel:
     def __init__(self, model, max_seq=8192, device="cuda", pf_bytes=PF_BYTES, quant="bf16", mtp=False,
-                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000):
+                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None):
+        """`mtp` loads the multi-token-prediction head for speculative decoding (`run_spec`); its drafts
+        come from the `draft_vocab` most frequent tokens listed in `draft_ids` (0: the whole vocabulary)."""
         if quant not in ("bf16", "int8"):
             raise ValueError(f"quant must be 'bf16' or 'int8', got {quant!r}")
         if kv_dtype not in ("bf16", "fp32"):
             raise ValueError(f"kv_dtype must be 'bf16' or 'fp32', got {kv_dtype!r}")
-        if mtp:
-            raise NotImplementedError("the MTP draft head is not part of this build yet")
         if not torch.cuda.is_available():
             raise RuntimeError("the decode megakernel needs a CUDA device; there is no CPU path")
         self.lib = _lib.load()
@@ -58,11 +59,17 @@ class Megakernel:
             device = torch.device(device.type, torch.cuda.current_device())
         torch.cuda.set_device(device)
         self.device = device
+        wm = None
         if isinstance(model, (tuple, list)):
-            self.cfg, w = model
+            self.cfg, w = model[0], model[1]
+            wm = model[2] if len(model) > 2 else None
         else:
             from . import weights as _weights
             self.cfg, w = _weights.load(model, "cpu")
+            if mtp:
+                wm = _weights.load_mtp(model, "cpu")
+        if mtp and not wm:
+            raise ValueError("mtp=True needs the MTP head's weights (a third element of `model`, or `mtp.*` tensors in the snapshot)")
         cfg = self.cfg
         assert isinstance(cfg, Config) or hasattr(cfg, "layer_types")
         self._check_shape(cfg)
@@ -107,14 +114,39 @@ class Megakernel:
         self.conv_hist, self.state, self.state_bak, self.k_cache, self.v_cache = [], [], [], [], []
         F = _lib.LAYER_FIELDS
         layer_vals = []
-        for i, kind in enumerate(cfg.layer_types):
-            m = f"layers.{i}."
+        def common(w, m):
             rec = dict.fromkeys(F, 0)
             gu = torch.stack([w[m + "mlp.gate_proj.weight"], w[m + "mlp.up_proj.weight"]], dim=1).reshape(-1, cfg.hidden)
             rec["w_gu"], rec["s_gu"] = mat(gu, unit=2)
             rec["w_down"], rec["s_down"] = mat(w[m + "mlp.down_proj.weight"])
             rec["in_norm"] = f32(w[m + "input_layernorm.weight"])
             rec["post_norm"] = f32(w[m + "post_attention_layernorm.weight"])
+            return rec
+
+        def attn_layer(w, m):
+            """Pointer record of a gated full-attention decoder layer and its (paged) KV cache."""
+            rec = common(w, m)
+            p = m + "self_attn."
+            w_in = torch.cat([w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"]])
+            rec["w_in"], rec["s_in"] = mat(w_in)
+            rec["w_out"], rec["s_out"] = mat(w[p + "o_proj.weight"])
+            rec["q_norm"] = f32(w[p + "q_norm.weight"])
+            rec["k_norm"] = f32(w[p + "k_norm.weight"])
+            kc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+            vc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+            rec["k_cache"], rec["v_cache"] = keep(kc), keep(vc)
+            rec["kind"] = 1
+            return rec, kc, vc
+
+        for i, kind in enumerate(cfg.layer_types):
+            m = f"layers.{i}."
+            if kind != "linear_attention":
+                rec, kc, vc = attn_layer(w, m)
+                self.k_cache.append(kc)
+                self.v_cache.append(vc)
+                layer_vals += [rec[f] for f in F]
+                continue
+            rec = common(w, m)
             if kind == "linear_attention":
                 p = m + "linear_attn."
                 w_in = torch.cat([w[p + "in_proj_qkv.weight"], w[p + "in_proj_z.weight"],
@@ -133,19 +165,6 @@ class Megakernel:
                 self.state_bak.append(bak)
                 rec["conv_hist"], rec["state"], rec["state_bak"] = keep(hist), keep(st), keep(bak)
                 rec["kind"] = 0
-            else:
-                p = m + "self_attn."
-                w_in = torch.cat([w[p + "q_proj.weight"], w[p + "k_proj.weight"], w[p + "v_proj.weight"]])
-                rec["w_in"], rec["s_in"] = mat(w_in)
-                rec["w_out"], rec["s_out"] = mat(w[p + "o_proj.weight"])
-                rec["q_norm"] = f32(w[p + "q_norm.weight"])
-                rec["k_norm"] = f32(w[p + "k_norm.weight"])
-                kc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
-                vc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
-                self.k_cache.append(kc)
-                self.v_cache.append(vc)
-                rec["k_cache"], rec["v_cache"] = keep(kc), keep(vc)
-                rec["kind"] = 1
             layer_vals += [rec[f] for f in F]
 
         cos, sin = rope_tables(cfg, self.max_seq, device)
@@ -153,9 +172,11 @@ class Megakernel:
         proj_max = max(cfg.gdn_in_rows, cfg.attn_in_rows)
         mix = cfg.n_heads * cfg.head_dim
         # flag-in-data activation buffers: (epoch << 32) | fp32 bits
-        self.ll = [torch.zeros(n, **u64) for n in (cfg.hidden, proj_max, mix, cfg.intermediate, 2 * self.grid)]
+        T = _lib.query("SPEC_T")   # every hand-off buffer holds a speculative cycle's two tokens
+        self.ll = [torch.zeros(n, **u64) for n in (T * cfg.hidden, T * proj_max, T * mix, T * cfg.intermediate,
+                                                   (T + 1) * 2 * self.grid, T * cfg.hidden)]
         max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
-        self.attn_part = zeros(cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
+        self.attn_part = zeros(T * cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
         self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
         self.block_table = torch.arange(n_blocks, device=device, dtype=torch.int32)
         self.status = zeros(4, dtype=torch.int32)
@@ -172,17 +193,46 @@ class Megakernel:
                  xl=keep(self.ll[0]), projl=keep(self.ll[1]), mixl=keep(self.ll[2]), actl=keep(self.ll[3]),
                  lml=keep(self.ll[4]), attn_part=keep(self.attn_part), attn_flag=keep(self.attn_flag),
                  block_table=keep(self.block_table), status=keep(self.status))
-        del w
+        g["xml"] = keep(self.ll[5])
         self.mtp = self.draft_ids = None
         self.draft_vocab = 0
+        mtp_vals = None
+        if mtp:
+            from .mtp import MTP
+            rec, mkc, mvc = attn_layer(wm, "layers.0.")
+            self.mtp_k_cache, self.mtp_v_cache = mkc, mvc
+            mtp_vals = [rec[f] for f in F]
+            g["mtp_fc"], g["mtp_fc_scale"] = mat(wm["fc.weight"])
+            g["mtp_norm_e"] = f32(wm["pre_fc_norm_embedding.weight"])
+            g["mtp_norm_h"] = f32(wm["pre_fc_norm_hidden.weight"])
+            g["mtp_norm"] = f32(wm["norm.weight"])
+            if 0 < draft_vocab < cfg.vocab:
+                if draft_ids is None:
+                    raise ValueError("a reduced draft vocabulary needs `draft_ids` (token ids, most frequent first)")
+                ranked = torch.as_tensor(draft_ids)[:draft_vocab]
+                # ascending ids, so that an argmax tie still goes to the smallest token id
+                self.draft_ids = ranked.sort().values.to(device=device, dtype=torch.int32)
+                g["draft_head"], g["draft_scale"] = mat(self.embed[self.draft_ids.long()])
+                g["draft_ids"] = keep(self.draft_ids)
+                self.draft_vocab = len(self.draft_ids)
+            else:
+                g["draft_head"], g["draft_scale"] = lm_ptr, lm_scale
+                self.draft_vocab = cfg.vocab
+            # what the kernel's arithmetic sees, for the host-side cache fill
+            seen = {k: (roundtrip_int8_rows(v.to(device)) if q8 and is_gemv_weight(k) else v.to(device).float())
+                    for k, v in wm.items()}
+            table = roundtrip_int8_rows(self.embed) if q8 else self.embed
+            self.mtp = MTP(cfg, seen, lambda t: table[t].float(), cos, sin, self._write_mtp_kv)
+        del w
 
         desc = _lib.ModelDesc(shape=_lib.MK_SHAPE_QWEN35_08B, n_layers=cfg.n_layers, vocab=cfg.vocab,
                               max_seq=self.max_seq, quant=_lib.MK_QUANT[quant], kv_dtype=_lib.MK_KV[kv_dtype],
-                              draft_vocab=0, device=device.index, grid=self.grid)
+                              draft_vocab=self.draft_vocab, device=device.index, grid=self.grid)
         self._h = ctypes.c_void_p()
         _lib.check(self.lib.mk_create(ctypes.byref(desc), ctypes.byref(self._h)))
         lv, gv = _lib.i64_array(layer_vals), _lib.i64_array([g[f] for f in _lib.GLOBAL_FIELDS])
-        _lib.check(self.lib.mk_set_params(self._h, lv, len(lv), None, 0, gv, len(gv)))
+        mv = _lib.i64_array(mtp_vals) if mtp_vals else None
+        _lib.check(self.lib.mk_set_params(self._h, lv, len(lv), mv, len(mv) if mv else 0, gv, len(gv)))
         self.weight_bytes = self._weight_bytes()
         self.last_step_ns = []
         self.launches = 0
@@ -232,6 +282,7 @@ class Megakernel:
         self.status.zero_()
         self.epoch = 1   # the buffers are zero, so epoch 0 never looks ready
         self.pos = 0
+        self.mtp_h = None   # (position, hidden state) whose draft-cache entry still awaits its next token
 
     def set_block_table(self, table):
         """Map logical KV pages to physical pages (a permutation of range(max_seq / KV_BLOCK))."""
@@ -284,6 +335,12 @@ class Megakernel:
         if int(self.status[0]) != 0:
             where = ctypes.c_int32()
             _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
+        track_mtp = track_mtp and self.mtp is not None
+        if track_mtp and done:
+            fed = (tokens + (0xFFFFFFFF - (out[n_forced - 1: done - 1] & 0xFFFFFFFF)).tolist())[:done]
+            self.mtp_fed(self.pos, mtp_mod.rmsnorm(resid[:done], self.final_norm, self.cfg.eps), fed)
+        elif done:
+            self.mtp_h = None
         self.pos += done
         self.epoch = epoch & 0xFFFFFFFF
         if self.epoch > 0xFFFF0000:
@@ -309,19 +366,102 @@ class Megakernel:
         """Feed all but the last token; returns the last one (`qwen_mk/engine.py:296-301`)."""
         tokens = list(tokens)
         for i in range(0, len(tokens) - 1, chunk):
-            self.run(tokens[i: min(i + chunk, len(tokens) - 1)])
+            self.run(tokens[i: min(i + chunk, len(tokens) - 1)], track_mtp=True)
         return tokens[-1]
+
+    # ---- draft-head cache for tokens fed outside speculative cycles (`qwen_mk/engine.py:178-196`)
+    # The entry at position i is built from (h_i, x_{i+1}), so it can only be written once the token
+    # after i is known.  Speculative cycles maintain it in the kernel; for prompt tokens it is
+    # computed on the host side in one batch.
+    def mtp_fed(self, start, hidden, tokens):
+        """Positions start .. start+n-1 were fed `tokens` and produced final hidden states `hidden`."""
+        if self.mtp is None or not len(tokens):
+            return
+        tok = torch.as_tensor(tokens, device=self.device)
+        self._mtp_close(start, tok[0])
+        if len(tok) > 1:
+            self.mtp.fill_kv(hidden[:-1], tok[1:], start)
+        self.mtp_h = (start + len(tok) - 1, hidden[-1:])
+
+    def _mtp_close(self, pos, token):
+        """Token `token` is going to position `pos`: finish the entry for pos - 1 if it is pending."""
+        if self.mtp_h is not None and self.mtp_h[0] == pos - 1:
+            self.mtp.fill_kv(self.mtp_h[1], torch.as_tensor([token], device=self.device), pos - 1)
+        self.mtp_h = None
+
+    def _write_mtp_kv(self, pos, k, v):
+        bt = self.block_table.long()
+        blk, off = bt[pos // self.KV_BLOCK], pos % self.KV_BLOCK
+        self.mtp_k_cache[blk, :, off] = k.to(self.mtp_k_cache.dtype)
+        self.mtp_v_cache[blk, :, off] = v.to(self.mtp_v_cache.dtype)
+
+    @torch.no_grad()
+    def run_spec(self, token, draft, n_generate, temperature=0.0, seed=0, stop_ids=(), timing=False,
+                 return_logits=False, prof=None, prof_step=0):
+        """Speculative decoding: `token` is pending at self.pos and `draft` guesses the one after.
+
+        One launch of up to `n_generate` cycles, each verifying the pending token plus the draft in a
+        single pass over the weights.  Returns (ids, next_draft): the emitted ids, at most `n_generate`
+        and ending early with a stop id, exactly as `run([token], n_generate)` would produce them; the
+        state has absorbed all but the last id, which is the next pending token, and `next_draft` is the
+        draft head's guess for the token after it.  Any `draft` is correct: a wrong one only costs its
+        cycle.  `self.last_cycles` lists (tokens emitted, draft) per cycle.  Same contract as the
+        reference's `run_spec` (`qwen_mk/engine.py:252-294`).
+        """
+        if self.mtp is None:
+            raise RuntimeError("construct the engine with mtp=True for speculative decoding")
+        n_cycles = min(n_generate, MAX_STEPS_PER_LAUNCH)
+        if self.pos + 2 * n_cycles + 1 > self.max_seq:
+            raise ValueError(f"sequence would exceed max_seq={self.max_seq}")
+        self._mtp_close(self.pos, token)
+        dev = self.device
+        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=dev)
+        out = torch.zeros(n_generate, dtype=torch.int32, device=dev)
+        cycles = torch.zeros(2 * n_cycles, dtype=torch.int32, device=dev)
+        info = torch.zeros(8, dtype=torch.int32, device=dev)
+        ts = torch.zeros(n_cycles + 1, dtype=torch.int64, device=dev) if timing else None
+        logits = torch.empty(n_cycles, 2, self.cfg.vocab, device=dev) if return_logits else None
+        ptr = lambda t: t.data_ptr() if t is not None else 0
+        a = _lib.LaunchArgs(forced=0, n_forced=0, n_steps=n_cycles, lm_from=0, start_pos=self.pos, epoch_base=self.epoch,
+                            seed=seed & 0xFFFFFFFF, inv_temperature=1.0 / temperature if temperature > 0 else 0.0,
+                            n_stop=len(stop_ids), stop_ids=stops.data_ptr(), tokens_out=0, logits_out=ptr(logits),
+                            step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof), prof_step=prof_step,
+                            grid=self.grid, pf_bytes=self.pf_bytes, spin_limit_ns=self.spin_limit_ns, spec=1,
+                            first_tok=int(token), first_draft=int(draft), limit=n_generate,
+                            spec_out=out.data_ptr(), cycle_out=cycles.data_ptr())
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(self.lib.mk_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+        self.launches += 1
+        emitted, epoch, pos, pending, next_draft, n_run = info[:6].tolist()
+        if int(self.status[0]) != 0:
+            where = ctypes.c_int32()
+            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
+        self.pos = pos
+        self.epoch = epoch & 0xFFFFFFFF
+        if self.epoch > 0xFFFF0000:
+            raise RuntimeError("epoch counter exhausted; call reset()")
+        self.last_cycles = cycles[: 2 * n_run].view(-1, 2).tolist()
+        if timing:
+            t = ts[: n_run + 1].cpu()
+            self.last_step_ns = (t[1:] - t[:-1]).tolist()
+        ids = out[:emitted].tolist()
+        assert ids[-1] == pending
+        if return_logits:
+            self.last_logits = logits[:n_run]
+        return ids, next_draft
 
     def generate(self, prompt_ids, max_new_tokens=256, temperature=0.0, seed=0, stop_ids=(), chunk=16, spec=False):
         """Yield generated ids (`qwen_mk/engine.py:307-327`).  The state ends exactly after the last
         fed token, so a conversation can continue by passing the next prompt."""
-        if spec:
-            raise NotImplementedError("speculative decoding needs the MTP head, which this build lacks")
         last = self.prefill(prompt_ids)
         produced = 0
+        draft = last  # any guess is valid for the first cycle; the draft head proposes every later one
         while produced < max_new_tokens:
             n = min(chunk, max_new_tokens - produced, MAX_STEPS_PER_LAUNCH)
-            ids = self.run([last], n_generate=n, temperature=temperature, seed=seed, stop_ids=stop_ids)
+            if spec:
+                ids, draft = self.run_spec(last, draft, n, temperature=temperature, seed=seed, stop_ids=stop_ids)
+            else:
+                ids = self.run([last], n_generate=n, temperature=temperature, seed=seed, stop_ids=stop_ids)
             for t in ids:
                 yield t
                 produced += 1
