@@ -118,7 +118,8 @@ typedef struct mk_launch_args {
     int32_t grid;            /* CTAs; 0 = one per SM                                           */
     int64_t pf_bytes;        /* L2 prefetch distance ahead of the shared-memory ring, per CTA  */
     int64_t spin_limit_ns;   /* bound on every device-side wait; 0 = library default (2 s)    */
-    /* speculative cycles (n_steps counts cycles) */
+    /* speculative cycles (spec = 1; n_steps counts cycles, each verifies the pending token and one draft;
+     * needs the MTP record and draft-head fields of mk_set_params; qwen3.5-0.8b/csrc/megakernel.cu:1196-1276) */
     int32_t spec;
     int32_t first_tok;
     int32_t first_draft;

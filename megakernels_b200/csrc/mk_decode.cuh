@@ -1019,17 +1019,28 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         if (c.tid < 2 * S::QPK) ll_store(part + NOUT + c.tid, e_out, stat_s[tk * 8 + (c.tid & 1) * S::QPK + (c.tid >> 1)]);
     }
     // -- 7. merge this task's share of the outputs.  `tpo` threads share one output, each takes the
-    //       splits s = sub, sub + tpo, ...; a fixed shuffle tree combines them.
-    const int opc = (NOUT + nsplit - 1) / nsplit;           // outputs per task and token
-    int tpo = 1;
-    while (tpo < 32 && 2 * tpo * opc <= NCT && tpo < nsplit) tpo *= 2;
-    const int oi = c.tid / tpo, sub = c.tid % tpo;
-    const int o = sp * opc + oi;
-    const bool live = oi < opc && o < NOUT;
-    const int h = o / S::HD;
+    //       splits s = sub, sub + tpo, ...; a fixed shuffle tree combines them.  Token j is merged over
+    //       the splits a plain step at its position would have, with that step's work split, so that a
+    //       speculative cycle rounds exactly like plain decoding.
     constexpr int SPT = 4;                                   // splits per thread at most (MAX_SPLITS / 32)
 #pragma unroll
     for (int tk = 0; tk < T; tk++) {
+        const int ns_t = min(nsplit, (pos + tk + ch) / ch);          // splits that hold positions <= pos + tk
+        if (ns_t == 1) {                                             // everything this token sees is in split 0
+            if (sp == 0) {
+                u64* out = P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
+                ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
+                ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
+            }
+            continue;
+        }
+        const int opc = (NOUT + ns_t - 1) / ns_t;                   // outputs per task
+        int tpo = 1;
+        while (tpo < 32 && 2 * tpo * opc <= NCT && tpo < ns_t) tpo *= 2;
+        const int oi = c.tid / tpo, sub = c.tid % tpo;
+        const int o = sp * opc + oi;
+        const bool live = sp < ns_t && oi < opc && o < NOUT;
+        const int h = o / S::HD;
         const u64* pg = P.attn_part + ((size_t)tk * S::NKV + g) * MAX_SPLITS * S::PART_STRIDE;
         float mv[SPT], lv[SPT], av[SPT];
         {
@@ -1038,7 +1049,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             for (int i = 0; i < SPT; i++) {
                 const int s2 = sub + i * tpo;
                 wa[i] = wm[i] = wl[i] = 0;
-                if (live && s2 < nsplit) {
+                if (live && s2 < ns_t) {
                     const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
                     wa[i] = ll_load(ps + o);
                     ll_load2(ps + NOUT + 2 * h, wm[i], wl[i]);
@@ -1050,7 +1061,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
 #pragma unroll
                 for (int i = 0; i < SPT; i++) {
                     const int s2 = sub + i * tpo;
-                    if (live && s2 < nsplit) {
+                    if (live && s2 < ns_t) {
                         const u64* ps = pg + (size_t)s2 * S::PART_STRIDE;
                         if ((uint32_t)(wa[i] >> 32) != e_out) { ok = false; wa[i] = ll_load(ps + o); }
                         if ((uint32_t)(wm[i] >> 32) != e_out || (uint32_t)(wl[i] >> 32) != e_out) {
@@ -1067,7 +1078,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             }
 #pragma unroll
             for (int i = 0; i < SPT; i++) {
-                const bool have = live && sub + i * tpo < nsplit;
+                const bool have = live && sub + i * tpo < ns_t;
                 mv[i] = have ? __uint_as_float((uint32_t)wm[i]) : -INFINITY;
                 lv[i] = have ? __uint_as_float((uint32_t)wl[i]) : 0.f;
                 av[i] = have ? __uint_as_float((uint32_t)wa[i]) : 0.f;
