@@ -167,6 +167,44 @@ int mk_launch(mk_engine* e, const mk_launch_args* args, void* stream);
 #define MK_STATIC_SCRATCH_BYTES (3u << 20)
 int mk_launch_static(mk_engine* e, const mk_launch_args* args, void* stream);
 
+/* Batched decoding: up to MK_MAX_BATCH independent sequences share every pass over the weights
+ * (int8 engines only).  The reference's 0.8B kernel decodes one sequence per launch; its batched
+ * engines are the gfx942 ones, whose `Engine.step(tok[M])` (qwen3.8-27b-gfx942/mk/runner.py:202-213)
+ * takes one token per sequence and step.  Here the whole generation of all sequences is one launch,
+ * like mk_launch: step s feeds position pos0[j] + s of sequence j, first the sequence's prompt tokens
+ * (forced, n_forced[j] of them), then its own greedy or sampled choices.
+ *
+ * The engine's buffers are those of mk_set_params with every per-sequence buffer `batch` times as
+ * large, sequence-major: the hand-off words (MK_G_XL, MK_G_PROJL, MK_G_MIXL, MK_G_ACTL [batch, width],
+ * MK_G_LML [batch, grid, 2], MK_G_ATTN_PART [batch, kv_heads, MK_Q_MAX_SPLITS, MK_Q_PART_STRIDE]), the
+ * DeltaNet state and conv history of every layer, and MK_G_BLOCK_TABLE [batch, max_seq / 64] with page
+ * numbers into one pool per layer (batch * max_seq / 64 <= 512 pages).  A sequence that has produced a
+ * stop id, or has run its n_total steps, keeps stepping until all have (its outputs are to be
+ * ignored), but its DeltaNet state and conv history stay as its last accepted token left them. */
+#define MK_MAX_BATCH 8
+typedef struct mk_batch_args {
+    uint64_t forced;                 /* int32[max n_forced, MK_MAX_BATCH], step-major                 */
+    int32_t n_forced[MK_MAX_BATCH];  /* prompt tokens of each sequence, >= 1                          */
+    int32_t n_total[MK_MAX_BATCH];   /* steps each sequence takes part in (n_forced + n_generate - 1) */
+    int32_t pos0[MK_MAX_BATCH];      /* position of each sequence's first token in this launch        */
+    int32_t batch;                   /* live sequences, 1..MK_MAX_BATCH                               */
+    int32_t n_steps;
+    int32_t lm_from;                 /* first step that runs the LM head: <= min n_forced - 1         */
+    uint32_t epoch_base;
+    uint32_t seed;                   /* sequence j samples with seed + j * 0x9E3779B9                 */
+    float inv_temperature;
+    int32_t n_stop;
+    int32_t prof_step;
+    uint64_t stop_ids;
+    uint64_t tokens_out;             /* u64[n_steps, MK_MAX_BATCH] keys of every step from lm_from on */
+    uint64_t logits_out;             /* optional fp32 [n_steps, MK_MAX_BATCH, vocab]                  */
+    uint64_t step_ts;                /* optional u64 [n_steps + 1]                                    */
+    uint64_t out_info;               /* int32[8]: steps run, next epoch, bit mask of stopped sequences */
+    uint64_t prof;
+    int64_t spin_limit_ns;
+} mk_batch_args;
+int mk_launch_batch(mk_engine* e, const mk_batch_args* args, void* stream);
+
 /* Replaces `watchdog_fired` (qwen3.5-0.8b/csrc/megakernel.cu:1284-1289): synchronises the device,
  * reads the status words of the last launch and returns MK_OK or MK_ERR_TIMEOUT.  Unlike the
  * reference, waits are bounded in every build, not only with -DMK_WATCHDOG. */
@@ -176,7 +214,7 @@ int mk_status(mk_engine* e, int32_t* where);
 enum {
     MK_Q_SMEM_BYTES = 0, MK_Q_N_THREADS, MK_Q_CONV_RING, MK_Q_KV_BLOCK, MK_Q_MAX_SPLITS, MK_Q_PART_STRIDE,
     MK_Q_OPS_PER_LAYER, MK_Q_PROF_MAX_OPS, MK_Q_PROF_FIELDS, MK_Q_SPEC_T, MK_Q_MAX_LAYERS, MK_Q_LAYER_FIELDS,
-    MK_Q_GLOBAL_FIELDS, MK_Q_SLOT_BYTES, MK_Q_STAGES, MK_Q_MAX_LM_ROWS
+    MK_Q_GLOBAL_FIELDS, MK_Q_SLOT_BYTES, MK_Q_STAGES, MK_Q_MAX_LM_ROWS, MK_Q_MAX_BATCH, MK_Q_BATCH_SMEM_BYTES
 };
 int64_t mk_query(int what);
 

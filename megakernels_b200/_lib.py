@@ -26,8 +26,8 @@ GLOBAL_FIELDS = ["embed", "embed_scale", "lm_head", "lm_scale", "final_norm", "r
                  "mtp_norm_e", "mtp_norm_h", "mtp_norm", "draft_head", "draft_scale", "draft_ids", "xml"]
 QUERIES = ["SMEM_BYTES", "N_THREADS", "CONV_RING", "KV_BLOCK", "MAX_SPLITS", "PART_STRIDE", "OPS_PER_LAYER",
            "PROF_MAX_OPS", "PROF_FIELDS", "SPEC_T", "MAX_LAYERS", "LAYER_FIELDS", "GLOBAL_FIELDS", "SLOT_BYTES",
-           "STAGES", "MAX_LM_ROWS"]
-EXPORTS = ["mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_status", "mk_query", "mk_bw_probe",
+           "STAGES", "MAX_LM_ROWS", "MAX_BATCH", "BATCH_SMEM_BYTES"]
+EXPORTS = ["mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_launch_batch", "mk_status", "mk_query", "mk_bw_probe",
            "mk_plan_rows", "mk_plan_attn_chunk", "mk_last_error"]
 
 
@@ -54,6 +54,19 @@ class LaunchArgs(ctypes.Structure):
                 ("spec_out", ctypes.c_uint64), ("cycle_out", ctypes.c_uint64)]
 
 
+MAX_BATCH = 8
+
+
+class BatchArgs(ctypes.Structure):
+    _fields_ = [("forced", ctypes.c_uint64), ("n_forced", ctypes.c_int32 * MAX_BATCH),
+                ("n_total", ctypes.c_int32 * MAX_BATCH), ("pos0", ctypes.c_int32 * MAX_BATCH),
+                ("batch", ctypes.c_int32), ("n_steps", ctypes.c_int32), ("lm_from", ctypes.c_int32),
+                ("epoch_base", ctypes.c_uint32), ("seed", ctypes.c_uint32), ("inv_temperature", ctypes.c_float),
+                ("n_stop", ctypes.c_int32), ("prof_step", ctypes.c_int32), ("stop_ids", ctypes.c_uint64),
+                ("tokens_out", ctypes.c_uint64), ("logits_out", ctypes.c_uint64), ("step_ts", ctypes.c_uint64),
+                ("out_info", ctypes.c_uint64), ("prof", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64)]
+
+
 _lib = None
 
 
@@ -73,6 +86,7 @@ def load():
                                   ctypes.c_int64, P(ctypes.c_int64), ctypes.c_int64]
     lib.mk_launch.argtypes = [ctypes.c_void_p, P(LaunchArgs), ctypes.c_void_p]
     lib.mk_launch_static.argtypes = [ctypes.c_void_p, P(LaunchArgs), ctypes.c_void_p]
+    lib.mk_launch_batch.argtypes = [ctypes.c_void_p, P(BatchArgs), ctypes.c_void_p]
     lib.mk_status.argtypes = [ctypes.c_void_p, P(ctypes.c_int32)]
     lib.mk_query.argtypes = [ctypes.c_int]
     lib.mk_query.restype = ctypes.c_int64
@@ -82,7 +96,7 @@ def load():
     lib.mk_plan_attn_chunk.argtypes = [ctypes.c_int, ctypes.c_int]
     lib.mk_plan_attn_chunk.restype = ctypes.c_int
     lib.mk_last_error.restype = ctypes.c_char_p
-    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_status", "mk_bw_probe", "mk_plan_rows"):
+    for name in ("mk_create", "mk_destroy", "mk_set_params", "mk_launch", "mk_launch_static", "mk_launch_batch", "mk_status", "mk_bw_probe", "mk_plan_rows"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib

@@ -8,6 +8,7 @@
 
 #include "../../include/mk_b200.h"
 #include "mk_decode.cuh"
+#include "mk_batch.cuh"
 
 using namespace mk;
 
@@ -188,7 +189,10 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
 }
 
 typedef void (*kernel_fn)(const int, const Args);
-static_assert(Geo<1>::SMEM == SMEM_BYTES && Geo<2>::SMEM == SMEM_BYTES, "one shared-memory size for both kernels");
+static_assert(Geo<1>::SMEM <= SMEM_BYTES && Geo<2>::SMEM <= SMEM_BYTES, "MK_Q_SMEM_BYTES reports the largest kernel");
+
+// Dynamic shared memory of the kernel variant: what is not requested stays with the L1 cache.
+static int kernel_smem(bool spec) { return spec ? Geo<2>::SMEM : Geo<1>::SMEM; }
 
 static kernel_fn pick_kernel(const mk_model_desc& d, bool spec = false) {
     const bool q8 = d.quant == MK_QUANT_INT8, f32 = d.kv_dtype == MK_KV_F32;
@@ -265,10 +269,10 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
 
     MK_CUDA(cudaSetDevice(e->desc.device));
     kernel_fn fn = pick_kernel(e->desc, spec);
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel_smem(spec)));
     int slot = e->slot;
     void* kargs[] = {&slot, &A};
-    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, SMEM_BYTES,
+    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, kernel_smem(spec),
                                         static_cast<cudaStream_t>(stream)));
     return MK_OK;
 }
@@ -369,10 +373,79 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     A.n_stop = a->n_stop;
     A.prof_step = a->prof_step;
     kernel_fn fn = pick_kernel(e->desc);
-    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel_smem(false)));
     int slot = pslot;
     void* kargs[] = {&slot, &A};
-    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, SMEM_BYTES, st));
+    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, kernel_smem(false), st));
+    return MK_OK;
+}
+
+// ---- batched decoding ---------------------------------------------------------------------------------
+static_assert(MK_MAX_BATCH == NB, "header and kernel agree on the batch width");
+typedef void (*batch_kernel_fn)(const int, const BatchArgs);
+
+extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* stream) {
+    typedef Qwen35_08B S;
+    if (!e || !a) return fail(MK_ERR_BADARG, "mk_launch_batch: null argument");
+    if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch_batch: mk_set_params has not succeeded on this engine");
+    if (e->desc.quant != MK_QUANT_INT8) return fail(MK_ERR_UNSUPPORTED, "mk_launch_batch: batched decoding is built for int8 weights only");
+    if (a->batch < 1 || a->batch > NB) return fail(MK_ERR_BADARG, "mk_launch_batch: batch %d out of [1, %d]", a->batch, NB);
+    if (a->n_steps < 1 || !a->forced || !a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch_batch: need n_steps >= 1, a token list, tokens_out and out_info");
+    if ((int64_t)a->batch * (e->desc.max_seq / KV_BLOCK) > MAX_BLOCKS)
+        return fail(MK_ERR_BADARG, "mk_launch_batch: %d sequences of %d positions need more than %d KV pages", a->batch, e->desc.max_seq, MAX_BLOCKS);
+    int min_forced = 1 << 30, last_pos = 0;
+    for (int j = 0; j < a->batch; j++) {
+        if (a->n_forced[j] < 1 || a->n_forced[j] > a->n_total[j] || a->n_total[j] > a->n_steps)
+            return fail(MK_ERR_BADARG, "mk_launch_batch: sequence %d: need 1 <= n_forced <= n_total <= n_steps", j);
+        if (a->pos0[j] < 0 || (int64_t)a->pos0[j] + a->n_steps > e->desc.max_seq)
+            return fail(MK_ERR_BADARG, "mk_launch_batch: sequence %d would exceed max_seq=%d", j, e->desc.max_seq);
+        min_forced = a->n_forced[j] < min_forced ? a->n_forced[j] : min_forced;
+        last_pos = a->pos0[j] + a->n_steps > last_pos ? a->pos0[j] + a->n_steps : last_pos;
+    }
+    if (a->lm_from < 0 || a->lm_from > min_forced - 1) return fail(MK_ERR_BADARG, "mk_launch_batch: lm_from must lie in [0, min n_forced - 1]");
+    if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch_batch: stop ids missing");
+    const int grid = e->desc.grid;
+    if ((S::GDN_IN + grid - 1) / grid > MAX_BODY_ROWS || (S::HID + grid - 1) / grid > 16 || grid > S::HID || grid < S::GDN_TASKS)
+        return fail(MK_ERR_BADARG, "mk_launch_batch: grid %d too small or too large for this shape", grid);
+    const int per = grid / a->batch;                     // CTAs that serve one sequence's attention
+    if (per < S::NKV) return fail(MK_ERR_BADARG, "mk_launch_batch: grid %d too small for %d sequences", grid, a->batch);
+    if (attn_chunk(last_pos, per / S::NKV < MAX_SPLITS ? per / S::NKV : MAX_SPLITS) > MAX_CHUNK_POS)
+        return fail(MK_ERR_BADARG, "mk_launch_batch: context of %d positions is too long for %d CTAs per sequence", last_pos, per);
+    const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1;
+    if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
+        return fail(MK_ERR_BADARG, "mk_launch_batch: epoch counter exhausted or zero; reset the engine");
+
+    BatchArgs A;
+    memset(&A, 0, sizeof A);
+    A.forced = as_ptr<const int*>(a->forced);
+    A.stop_ids = as_ptr<const int*>(a->stop_ids);
+    A.tokens_out = as_ptr<unsigned long long*>(a->tokens_out);
+    A.logits_out = as_ptr<float*>(a->logits_out);
+    A.step_ts = as_ptr<unsigned long long*>(a->step_ts);
+    A.out_info = as_ptr<int*>(a->out_info);
+    A.prof = as_ptr<unsigned long long*>(a->prof);
+    A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
+    for (int j = 0; j < NB; j++) {
+        A.n_forced[j] = j < a->batch ? a->n_forced[j] : 0;
+        A.n_total[j] = j < a->batch ? a->n_total[j] : 0;
+        A.pos0[j] = j < a->batch ? a->pos0[j] : 0;
+    }
+    A.nb = a->batch;
+    A.n_steps = a->n_steps;
+    A.lm_from = a->lm_from;
+    A.epoch_base = a->epoch_base;
+    A.seed = a->seed;
+    A.inv_temperature = a->inv_temperature;
+    A.n_stop = a->n_stop;
+    A.prof_step = a->prof_step;
+
+    MK_CUDA(cudaSetDevice(e->desc.device));
+    batch_kernel_fn fn = e->desc.kv_dtype == MK_KV_F32 ? batch_kernel<S, true> : batch_kernel<S, false>;
+    MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, GeoB::SMEM));
+    int slot = e->slot;
+    void* kargs[] = {&slot, &A};
+    MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, GeoB::SMEM,
+                                        static_cast<cudaStream_t>(stream)));
     return MK_OK;
 }
 
@@ -405,6 +478,8 @@ extern "C" int64_t mk_query(int what) {
         case MK_Q_SLOT_BYTES: return SLOT_BYTES;
         case MK_Q_STAGES: return NSTAGE;
         case MK_Q_MAX_LM_ROWS: return MAX_LM_ROWS;
+        case MK_Q_MAX_BATCH: return NB;
+        case MK_Q_BATCH_SMEM_BYTES: return GeoB::SMEM;
         default: return -1;
     }
 }

@@ -42,6 +42,8 @@ struct Smem {
     u64* best_s;        // [NCW] block-reduction scratch for 64-bit keys
     float* scale_s;     // per-row scales: two 128-row buffers for layer GEMVs, then the streaming ring
     float* xscale_s;    // [T] power-of-two factors that undo the fixed-point scaling of the staged inputs
+    float* ssq_s;       // batched decoding: [sequence][NCW] per-warp sums of squares of the RMSNorm input staged last
+    float* wsc_s;       // batched decoding: [NCW][sequence] inverse fixed-point scales of each warp's k-slice
     uint64_t* full;     // [ring stages]
     uint64_t* empty;    // [ring stages]
     volatile int* abort_flag;
@@ -78,18 +80,21 @@ struct Spin {
     uint32_t it = 0;
     u64 t0 = 0;
 };
+constexpr u64 SPIN_FAILED = ~0ull;
 
-// Slow path of every spin loop, entered once per 256 polls.
-__device__ __noinline__ bool spin_slow(volatile int* abort_flag, int* status, u64 limit_ns, Spin& s, int where) {
-    if (*abort_flag) return true;
+// Slow path of every spin loop, entered once per 256 polls.  Takes and returns the time of the
+// loop's first visit by value: a `Spin` whose address went to a function that is not inlined would
+// live in local memory, and every poll of every loop would then load and store it there.
+__device__ __noinline__ u64 spin_slow(volatile int* abort_flag, int* status, u64 limit_ns, u64 t0, int where) {
+    if (*abort_flag) return SPIN_FAILED;
     if (ld_volatile_i32(status) != 0) {
         *abort_flag = 1;
-        return true;
+        return SPIN_FAILED;
     }
     const u64 now = globaltimer();
-    if (!s.t0) {
-        s.t0 = now;
-    } else if (now - s.t0 > limit_ns) {
+    if (!t0) {
+        t0 = now;
+    } else if (now - t0 > limit_ns) {
         if (atomicCAS(status, 0, ERR_TIMEOUT) == 0) {
             status[1] = where;
             status[2] = (int)blockIdx.x;
@@ -97,13 +102,14 @@ __device__ __noinline__ bool spin_slow(volatile int* abort_flag, int* status, u6
         }
         __threadfence();
         *abort_flag = 1;
-        return true;
+        return SPIN_FAILED;
     }
     __nanosleep(40);
-    return false;
+    return t0;
 }
-#define MK_SPIN_FAIL(c, s, where) \
-    ((((++(s).it) & 255u) == 0) && spin_slow((c).sm.abort_flag, (c).status, (c).limit_ns, (s), (where)))
+#define MK_SPIN_FAIL(c, s, where)          \
+    ((((++(s).it) & 255u) == 0) &&         \
+     (((s).t0 = spin_slow((c).sm.abort_flag, (c).status, (c).limit_ns, (s).t0, (where))) == SPIN_FAILED))
 
 __device__ __forceinline__ void mbar_wait(Ctx& c, uint64_t* b, uint32_t parity, int where) {
     Spin s;
@@ -195,6 +201,42 @@ __device__ __forceinline__ void ll_wait_pairs(Ctx& c, const u64* const (&p)[N], 
     }
 }
 
+// The same with the addresses and epochs given as functions of the pair's index, so that a caller whose
+// addresses follow from a few bases keeps no pointer array in registers.  addr(i) may be null.
+template <int N, class Addr, class Epoch>
+__device__ __forceinline__ void ll_wait_pairs_fn(Ctx& c, Addr&& addr, Epoch&& epoch, float (&v)[2 * N], int where) {
+    u64 w[2 * N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        w[2 * i] = w[2 * i + 1] = 0;
+        if (const u64* p = addr(i)) ll_load2(p, w[2 * i], w[2 * i + 1]);
+    }
+    Spin s;
+    while (true) {
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; i++) {
+            const u64* p = addr(i);
+            const uint32_t e = epoch(i);
+            if (p && ((uint32_t)(w[2 * i] >> 32) != e || (uint32_t)(w[2 * i + 1] >> 32) != e)) {
+                ok = false;
+                ll_load2(p, w[2 * i], w[2 * i + 1]);
+            }
+        }
+        if (ok) break;
+        if (MK_SPIN_FAIL(c, s, where)) {
+            c.dead = true;
+            break;
+        }
+        poll_backoff(s.it);
+    }
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        v[2 * i] = __uint_as_float((uint32_t)w[2 * i]);
+        v[2 * i + 1] = __uint_as_float((uint32_t)w[2 * i + 1]);
+    }
+}
+
 // A CTA that had no part in the op it now waits for arrives early.  If all of its threads polled
 // right away, their loads would queue in front of the very stores they wait for.  Instead one warp
 // watches 32 words spread over the buffer, at a relaxed pace, and releases the CTA when all of them
@@ -220,7 +262,13 @@ __device__ __forceinline__ void gate_on_samples(Ctx& c, const u64* buf, int nwor
 // Geometry that depends on how many tokens one pass over the weights serves (1: plain decode,
 // 2: a speculative cycle).  Two tokens need twice the input planes, so the ring gives up a stage.
 template <int T> struct Geo {
-    static constexpr int NS = T == 1 ? 6 : 5;                       // ring stages
+#ifndef MK_NS1
+#define MK_NS1 6
+#endif
+#ifndef MK_NS2
+#define MK_NS2 5
+#endif
+    static constexpr int NS = T == 1 ? MK_NS1 : MK_NS2;             // ring stages
     static constexpr int RING = NS * SLOT_BYTES;
     static constexpr int XQ = (T == 1 ? 3 : 7) * 2 * 3584;          // input planes: bf16 pieces of K = 3584 are the largest
     static constexpr int PART = NCW * T * 64 * 4;                   // per-warp partial sums
@@ -777,17 +825,30 @@ __device__ __forceinline__ void store1(void* base, size_t elem, float v) {
 // projection and the scores.  With one split the task publishes the normalised outputs itself;
 // otherwise every task publishes (acc, m, l) partials as flag-in-data words and then merges a
 // 1/nsplit share of the head group's outputs from all partials, in a fixed order.
+//
+// `V` says which CTAs serve the sequence and where its hand-off words and block table are: the whole
+// grid and the engine's buffers for a single sequence, a group of CTAs and a slice of the buffers per
+// sequence when several sequences decode side by side.
+struct AttnView {
+    int cta, grid;          // this CTA's index among the CTAs that serve the sequence, and their number
+    const u64* projl;       // projection words of the sequence's first token slot
+    u64* mixl;              // mixer output words of that slot
+    u64* part;              // split partials of that slot
+    const int* bt;          // the sequence's block table (shared memory)
+};
+
 template <class S, bool KVF32, int T>
-__device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op) {
+__device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView& V, int pos, uint32_t e_proj,
+                        uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
     constexpr int NOUT = S::QPK * S::HD;        // outputs per KV head and token
     constexpr int PFV = 16;                     // V rows requested early per thread
     const int n = pos + T;
-    const int max_splits = min(c.grid / S::NKV, MAX_SPLITS);
+    const int max_splits = min(V.grid / S::NKV, MAX_SPLITS);
     const int ch = attn_chunk(n, max_splits);
     const int nsplit = (n + ch - 1) / ch;
-    if (c.cta >= nsplit * S::NKV) return false;
-    const int g = c.cta % S::NKV, sp = c.cta / S::NKV;
+    if (V.cta >= nsplit * S::NKV) return false;
+    const int g = V.cta % S::NKV, sp = V.cta / S::NKV;
     const int p0 = sp * ch, p1 = min(n, p0 + ch);
     const int np = p1 - p0;
 
@@ -799,7 +860,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
 
     const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
     auto kv_elem = [&](int p) -> size_t {
-        const int blk = c.sm.bt_s[p >> 6];
+        const int blk = V.bt[p >> 6];
         return ((size_t)blk * S::NKV + g) * kv_head_stride + (size_t)(p & (KV_BLOCK - 1)) * S::HD;
     };
     // -- 0. request cached rows early: the K row of this warp's first position, V elements of this thread's dim
@@ -828,7 +889,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         uint32_t eps[2 * T];
 #pragma unroll
         for (int tk = 0; tk < T; tk++) {
-            const u64* pj = P.projl + (size_t)tk * S::PROJ_MAX;
+            const u64* pj = V.projl + (size_t)tk * S::PROJ_MAX;
             ptrs[2 * tk] = pj + (g * S::QPK + hh) * 2 * S::HD + dd;
             ptrs[2 * tk + 1] = hh == 0 ? pj + S::ATT_K_OFF + g * S::HD + dd
                                        : (hh == 1 ? pj + S::ATT_V_OFF + g * S::HD + dd : nullptr);
@@ -1000,7 +1061,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     if (nsplit == 1) {
 #pragma unroll
         for (int tk = 0; tk < T; tk++) {
-            u64* out = P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
+            u64* out = V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
             ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
             ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
         }
@@ -1013,7 +1074,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
     // -- 6. partials as flag-in-data words: per token acc [4][256], then (m, l) per head
 #pragma unroll
     for (int tk = 0; tk < T; tk++) {
-        u64* part = P.attn_part + (((size_t)tk * S::NKV + g) * MAX_SPLITS + sp) * S::PART_STRIDE;
+        u64* part = V.part + (((size_t)tk * S::NKV + g) * MAX_SPLITS + sp) * S::PART_STRIDE;
         ll_store(part + (2 * hp) * S::HD + d, e_out, acc[tk][0]);
         ll_store(part + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1]);
         if (c.tid < 2 * S::QPK) ll_store(part + NOUT + c.tid, e_out, stat_s[tk * 8 + (c.tid & 1) * S::QPK + (c.tid >> 1)]);
@@ -1028,7 +1089,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         const int ns_t = min(nsplit, (pos + tk + ch) / ch);          // splits that hold positions <= pos + tk
         if (ns_t == 1) {                                             // everything this token sees is in split 0
             if (sp == 0) {
-                u64* out = P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
+                u64* out = V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
                 ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
                 ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
             }
@@ -1041,7 +1102,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
         const int o = sp * opc + oi;
         const bool live = sp < ns_t && oi < opc && o < NOUT;
         const int h = o / S::HD;
-        const u64* pg = P.attn_part + ((size_t)tk * S::NKV + g) * MAX_SPLITS * S::PART_STRIDE;
+        const u64* pg = V.part + ((size_t)tk * S::NKV + g) * MAX_SPLITS * S::PART_STRIDE;
         float mv[SPT], lv[SPT], av[SPT];
         {
             u64 wa[SPT], wm[SPT], wl[SPT];
@@ -1097,7 +1158,7 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint3
             Ls += __shfl_xor_sync(0xffffffffu, Ls, x);
             Os += __shfl_xor_sync(0xffffffffu, Os, x);
         }
-        if (live && sub == 0) ll_store(P.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD + o, e_out, Os / Ls);
+        if (live && sub == 0) ll_store(V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD + o, e_out, Os / Ls);
     }
     __threadfence();      // K/V append before anything this CTA publishes later (see above)
     consumer_sync();      // scratch aliases the GEMV input planes that the next prologue writes
@@ -1143,7 +1204,8 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
     }
     // ---- B: mixer
     prof_stamp(c, op0 + 1, 0);
-    const bool had_task = attn ? attn_op<S, KVF32, T>(c, P, L, pos, eA, eB, op0 + 1)
+    const AttnView view = {c.cta, c.grid, P.projl, P.mixl, P.attn_part, c.sm.bt_s};
+    const bool had_task = attn ? attn_op<S, KVF32, T>(c, P, L, view, pos, eA, eB, op0 + 1)
                                : gdn_op<S, T>(c, P, L, pos, eA, eB, op0 + 1, from_bak);
     prof_stamp(c, op0 + 1, 3);
     // ---- C: out-projection + residual

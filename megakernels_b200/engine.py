@@ -11,6 +11,9 @@ The class keeps the interface of the reference's `Megakernel`
 * `quant="int8"` is per output channel (see `quant.py`) and covers the embedding table;
 * the KV cache is paged (`KV_BLOCK` positions per page, `block_table` maps logical to physical
   pages) and its element type is selectable (`kv_dtype`);
+* `batch=B` (int8 engines, B <= 8) keeps B independent sequences, each with its own recurrent
+  state, conv history, KV pages and position, and `run_batch` advances them side by side with one
+  pass over the weights per step;
 * PyTorch only allocates device memory and provides the stream; every launch goes through the C
   ABI in `include/mk_b200.h`.
 """
@@ -42,15 +45,20 @@ def rope_tables(cfg, max_seq, device):
 
 class Megakernel:
     def __init__(self, model, max_seq=8192, device="cuda", pf_bytes=PF_BYTES, quant="bf16", mtp=False,
-                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None):
+                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None, batch=1):
         """`mtp` loads the multi-token-prediction head for speculative decoding (`run_spec`); its drafts
         come from the `draft_vocab` most frequent tokens listed in `draft_ids` (0: the whole vocabulary)."""
         if quant not in ("bf16", "int8"):
             raise ValueError(f"quant must be 'bf16' or 'int8', got {quant!r}")
         if kv_dtype not in ("bf16", "fp32"):
             raise ValueError(f"kv_dtype must be 'bf16' or 'fp32', got {kv_dtype!r}")
+        if not 1 <= batch <= _lib.MAX_BATCH:
+            raise ValueError(f"batch must lie in [1, {_lib.MAX_BATCH}], got {batch}")
+        if batch > 1 and quant != "int8":
+            raise ValueError("batched decoding is built for int8 weights only")
         if not torch.cuda.is_available():
             raise RuntimeError("the decode megakernel needs a CUDA device; there is no CPU path")
+        self.batch = batch
         self.lib = _lib.load()
         self.quant, self.kv_dtype, self.pf_bytes = quant, kv_dtype, pf_bytes
         self.spin_limit_ns = int(spin_limit_ms * 1e6)
@@ -78,6 +86,8 @@ class Megakernel:
         self.GDN_TASKS = cfg.lin_heads * cfg.lin_v_dim // self.GDN_SLICE
         self.TASK_CHANNELS = 2 * cfg.lin_k_dim + self.GDN_SLICE
         self.max_seq = (max_seq + self.KV_BLOCK - 1) // self.KV_BLOCK * self.KV_BLOCK
+        if batch > 1 and batch * (self.max_seq // self.KV_BLOCK) > 512:
+            raise ValueError(f"{batch} sequences of {self.max_seq} positions exceed the 512 KV pages one launch can map")
         self.grid = torch.cuda.get_device_properties(device).multi_processor_count
         self._keep = []   # every tensor whose address the kernel holds
 
@@ -108,10 +118,11 @@ class Megakernel:
             return keep(packed), (keep(s) if s is not None else 0)
 
         kvt = torch.float32 if kv_dtype == "fp32" else torch.bfloat16
-        n_blocks = self.max_seq // self.KV_BLOCK
+        n_blocks = self.max_seq // self.KV_BLOCK          # pages per sequence; the pool holds `batch` times as many
         ring = _lib.query("CONV_RING")
         zeros = lambda *shape, dtype=torch.float32: torch.zeros(*shape, device=device, dtype=dtype)
         self.conv_hist, self.state, self.state_bak, self.k_cache, self.v_cache = [], [], [], [], []
+        self.bconv_hist, self.bstate = [], []             # the same with a leading sequence dimension
         F = _lib.LAYER_FIELDS
         layer_vals = []
         def common(w, m):
@@ -132,8 +143,8 @@ class Megakernel:
             rec["w_out"], rec["s_out"] = mat(w[p + "o_proj.weight"])
             rec["q_norm"] = f32(w[p + "q_norm.weight"])
             rec["k_norm"] = f32(w[p + "k_norm.weight"])
-            kc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
-            vc = zeros(n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+            kc = zeros(batch * n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
+            vc = zeros(batch * n_blocks, cfg.n_kv_heads, self.KV_BLOCK, cfg.head_dim, dtype=kvt)
             rec["k_cache"], rec["v_cache"] = keep(kc), keep(vc)
             rec["kind"] = 1
             return rec, kc, vc
@@ -157,11 +168,13 @@ class Megakernel:
                 rec["A_log"] = f32(w[p + "A_log"])
                 rec["dt_bias"] = f32(w[p + "dt_bias"])
                 rec["gdn_norm"] = f32(w[p + "norm.weight"])
-                hist = zeros(self.GDN_TASKS, self.TASK_CHANNELS, ring)   # per recurrence task
-                st = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)   # [head][v][k]: the oracle's transposed
+                hist = zeros(batch, self.GDN_TASKS, self.TASK_CHANNELS, ring)   # per sequence and recurrence task
+                st = zeros(batch, cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)   # [head][v][k]: the oracle's transposed
                 bak = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)
-                self.conv_hist.append(hist)
-                self.state.append(st)
+                self.bconv_hist.append(hist)
+                self.bstate.append(st)
+                self.conv_hist.append(hist[0])            # sequence 0 is what the single-sequence launches use
+                self.state.append(st[0])
                 self.state_bak.append(bak)
                 rec["conv_hist"], rec["state"], rec["state_bak"] = keep(hist), keep(st), keep(bak)
                 rec["kind"] = 0
@@ -172,13 +185,13 @@ class Megakernel:
         proj_max = max(cfg.gdn_in_rows, cfg.attn_in_rows)
         mix = cfg.n_heads * cfg.head_dim
         # flag-in-data activation buffers: (epoch << 32) | fp32 bits
-        T = _lib.query("SPEC_T")   # every hand-off buffer holds a speculative cycle's two tokens
+        T = max(_lib.query("SPEC_T"), batch)   # token slots per hand-off buffer: a speculative cycle's two tokens, or one per sequence
         self.ll = [torch.zeros(n, **u64) for n in (T * cfg.hidden, T * proj_max, T * mix, T * cfg.intermediate,
                                                    (T + 1) * 2 * self.grid, T * cfg.hidden)]
         max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
         self.attn_part = zeros(T * cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
         self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
-        self.block_table = torch.arange(n_blocks, device=device, dtype=torch.int32)
+        self.block_table = torch.arange(batch * n_blocks, device=device, dtype=torch.int32)   # [sequence][page]
         self.status = zeros(4, dtype=torch.int32)
 
         self.embed = w["embed_tokens.weight"].to(device)
@@ -249,6 +262,15 @@ class Megakernel:
         if abs(c.eps - 1e-6) > 1e-12:
             raise ValueError("rms_norm_eps must be 1e-6")
 
+    @property
+    def pos(self):
+        """Position of the (first) sequence: the next token goes here."""
+        return self.bpos[0]
+
+    @pos.setter
+    def pos(self, value):
+        self.bpos[0] = value
+
     def __del__(self):
         h = getattr(self, "_h", None)
         if h:
@@ -275,19 +297,19 @@ class Megakernel:
 
     def reset(self):
         """Start a new sequence (cached K/V need no clearing: positions are rewritten)."""
-        for t in self.conv_hist + self.state + self.ll:
+        for t in self.bconv_hist + self.bstate + self.ll:
             t.zero_()
+        self.bpos = [0] * self.batch   # position of every sequence; `pos` is that of sequence 0
         self.attn_flag.zero_()
         self.attn_part.zero_()
         self.status.zero_()
         self.epoch = 1   # the buffers are zero, so epoch 0 never looks ready
-        self.pos = 0
         self.mtp_h = None   # (position, hidden state) whose draft-cache entry still awaits its next token
 
     def set_block_table(self, table):
         """Map logical KV pages to physical pages (a permutation of range(max_seq / KV_BLOCK))."""
         t = torch.as_tensor(table, dtype=torch.int32, device=self.device)
-        if t.shape != self.block_table.shape or sorted(t.tolist()) != list(range(len(t))):
+        if t.shape != self.block_table.shape or sorted(t.flatten().tolist()) != list(range(t.numel())):
             raise ValueError("block table must be a permutation of all pages")
         self.block_table.copy_(t)
 
@@ -355,6 +377,82 @@ class Megakernel:
         if return_logits:
             return ids, logits[n_forced - 1: done]
         return ids
+
+    # ------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def run_batch(self, prompts, n_generate=1, temperature=0.0, seed=0, stop_ids=(), return_logits=False,
+                  timing=False, prof=None, prof_step=0):
+        """Advance `len(prompts)` sequences side by side: feed each its tokens, then let each continue
+        for up to `n_generate` predicted tokens.  One launch; every step is one pass over the weights
+        for all sequences.  Sequence j continues from `self.bpos[j]`; per sequence the contract is that
+        of `run` (a predicted stop id ends that sequence and is reported but not fed; its state has
+        absorbed every returned id but the last).  Returns one id list per sequence, plus one logits
+        tensor per sequence with `return_logits`.  The batched counterpart in the reference is the
+        gfx942 engines' `Engine.step(tok[M])` (`qwen3.8-27b-gfx942/mk/runner.py:202-213`), which takes
+        one token per sequence and call; here the whole generation is one launch as in `run`."""
+        B = len(prompts)
+        if not 1 <= B <= self.batch:
+            raise ValueError(f"this engine holds {self.batch} sequences, got {B} prompts")
+        prompts = [[int(t) for t in p] for p in prompts]
+        if any(not p for p in prompts):
+            raise ValueError("every sequence needs at least one input token")
+        if n_generate < 1:
+            raise ValueError("n_generate must be >= 1")
+        NBW = _lib.MAX_BATCH
+        n_forced = [len(p) for p in prompts]
+        n_total = [n + n_generate - 1 for n in n_forced]
+        n_steps = max(n_total)
+        if any(self.bpos[j] + n_steps > self.max_seq for j in range(B)):
+            raise ValueError(f"a sequence would exceed max_seq={self.max_seq}")
+        dev = self.device
+        forced = torch.zeros(max(n_forced), NBW, dtype=torch.int32)
+        for j, p in enumerate(prompts):
+            forced[: len(p), j] = torch.tensor(p, dtype=torch.int32)
+        forced = forced.pin_memory().to(dev, non_blocking=True)
+        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=dev)
+        out = torch.zeros(n_steps, NBW, dtype=torch.int64, device=dev)
+        info = torch.zeros(8, dtype=torch.int32, device=dev)
+        ts = torch.zeros(n_steps + 1, dtype=torch.int64, device=dev) if timing else None
+        logits = torch.empty(n_steps, NBW, self.cfg.vocab, device=dev) if return_logits else None
+        ptr = lambda t: t.data_ptr() if t is not None else 0
+        pad = lambda v: (ctypes.c_int32 * NBW)(*(list(v) + [0] * (NBW - len(v))))
+        a = _lib.BatchArgs(forced=forced.data_ptr(), n_forced=pad(n_forced), n_total=pad(n_total),
+                           pos0=pad(self.bpos[:B]), batch=B, n_steps=n_steps, lm_from=min(n_forced) - 1,
+                           epoch_base=self.epoch, seed=seed & 0xFFFFFFFF,
+                           inv_temperature=1.0 / temperature if temperature > 0 else 0.0, n_stop=len(stop_ids),
+                           prof_step=prof_step, stop_ids=stops.data_ptr(), tokens_out=out.data_ptr(),
+                           logits_out=ptr(logits), step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof),
+                           spin_limit_ns=self.spin_limit_ns)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(self.lib.mk_launch_batch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+        self.launches += 1
+        done, epoch, _ = info[:3].tolist()          # synchronises with the launch
+        if int(self.status[0]) != 0:
+            where = ctypes.c_int32()
+            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
+        self.epoch = epoch & 0xFFFFFFFF
+        if self.epoch > 0xFFFF0000:
+            raise RuntimeError("epoch counter exhausted; call reset()")
+        if timing:
+            t = ts[: done + 1].cpu()
+            self.last_step_ns = (t[1:] - t[:-1]).tolist()
+        ids_all = (0xFFFFFFFF - (out[:done] & 0xFFFFFFFF)).cpu()
+        stop_set = set(int(s) for s in stop_ids)
+        result, result_logits = [], []
+        for j in range(B):
+            first, last = n_forced[j] - 1, min(done, n_total[j])
+            ids = ids_all[first:last, j].tolist()
+            for i, t in enumerate(ids):
+                if t in stop_set:
+                    ids = ids[: i + 1]
+                    last = first + i + 1
+                    break
+            self.bpos[j] += last
+            result.append(ids)
+            if return_logits:
+                result_logits.append(logits[first:last, j])
+        self.mtp_h = None
+        return (result, result_logits) if return_logits else result
 
     def prof_buffer(self):
         """Zeroed timestamp buffer for `run(prof=...)`: [grid, PROF_MAX_OPS, PROF_FIELDS] GPU nanoseconds
@@ -471,17 +569,17 @@ class Megakernel:
         self.pending = last
 
     # ---- state access in the oracle's layouts (for tests, snapshots and state import) -----------
-    def deltanet_state(self, i):
-        """Recurrent state of the i-th DeltaNet layer as [head][k][v] (the reference decoder's layout,
-        `qwen_mk/reference.py:54`; the kernel stores [head][v][k])."""
-        return self.state[i].transpose(1, 2).contiguous()
+    def deltanet_state(self, i, seq=0):
+        """Recurrent state of the i-th DeltaNet layer of sequence `seq` as [head][k][v] (the reference
+        decoder's layout, `qwen_mk/reference.py:54`; the kernel stores [head][v][k])."""
+        return self.bstate[i][seq].transpose(1, 2).contiguous()
 
-    def conv_window(self, i):
+    def conv_window(self, i, seq=0):
         """Last three conv inputs of the i-th DeltaNet layer as [conv_dim, 3], oldest first (the
         reference decoder's `conv_hist`, `qwen_mk/reference.py:53,70-71`)."""
         c, ring = self.cfg, self.conv_hist[i].shape[-1]
-        slots = [(self.pos - 3 + j) % ring for j in range(3)]
-        h = self.conv_hist[i][:, :, slots]                       # [task, channel, 3]
+        slots = [(self.bpos[seq] - 3 + j) % ring for j in range(3)]
+        h = self.bconv_hist[i][seq][:, :, slots]                 # [task, channel, 3]
         spt = c.lin_v_dim // self.GDN_SLICE                     # tasks per head
         out = torch.empty(c.conv_dim, 3, device=self.device)
         nqk = c.lin_heads * c.lin_k_dim
@@ -491,9 +589,9 @@ class Megakernel:
         out[2 * nqk:] = h[:, 2 * c.lin_k_dim:].reshape(c.lin_heads * c.lin_v_dim, 3)
         return out
 
-    def kv_rows(self, i, n):
-        """K, V of the i-th attention layer for positions [0, n) as [kv_head, n, head_dim] fp32."""
-        bt = self.block_table.long()
+    def kv_rows(self, i, n, seq=0):
+        """K, V of the i-th attention layer for positions [0, n) of sequence `seq` as [kv_head, n, head_dim] fp32."""
+        bt = self.block_table.long().view(self.batch, -1)[seq]
         pos = torch.arange(n, device=self.device)
         blk, off = bt[pos // self.KV_BLOCK], pos % self.KV_BLOCK
         k = self.k_cache[i][blk, :, off].transpose(0, 1).float()
