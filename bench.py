@@ -1,12 +1,15 @@
 """Decode throughput of the megakernel on the benchmark's int8 0.8B configuration.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B]
 
 Workload (configuration 2 of the benchmark definition): the 0.8B Gated-DeltaNet / attention hybrid,
-vocab 151936, int8 per-channel weights quantised from seeded N(0, 0.02) bf16 weights, batch 1, a
-512-token uniform-random prompt already in the recurrent state and KV cache, then 512 greedy decode
-steps.  One bench "step" is one such 512-token generation: one kernel launch.  Synthetic weights and
-prompt stand in for the checkpoint and text the reference measures on.
+vocab 151936, int8 per-channel weights quantised from seeded N(0, 0.02) bf16 weights; every sequence
+has a 512-token uniform-random prompt already in its recurrent state and KV cache, then takes 512
+greedy decode steps.  The configuration is measured at batch 8 (the headline value: eight sequences
+per pass over the weights, `Megakernel.run_batch`) and at batch 1 (reported beside it under
+"batch1": the single-sequence kernel, `Megakernel.run`).  One bench "step" is one such generation of
+512 tokens per sequence: one kernel launch.  Synthetic weights and prompts stand in for the
+checkpoint and text the reference measures on.
 
 The 0.8B model is not sharded: with --gpus N every rank runs an independent replica (weak scaling)
 and the value is the sum over ranks divided by the slowest rank's time.
@@ -28,13 +31,13 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-METRIC = "decode tok/s at batch 1 (0.8B hybrid, int8 per-channel, 512-token prompt + 512 greedy steps)"
+METRIC = "decode tok/s at batch 8 and batch 1 (0.8B hybrid, int8 per-channel, 512-token prompt + 512 greedy steps)"
 PROMPT, GENERATE = 512, 512
 L2_BYTES = 126e6
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, per generated token, from the
-# ncu capture summarised in profiles/decode_kernel_int8_64prompt_16steps.md (a 16-step launch at a 64-token
-# context, scaled by steps; the KV part grows with context, the weight part does not).
-NCU_DRAM_BYTES_PER_TOKEN = (10.533937e9 + 337.758208e6) / 16
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per decode step, from the ncu captures
+# summarised under profiles/ (short launches at a short context, scaled by steps; the KV part grows with
+# context, the weight part does not): decode_kernel at batch 1, batch_kernel at batch 8.
+NCU_DRAM_BYTES_PER_STEP = {1: (10.533937e9 + 337.758208e6) / 16, 8: None}
 
 
 def measured_peak_gbs():
@@ -80,12 +83,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def bytes_per_token(mk):
-    """Algorithmic bytes one decode step must move: every weight once, the DeltaNet state read and
-    written, the KV cache read at the average context of the generation."""
+def bytes_per_step(mk, batch):
+    """Algorithmic bytes one decode step must move: every weight once, and per sequence the DeltaNet
+    state read and written and the KV cache read at the average context of the generation."""
     body, head = mk.weight_bytes
     kv = mk.kv_bytes_per_pos() * (PROMPT + GENERATE // 2)
-    return body + head + mk.state_bytes() + kv
+    return body + head + batch * (mk.state_bytes() + kv)
 
 
 def build_model(quant):
@@ -144,12 +147,84 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * n_decode / value, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "qwen3.5-0.8b hybrid, int8-dequantised weights, batch 1", "prompt": PROMPT,
+        "config": {"workload": "qwen3.5-0.8b hybrid, int8-dequantised weights, one sequence at a time", "prompt": PROMPT,
                    "generate": GENERATE, "vocab": cfg.vocab, "layers": cfg.n_layers},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
+
+
+def measure(mk, batch, prompts, args, world, device, sampler=None):
+    """Time `args.steps` generations of GENERATE tokens per sequence at `batch` sequences.  Returns
+    (kernel ms summed over the steps, wall seconds, launches, per-decode-step ns, clock record)."""
+    stream = torch.cuda.current_stream()
+    if batch == 1:
+        last = [mk.prefill(prompts[0])]           # the prompt goes through the kernel, one token per step
+    else:
+        for i in range(0, PROMPT - 1, 512):
+            mk.run_batch([p[i: min(i + 512, PROMPT - 1)] for p in prompts[:batch]])
+        last = [p[-1] for p in prompts[:batch]]
+    snap = mk.snapshot()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def one_step(timing=False):
+        mk.restore(snap)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        if batch == 1:
+            ids = [mk.run(last, n_generate=GENERATE, timing=timing)]
+        else:
+            ids = mk.run_batch([[t] for t in last], n_generate=GENERATE, timing=timing)
+        e1.record(stream)
+        return ids, e0, e1
+
+    for _ in range(args.warmup):
+        ids, _, _ = one_step()
+    assert len(ids) == batch and all(len(x) == GENERATE for x in ids)
+    # ---- timed region: kernel time with inputs resident (CUDA events on the launching stream)
+    if sampler:
+        sampler.start()
+    barrier()
+    launches0 = mk.launches
+    wall0 = time.perf_counter()
+    kernel_events, step_ns = [], []
+    for _ in range(args.steps):
+        ids, e0, e1 = one_step(timing=True)
+        kernel_events.append((e0, e1))
+        step_ns += mk.last_step_ns
+    barrier()
+    wall_s = time.perf_counter() - wall0
+    clocks = sampler.stop() if sampler else None
+    kernel_ms = [a.elapsed_time(b) for a, b in kernel_events]      # launch + readback of one generation
+    return sum(kernel_ms), wall_s, mk.launches - launches0, step_ns, clocks
+
+
+def report(mk, batch, kernel_ms, wall_s, step_ns, args, world, device):
+    """Throughput, end-to-end throughput and roofline of one measured batch size."""
+    tokens = args.steps * GENERATE * batch
+    total_ms, total_tokens = aggregate(kernel_ms, tokens, world, device)
+    e2e_ms, _ = aggregate(wall_s * 1e3, tokens, world, device)
+    peak, peak_kind = measured_peak_gbs()
+    bps = bytes_per_step(mk, batch)
+    launch_s = kernel_ms / args.steps / 1e3
+    achieved = bps * GENERATE / launch_s / 1e9
+    traffic = NCU_DRAM_BYTES_PER_STEP.get(batch)
+    return {
+        "value": total_tokens / (total_ms / 1e3), "ms_per_step": total_ms / args.steps,
+        "e2e": {"value": total_tokens / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * 8 + 4,
+                "d2h_bytes_per_step": 8 * GENERATE * (8 if batch > 1 else 1) + 32 + 4},
+        "median_decode_step_us": statistics.median(step_ns) / 1e3, "bytes_per_decode_step": bps,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
+                     "traffic": traffic * GENERATE if traffic else None,
+                     "algorithmic_bytes_per_launch": bps * GENERATE,
+                     "kernel": "batch_kernel" if batch > 1 else "decode_kernel"},
+    }
 
 
 def main():
@@ -161,6 +236,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--quant", default="int8", choices=["int8", "bf16"])
     ap.add_argument("--kv-dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--batch", type=int, default=8, help="sequences of the headline measurement (1..8; bf16 weights: 1)")
+    ap.add_argument("--no-batch1", action="store_true", help="skip the batch-1 measurement beside a batched headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="shrink the case (profiling only)")
     ap.add_argument("--generate", type=int, default=GENERATE, help="shrink the case (profiling only)")
@@ -169,6 +246,8 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)
+    if args.quant != "int8":
+        args.batch = 1
 
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -180,87 +259,50 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     from megakernels_b200.engine import Megakernel
+    from megakernels_b200.synth import make_prompt
     cfg, w, prompt = build_model(args.quant)
-    mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant=args.quant, kv_dtype=args.kv_dtype, device=device)
-    last = mk.prefill(prompt)                 # the prompt goes through the kernel, one token per step
-    snap = mk.snapshot()
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    stream = torch.cuda.current_stream()
-
-    def one_step(timing=False):
-        mk.restore(snap)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        ids = mk.run([last], n_generate=GENERATE, timing=timing)
-        e1.record(stream)
-        return ids, e0, e1
-
-    for _ in range(args.warmup):
-        ids, _, _ = one_step()
-    assert len(ids) == GENERATE
-    # ---- timed region: kernel time with inputs resident (CUDA events on the launching stream)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    barrier()
-    launches0 = mk.launches
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    wall0 = time.perf_counter()
-    start.record(stream)
-    kernel_events, step_ns = [], []
-    for _ in range(args.steps):
-        ids, e0, e1 = one_step(timing=True)
-        kernel_events.append((e0, e1))
-        step_ns += mk.last_step_ns
-    end.record(stream)
-    barrier()
-    wall_s = time.perf_counter() - wall0
-    launches = mk.launches - launches0
-    clocks = sampler.stop() if rank == 0 else None
-    kernel_ms = [a.elapsed_time(b) for a, b in kernel_events]      # launch + readback of one generation
-    local_ms = sum(kernel_ms)
-    tokens = args.steps * GENERATE
-    total_ms, total_tokens = aggregate(local_ms, tokens, world, device)
-    value = total_tokens / (total_ms / 1e3)
-    # e2e: the public call with host inputs and outputs, wall clock around the same K steps
-    e2e_ms, _ = aggregate(wall_s * 1e3, tokens, world, device)
-    e2e = total_tokens / (e2e_ms / 1e3)
+    prompts = [prompt] + [make_prompt(cfg, PROMPT, seed=1000 + j) for j in range(1, args.batch)]
+    mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant=args.quant, kv_dtype=args.kv_dtype, device=device,
+                    batch=args.batch)
+    sampler = ClockSampler(local) if rank == 0 else None
+    kernel_ms, wall_s, launches, step_ns, clocks = measure(mk, args.batch, prompts, args, world, device, sampler)
+    head = report(mk, args.batch, kernel_ms, wall_s, step_ns, args, world, device)
+    single = None
+    if args.batch > 1 and not args.no_batch1:
+        mk.reset()
+        k1, w1, l1, s1, _ = measure(mk, 1, prompts, args, world, device)
+        single = report(mk, 1, k1, w1, s1, args, world, device)
+        launches += l1
 
     if rank != 0:
         return
-    peak, peak_kind = measured_peak_gbs()
-    bpt = bytes_per_token(mk)
-    launch_s = statistics.mean(kernel_ms) / 1e3
-    achieved = bpt * GENERATE / launch_s / 1e9
-    median_step_us = statistics.median(step_ns) / 1e3
     out = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": head["value"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": args.quant if args.quant == "int8" else "bf16", "data": "synthetic",
         "config": {"workload": "qwen3.5-0.8b hybrid (24 layers, hidden 1024, vocab 151936), "
-                               f"{args.quant} weights, batch 1, replicas only",
-                   "prompt_tokens": PROMPT, "decode_steps_per_bench_step": GENERATE, "kv_dtype": args.kv_dtype,
+                               f"{args.quant} weights, batch {args.batch}, replicas only",
+                   "batch": args.batch, "prompt_tokens": PROMPT, "decode_steps_per_bench_step": GENERATE,
+                   "kv_dtype": args.kv_dtype,
                    "l2": "weights streamed per decode step (0.65 GB int8) exceed the 126 MB L2; no flush needed",
-                   "median_decode_step_us": median_step_us, "bytes_per_token": bpt},
+                   "median_decode_step_us": head["median_decode_step_us"],
+                   "bytes_per_decode_step": head["bytes_per_decode_step"]},
         "clocks": clocks,
-        "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 + 4, "d2h_bytes_per_step": 8 * GENERATE + 32 + 4},
+        "e2e": head["e2e"],
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
-                     "traffic": NCU_DRAM_BYTES_PER_TOKEN * GENERATE if NCU_DRAM_BYTES_PER_TOKEN else None,
-                     "algorithmic_bytes_per_launch": bpt * GENERATE},
+        "roofline": head["roofline"],
     }
+    if single:
+        out["batch1"] = {"value": single["value"], "unit": "tok/s", "ms_per_step": single["ms_per_step"],
+                         "median_decode_step_us": single["median_decode_step_us"],
+                         "bytes_per_decode_step": single["bytes_per_decode_step"], "e2e": single["e2e"],
+                         "roofline": single["roofline"]}
     if world == 1 and not args.no_cpu_baseline:
         n_prompt, n_decode = 32, 48
         rate = cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode)[0]
         out["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"{n_prompt}-token prompt then {n_decode} greedy steps, full depth, "
-                                         "int8-dequantised weights in fp32"}
+                               "sample": f"{n_prompt}-token prompt then {n_decode} greedy steps of one sequence, "
+                                         "full depth, int8-dequantised weights in fp32"}
     print(json.dumps(out))
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -54,7 +54,8 @@ enum {
     MK_L_K_CACHE,       /* paged: [n_blocks, kv_heads, MK_KV_BLOCK, head_dim], bf16 or fp32   */
     MK_L_V_CACHE,
     MK_L_KIND,          /* 0 = Gated DeltaNet, 1 = gated full attention (a value, not a pointer) */
-    MK_L_RESERVED0, MK_L_RESERVED1,
+    MK_L_CONV_HIST_B,   /* fp32 [batch, 16 heads, 384 channels, 8]: conv history of batched decoding (0 if unused) */
+    MK_L_RESERVED1,
     MK_LAYER_FIELDS
 };
 
@@ -177,7 +178,9 @@ int mk_launch_static(mk_engine* e, const mk_launch_args* args, void* stream);
  * The engine's buffers are those of mk_set_params with every per-sequence buffer `batch` times as
  * large, sequence-major: the hand-off words (MK_G_XL, MK_G_PROJL, MK_G_MIXL, MK_G_ACTL [batch, width],
  * MK_G_LML [batch, grid, 2], MK_G_ATTN_PART [batch, kv_heads, MK_Q_MAX_SPLITS, MK_Q_PART_STRIDE]), the
- * DeltaNet state and conv history of every layer, and MK_G_BLOCK_TABLE [batch, max_seq / 64] with page
+ * DeltaNet state (MK_L_STATE [batch, 16, 128, 128]) and the batched conv history (MK_L_CONV_HIST_B: a
+ * DeltaNet task here is one head of one sequence, so the history is kept per head, not per task of
+ * MK_L_CONV_HIST) of every layer, and MK_G_BLOCK_TABLE [batch, max_seq / 64] with page
  * numbers into one pool per layer (batch * max_seq / 64 <= 512 pages).  A sequence that has produced a
  * stop id, or has run its n_total steps, keeps stepping until all have (its outputs are to be
  * ignored), but its DeltaNet state and conv history stay as its last accepted token left them. */

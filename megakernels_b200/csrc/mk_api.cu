@@ -60,6 +60,7 @@ static void fill_layer(LayerP& L, const int64_t* f) {
     L.dt_bias = as_ptr<const float*>(f[MK_L_DT_BIAS]);
     L.gdn_norm = as_ptr<const float*>(f[MK_L_GDN_NORM]);
     L.conv_hist = as_ptr<float*>(f[MK_L_CONV_HIST]);
+    L.conv_hist_b = as_ptr<float*>(f[MK_L_CONV_HIST_B]);
     L.state = as_ptr<float*>(f[MK_L_STATE]);
     L.state_bak = as_ptr<float*>(f[MK_L_STATE_BAK]);
     L.q_norm = as_ptr<const float*>(f[MK_L_Q_NORM]);
@@ -414,6 +415,9 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     const uint64_t ops = (uint64_t)e->desc.n_layers * OPS_PER_LAYER + 1;
     if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
         return fail(MK_ERR_BADARG, "mk_launch_batch: epoch counter exhausted or zero; reset the engine");
+    for (int l = 0; l < e->desc.n_layers; l++)
+        if (e->host.layer[l].kind == 0 && !e->host.layer[l].conv_hist_b)
+            return fail(MK_ERR_BADARG, "mk_launch_batch: layer %d has no batched conv history (MK_L_CONV_HIST_B)", l);
 
     BatchArgs A;
     memset(&A, 0, sizeof A);
@@ -476,7 +480,7 @@ extern "C" int64_t mk_query(int what) {
         case MK_Q_LAYER_FIELDS: return MK_LAYER_FIELDS;
         case MK_Q_GLOBAL_FIELDS: return MK_GLOBAL_FIELDS;
         case MK_Q_SLOT_BYTES: return SLOT_BYTES;
-        case MK_Q_STAGES: return NSTAGE;
+        case MK_Q_STAGES: return Geo<1>::NS;
         case MK_Q_MAX_LM_ROWS: return MAX_LM_ROWS;
         case MK_Q_MAX_BATCH: return NB;
         case MK_Q_BATCH_SMEM_BYTES: return GeoB::SMEM;

@@ -8,10 +8,13 @@
 //     two unsigned); byte d of sequence j is plane d * 8 + j, so digit d of all sequences is one
 //     s8 x s8 (top) or s8 x u8 (lower) MMA.  Integer MMAs are exact; the digits recombine in fp32.
 //   * Every warp owns a contiguous k-slice of the rows and stages exactly the inputs of that slice,
-//     with its own power-of-two scale per sequence (undone on its partial sums), so nothing block-wide
-//     sits between the arrival of the inputs and the MMAs.  The 1 / rms factor of an RMSNorm is
-//     applied to the finished rows from per-warp sums of squares.
-//   * The DeltaNet task of a CTA runs its head slice for every sequence; attention gives each
+//     with its own power-of-two scale per pair of sequences (undone on its partial sums), so nothing
+//     block-wide sits between the arrival of the inputs and the MMAs.  The 1 / rms factor of an
+//     RMSNorm is applied to the finished rows from per-warp sums of squares.
+//   * Every CTA stages all inputs of all sequences, so whatever can be done once is done by the op
+//     that produces a value: the mixers publish gated outputs (DeltaNet: per-head RMSNorm times
+//     silu(z); attention: times the sigmoid gate), and the out-projection only quantises them.
+//   * A DeltaNet task is one head of one sequence (16 x sequences tasks); attention gives each
 //     sequence an equal group of CTAs, each group running the single-sequence split-K op on its own
 //     block table; the LM head keeps one best key per sequence.
 // Sequences advance in lockstep: step s feeds position pos0[j] + s of sequence j.  A sequence whose
@@ -68,14 +71,40 @@ __device__ __forceinline__ void mma_s8u8(int (&c)[4], uint32_t a0, uint32_t a1, 
 // integers stay inside the signed 24-bit range.
 __device__ __forceinline__ float fixed_scale24(float mx) { return fixed_scale(mx) * 0.03125f; }
 
-// Stage inputs k, k + 1 of sequence `seq` into the three digit planes.
+// Stage inputs k, k + 1 of sequence `seq` into the three digit planes: byte d of both integers is one
+// byte permute and one 16-bit store.
 __device__ __forceinline__ void stage_pair_b(uint8_t* xq, int rb, int seq, int k, float v0, float v1, float scale) {
-    const int a = __float2int_rn(v0 * scale), b = __float2int_rn(v1 * scale);
+    const uint32_t a = (uint32_t)__float2int_rn(v0 * scale), b = (uint32_t)__float2int_rn(v1 * scale);
+    uint8_t* p = xq + (size_t)seq * rb + k;
+    *reinterpret_cast<uint16_t*>(p) = (uint16_t)__byte_perm(a, b, 0x0040);
+    *reinterpret_cast<uint16_t*>(p + (size_t)NB * rb) = (uint16_t)__byte_perm(a, b, 0x0051);
+    *reinterpret_cast<uint16_t*>(p + (size_t)2 * NB * rb) = (uint16_t)__byte_perm(a, b, 0x0062);
+}
+
+// Sums of eight values per lane over the warp in 9 shuffles instead of 40: every step halves the set a
+// lane carries.  Returns the total of value `warp_sum8_index(lane)`; lanes that agree in their low
+// three bits hold the same total.
+__device__ __forceinline__ int warp_sum8_index(int lane) { return ((lane & 1) << 2) | (lane & 2) | ((lane & 4) >> 2); }
+__device__ __forceinline__ float warp_sum8(const float (&v)[8], int lane) {
+    float a[4], b[2], r;
+    const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4;
 #pragma unroll
-    for (int d = 0; d < 3; d++) {
-        const int da = (a >> (8 * d)) & 255, db = (b >> (8 * d)) & 255;
-        *reinterpret_cast<uint16_t*>(xq + (size_t)(d * NB + seq) * rb + k) = (uint16_t)(da | (db << 8));
+    for (int i = 0; i < 4; i++) {
+        const float send = b0 ? v[i] : v[i + 4], keep = b0 ? v[i + 4] : v[i];
+        a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
     }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const float send = b1 ? a[i] : a[i + 2], keep = b1 ? a[i + 2] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    {
+        const float send = b2 ? b[0] : b[1], keep = b2 ? b[1] : b[0];
+        r = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    r += __shfl_xor_sync(0xffffffffu, r, 8);
+    r += __shfl_xor_sync(0xffffffffu, r, 16);
+    return r;
 }
 
 // K-blocks [kb0, kb1) of a row of `nkb` 64-byte k-blocks that warp `warp` owns.
@@ -120,7 +149,8 @@ __device__ __forceinline__ void mma_block_b(const uint8_t* buf, const uint8_t* x
 }
 
 // Streams this CTA's rows [r0, r1) of a matrix with `rb`-byte int8 rows out of the ring, for every
-// sequence.  The warp has staged its k-slice of the planes and left its inverse scales in `wsc_s`.
+// sequence.  The warp has staged its k-slice of the planes and left the inverse scale of each pair of
+// sequences in `wsc_s`.
 //   STREAM = false  (layer GEMVs, at most 64 rows per CTA): one barrier after the last chunk, then
 //                   warps 2j and 2j + 1 finish sequence j's rows, then one more barrier (the partial
 //                   sums and scales are free again);
@@ -138,7 +168,7 @@ __device__ __forceinline__ bool gemv_b(Ctx& c, int r0, int r1, int rb, const flo
     warp_kslice(rb >> 6, c.warp, kb0, kb1);
     const int g = c.lane >> 2, t = c.lane & 3;
     const uint8_t* xrow = c.sm.xq + (size_t)g * rb + t * 16;             // plane d * 8 + g = column g of digit d
-    const float is0 = c.sm.wsc_s[c.warp * NB + 2 * t], is1 = c.sm.wsc_s[c.warp * NB + 2 * t + 1];
+    const float is0 = c.sm.wsc_s[c.warp * 4 + t], is1 = is0;             // columns 2t, 2t + 1 are sequence pair t
     const float* scales = STREAM ? c.sm.scale_s + 2 * SCALE_BODY : c.sm.scale_s + (c.gemv_n & 1) * SCALE_BODY;
     c.gemv_n++;
     auto post_factor = [&](int j) {
@@ -219,22 +249,24 @@ __device__ __forceinline__ bool gemv_b(Ctx& c, int r0, int r1, int rb, const flo
 }
 
 // RMSNorm input of every sequence, warp-local: this thread's elements 2 tid, 2 tid + 1 of x (1 + w)
-// go into the planes of the warp's 64-element k-slice; the warp's sum of squares goes to `ssq_s`.
+// go into the planes of the warp's 64-element k-slice with one scale for all sequences; the warp's
+// sums of squares go to `ssq_s`.
 template <class S>
 __device__ __forceinline__ void stage_rms_b(Ctx& c, const float (&x)[NB][2], float2 g) {
     static_assert(S::HID == 2 * NCT, "two residual elements per consumer thread");
     const int k = 2 * c.tid;
+    float ss[NB], mx = 0.f;
 #pragma unroll
     for (int j = 0; j < NB; j++) {
-        const float y0 = x[j][0] * (1.0f + g.x), y1 = x[j][1] * (1.0f + g.y);
-        const float ss = warp_sum(x[j][0] * x[j][0] + x[j][1] * x[j][1]);
-        const float scale = fixed_scale24(warp_max(fmaxf(fabsf(y0), fabsf(y1))));
-        stage_pair_b(c.sm.xq, S::HID, j, k, y0, y1, scale);
-        if (c.lane == 0) {
-            c.sm.ssq_s[j * NCW + c.warp] = ss;
-            c.sm.wsc_s[c.warp * NB + j] = 1.0f / scale;
-        }
+        ss[j] = x[j][0] * x[j][0] + x[j][1] * x[j][1];
+        mx = fmaxf(mx, fmaxf(fabsf(x[j][0] * (1.0f + g.x)), fabsf(x[j][1] * (1.0f + g.y))));
     }
+    const float scale = fixed_scale24(warp_max(mx));
+#pragma unroll
+    for (int j = 0; j < NB; j++) stage_pair_b(c.sm.xq, S::HID, j, k, x[j][0] * (1.0f + g.x), x[j][1] * (1.0f + g.y), scale);
+    const float tot = warp_sum8(ss, c.lane);
+    if (c.lane < 8) c.sm.ssq_s[warp_sum8_index(c.lane) * NCW + c.warp] = tot;
+    if (c.lane < 4) c.sm.wsc_s[c.warp * 4 + c.lane] = 1.0f / scale;
     __syncwarp();
 }
 
@@ -250,109 +282,105 @@ __device__ __forceinline__ void wait_residual_b(Ctx& c, const u64* xbuf, uint32_
 }
 
 // ---- Gated DeltaNet recurrence, every sequence ---------------------------------------------------------
-// Task t < GDN_TASKS as in the single-sequence op (head t / 8, value columns [16 (t % 8), +16)); the
-// task runs its slice for each sequence on that sequence's state and conv history.  A sequence in
-// `frozen` (it has produced a stop token) still gets outputs, so that nothing downstream stalls, but
-// its state and history stay as the last accepted token left them.
+// Task t < 16 * sequences: head t % 16 of sequence t / 16, all 128 value columns (warp w owns columns
+// 8w .. 8w + 7; a lane holds 4 consecutive key indices of each).  One CTA sees the whole head, so the
+// gated per-head RMSNorm (norm weight, silu(z)) is applied here, once, instead of by every CTA's
+// out-projection prologue.  A sequence in `frozen` (it has produced a stop token or run its steps)
+// still gets outputs, so that nothing downstream stalls, but its state and history stay as the last
+// accepted token left them.
 template <class S>
 __device__ bool gdn_batch(Ctx& c, const Params& P, const LayerP& L, const BatchArgs& A, int step, unsigned frozen,
                           uint32_t e_proj, uint32_t e_out, int op) {
-    static_assert(S::GDN_SLICE == NCW && S::LIN_DK == 128, "one warp per value column, 4 keys per lane");
-    constexpr int SL = S::LIN_DV / S::GDN_SLICE;
-    if (c.cta >= S::GDN_TASKS) return false;
-    const int nb = A.nb;
-    const int h = c.cta / SL, sl = c.cta % SL;
-    const int vcol = sl * S::GDN_SLICE + c.warp;
-    constexpr int NCH = 2 * S::LIN_DK + S::GDN_SLICE;           // 272 conv channels this task needs
-    constexpr int QS = NCH + 8;                                 // per-sequence stride of the scratch
-    constexpr size_t STATE_SEQ = (size_t)S::LIN_H * S::LIN_DV * S::LIN_DK;
-    constexpr size_t HIST_SEQ = (size_t)S::GDN_TASKS * NCH * CONV_RING;
-    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);           // per sequence: [q 128 | k 128 | v 16 | b | a]
-    const size_t soff = ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
-    // Every sequence's state rows are requested before the wait, as asynchronous copies into shared
-    // memory (behind the conv scratch), so that they cost no registers while the projection is awaited.
-    float4* st_s = reinterpret_cast<float4*>(c.sm.xq + 16384);  // [sequence][consumer thread]
-    static_assert(NB * QS * 4 <= 16384 && 16384 + NB * NCT * 16 <= GeoB::XQ, "mixer scratch fits the plane area");
-    for (int q = 0; q < nb; q++)
-        cp_async16(st_s + q * NCT + c.tid, L.state + q * STATE_SEQ + soff);
+    static_assert(S::LIN_DK == 128 && S::LIN_DV == 128 && NCW == 16, "8 value columns per warp, 4 keys per lane");
+    if (c.cta >= S::LIN_H * A.nb) return false;
+    const int q = c.cta / S::LIN_H, h = c.cta % S::LIN_H;
+    const bool keep = !((frozen >> q) & 1u);
+    const int pos = A.pos0[q] + step;
+    constexpr int NCH = 2 * S::LIN_DK + S::LIN_DV;              // 384 conv channels of the head: q | k | v
+    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);           // [q 128 | k 128 | v 128 | z 128 | b | a]
+    float4* st_s = reinterpret_cast<float4*>(c.sm.xq + 4096);   // [value column][lane]: the head's 64 KB of state
+    float* red = c.sm.red_s + (c.red_n++ & 1) * (2 * NCW);
+    static_assert(4096 + S::LIN_DV * 32 * 16 <= GeoB::XQ, "mixer scratch fits the plane area");
+    const u64* proj = P.projl + (size_t)q * S::PROJ_MAX;
+    float* state = L.state + (size_t)q * S::LIN_H * S::LIN_DV * S::LIN_DK + (size_t)h * S::LIN_DV * S::LIN_DK;
+    // The state rows are requested before the wait, as asynchronous copies into shared memory, so that
+    // they cost no registers while the projection is awaited.
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int vcol = c.warp * 8 + i;
+        cp_async16(st_s + vcol * 32 + c.lane, state + (size_t)vcol * S::LIN_DK + 4 * c.lane);
+    }
     cp_async_commit();
     const float a_log = L.A_log[h], dt_bias = L.dt_bias[h];
     if (c.tid < NCH) {
-        int ch;
-        if (c.tid < S::LIN_DK) ch = h * S::LIN_DK + c.tid;
-        else if (c.tid < 2 * S::LIN_DK) ch = S::LIN_QK + h * S::LIN_DK + (c.tid - S::LIN_DK);
-        else ch = 2 * S::LIN_QK + h * S::LIN_DV + sl * S::GDN_SLICE + (c.tid - 2 * S::LIN_DK);
+        const int ch = (c.tid >> 7) * S::LIN_QK + h * S::LIN_DK + (c.tid & 127);   // q, k and v blocks are 2048 channels each
         const float4 taps = *reinterpret_cast<const float4*>(L.conv_w + 4 * ch);
-        u64 w[NB];
-#pragma unroll
-        for (int q = 0; q < NB; q++) w[q] = q < nb ? ll_load(P.projl + (size_t)q * S::PROJ_MAX + ch) : 0;
-        Spin sp;
-        while (true) {
-            bool ok = true;
-#pragma unroll
-            for (int q = 0; q < NB; q++)
-                if (q < nb && (uint32_t)(w[q] >> 32) != e_proj) {
-                    ok = false;
-                    w[q] = ll_load(P.projl + (size_t)q * S::PROJ_MAX + ch);
-                }
-            if (ok) break;
-            if (MK_SPIN_FAIL(c, sp, W_PROJ)) {
-                c.dead = true;
-                break;
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < NB; q++) {
-            if (q < nb) {
-                const int pos = A.pos0[q] + step;
-                float* hist = L.conv_hist + q * HIST_SEQ + ((size_t)c.cta * NCH + c.tid) * CONV_RING;
-                const float h3 = hist[(pos - 3) & (CONV_RING - 1)];
-                const float h2 = hist[(pos - 2) & (CONV_RING - 1)];
-                const float h1 = hist[(pos - 1) & (CONV_RING - 1)];
-                const float cur = __uint_as_float((uint32_t)w[q]);
-                float a = h3 * taps.x;
-                a = fmaf(h2, taps.y, a);
-                a = fmaf(h1, taps.z, a);
-                a = fmaf(cur, taps.w, a);
-                qkv_s[q * QS + c.tid] = silu_f(a);
-                if (!((frozen >> q) & 1u)) hist[pos & (CONV_RING - 1)] = cur;
-            }
-        }
-    } else if (c.tid < NCH + 2) {
-        const int off = (c.tid == NCH ? S::B_OFF : S::A_OFF) + h;
-        for (int q = 0; q < nb; q++)
-            qkv_s[q * QS + c.tid] = ll_wait(c, P.projl + (size_t)q * S::PROJ_MAX + off, e_proj, W_PROJ);
+        float* hist = L.conv_hist_b + (((size_t)q * S::LIN_H + h) * NCH + c.tid) * CONV_RING;
+        const float h3 = hist[(pos - 3) & (CONV_RING - 1)];
+        const float h2 = hist[(pos - 2) & (CONV_RING - 1)];
+        const float h1 = hist[(pos - 1) & (CONV_RING - 1)];
+        const float cur = ll_wait(c, proj + ch, e_proj, W_PROJ);
+        float a = h3 * taps.x;
+        a = fmaf(h2, taps.y, a);
+        a = fmaf(h1, taps.z, a);
+        a = fmaf(cur, taps.w, a);
+        qkv_s[c.tid] = silu_f(a);
+        if (keep) hist[pos & (CONV_RING - 1)] = cur;
+    } else {
+        const int i = c.tid - NCH;                               // 128 threads: z of the head, and b, a
+        qkv_s[NCH + i] = ll_wait(c, proj + S::Z_OFF + h * S::LIN_DV + i, e_proj, W_PROJ);
+        if (i < 2) qkv_s[NCH + S::LIN_DV + i] = ll_wait(c, proj + (i == 0 ? S::B_OFF : S::A_OFF) + h, e_proj, W_PROJ);
     }
-    cp_async_wait_all();                                        // this thread's own copies: no barrier needed for them
+    cp_async_wait_all();                                        // this thread's own copies
     consumer_sync();
     prof_stamp(c, op, 1);
-#pragma unroll 2
-    for (int q = 0; q < NB; q++) {
-        if (q < nb) {
-            const float4 st = st_s[q * NCT + c.tid];
-            float s0 = st.x, s1 = st.y, s2 = st.z, s3 = st.w;
-            const float* qs_ = qkv_s + q * QS;
-            const float4 q4 = *reinterpret_cast<const float4*>(qs_ + 4 * c.lane);
-            const float4 k4 = *reinterpret_cast<const float4*>(qs_ + S::LIN_DK + 4 * c.lane);
-            const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
-            const float kn = warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w);
-            const float qs = 0.08838834764831845f / fmaxf(sqrtf(qn), 1e-6f);
-            const float ks = 1.0f / fmaxf(sqrtf(kn), 1e-6f);
-            const float vval = qs_[2 * S::LIN_DK + c.warp];
-            const float beta = sigmoid_f(qs_[NCH]);
-            const float decay = expf(-expf(a_log) * softplus_f(qs_[NCH + 1] + dt_bias));
-            const float kx = k4.x * ks, ky = k4.y * ks, kz = k4.z * ks, kw = k4.w * ks;
-            s0 *= decay; s1 *= decay; s2 *= decay; s3 *= decay;
-            const float recalled = warp_sum(fmaf(s3, kw, fmaf(s2, kz, fmaf(s1, ky, s0 * kx))));
-            const float delta = (vval - recalled) * beta;
-            s0 = fmaf(kx, delta, s0);
-            s1 = fmaf(ky, delta, s1);
-            s2 = fmaf(kz, delta, s2);
-            s3 = fmaf(kw, delta, s3);
-            if (!((frozen >> q) & 1u)) *reinterpret_cast<float4*>(L.state + q * STATE_SEQ + soff) = make_float4(s0, s1, s2, s3);
-            const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
-            if (c.lane == 0) ll_store(P.mixl + (size_t)q * S::MIX + h * S::LIN_DV + vcol, e_out, o);
-        }
+    const float4 q4 = *reinterpret_cast<const float4*>(qkv_s + 4 * c.lane);
+    const float4 k4 = *reinterpret_cast<const float4*>(qkv_s + S::LIN_DK + 4 * c.lane);
+    const float qn = warp_sum(q4.x * q4.x + q4.y * q4.y + q4.z * q4.z + q4.w * q4.w);
+    const float kn = warp_sum(k4.x * k4.x + k4.y * k4.y + k4.z * k4.z + k4.w * k4.w);
+    // x / max(|x|, 1e-6), and the 1/sqrt(dk) query scale
+    const float qs = 0.08838834764831845f / fmaxf(sqrtf(qn), 1e-6f);
+    const float ks = 1.0f / fmaxf(sqrtf(kn), 1e-6f);
+    const float beta = sigmoid_f(qkv_s[NCH + S::LIN_DV]);
+    const float decay = expf(-expf(a_log) * softplus_f(qkv_s[NCH + S::LIN_DV + 1] + dt_bias));
+    const float kx = k4.x * ks, ky = k4.y * ks, kz = k4.z * ks, kw = k4.w * ks;
+    // Two passes over the state rows in shared memory rather than 32 registers of state per lane.
+    float rec[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float4 sv = st_s[(c.warp * 8 + i) * 32 + c.lane];
+        rec[i] = fmaf(sv.w * decay, kw, fmaf(sv.z * decay, kz, fmaf(sv.y * decay, ky, sv.x * decay * kx)));
+    }
+    // what the decayed state recalls for k, per column: lane l ends up with column warp_sum8_index(l)
+    const float recalled = warp_sum8(rec, c.lane);
+    const int mine = warp_sum8_index(c.lane);
+    const float delta_mine = (qkv_s[2 * S::LIN_DK + c.warp * 8 + mine] - recalled) * beta;
+    float out[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        // column i's delta sits in the lanes whose index maps to i: lane ((i & 1) << 2) | (i & 2) | ((i & 4) >> 2)
+        const float delta = __shfl_sync(0xffffffffu, delta_mine, ((i & 1) << 2) | (i & 2) | ((i & 4) >> 2));
+        float4 sv = st_s[(c.warp * 8 + i) * 32 + c.lane];
+        sv.x = fmaf(kx, delta, sv.x * decay);
+        sv.y = fmaf(ky, delta, sv.y * decay);
+        sv.z = fmaf(kz, delta, sv.z * decay);
+        sv.w = fmaf(kw, delta, sv.w * decay);
+        if (keep) *reinterpret_cast<float4*>(state + (size_t)(c.warp * 8 + i) * S::LIN_DK + 4 * c.lane) = sv;
+        out[i] = fmaf(sv.w, q4.w, fmaf(sv.z, q4.z, fmaf(sv.y, q4.y, sv.x * q4.x)));
+    }
+    const float o = warp_sum8(out, c.lane) * qs;                 // output of column `mine`
+    // per-head RMSNorm over the 128 columns: lanes 0..7 of the 16 warps hold them
+    const float osq = warp_sum(c.lane < 8 ? o * o : 0.f);
+    if (c.lane == 0) red[c.warp] = osq;
+    consumer_sync();
+    if (c.lane < 8) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < NCW; w++) tot += red[w];
+        const float inv = rsqrtf(tot * (1.0f / S::LIN_DV) + S::EPS);
+        const int vcol = c.warp * 8 + mine;
+        const float m = o * inv * L.gdn_norm[vcol] * silu_f(qkv_s[NCH + vcol]);
+        ll_store(P.mixl + (size_t)q * S::MIX + h * S::LIN_DV + vcol, e_out, m);
     }
     prof_stamp(c, op, 2);
     consumer_sync();  // the scratch aliases the GEMV input planes that the next prologue writes
@@ -409,7 +437,7 @@ __device__ __forceinline__ bool run_layer_b(Ctx& c, const Params& P, const Layer
         if (q < nb) {
             const AttnView view = {c.cta - q * per, per, P.projl + (size_t)q * S::PROJ_MAX, P.mixl + (size_t)q * S::MIX,
                                    P.attn_part + (size_t)q * S::NKV * MAX_SPLITS * S::PART_STRIDE,
-                                   c.sm.bt_s + q * (P.max_seq / KV_BLOCK)};
+                                   c.sm.bt_s + q * (P.max_seq / KV_BLOCK), true};
             had_task = attn_op<S, KVF32, 1>(c, P, L, view, A.pos0[q] + step, eA, eB, op0 + 1);
         }
     } else {
@@ -422,52 +450,30 @@ __device__ __forceinline__ bool run_layer_b(Ctx& c, const Params& P, const Layer
         prof_stamp(c, op, 0);
         scale_prefetch(c, L.s_out, xr0, xr1, false);
         if (!had_task) gate_on_samples(c, P.mixl + (size_t)(nb - 1) * S::MIX, S::MIX, eB);
-        // a lane stages 4 consecutive mixer outputs; the warp's 128 are one DeltaNet head and its k-slice
+        // a lane stages 4 consecutive (already gated) mixer outputs of every sequence: the warp's 128 are its k-slice
         const int k = 4 * c.tid;
-        const float4 gw = attn ? make_float4(0.f, 0.f, 0.f, 0.f)
-                               : *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
 #pragma unroll 1
-        for (int jj = 0; jj < NB; jj += 2) {
-            if (jj >= nb) {                         // planes of absent sequences are zero
-#pragma unroll
-                for (int u = 0; u < 2; u++) {
-                    stage_pair_b(c.sm.xq, S::MIX, jj + u, k, 0.f, 0.f, 1.f);
-                    stage_pair_b(c.sm.xq, S::MIX, jj + u, k + 2, 0.f, 0.f, 1.f);
-                    if (c.lane == 0) c.sm.wsc_s[c.warp * NB + jj + u] = 1.f;
-                }
-                continue;
-            }
+        for (int jj = 0; jj < NB; jj += 4) {        // four sequences per round: 8 word pairs in flight
             float v[16];
-            // pair i of the round: sequence jj + i / 4; pairs 0, 1 are mixer outputs, 2, 3 the gate or z
             const u64* mix0 = P.mixl + (size_t)jj * S::MIX + k;
-            const u64* aux0 = P.projl + (size_t)jj * S::PROJ_MAX +
-                              (attn ? (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD) : S::Z_OFF + k);
             ll_wait_pairs_fn<8>(c,
                                 [&](int i) -> const u64* {
-                                    if (jj + (i >> 2) >= nb) return nullptr;
-                                    return ((i & 2) ? aux0 + (size_t)(i >> 2) * S::PROJ_MAX : mix0 + (size_t)(i >> 2) * S::MIX) + 2 * (i & 1);
+                                    if (jj + (i >> 1) >= nb) return nullptr;
+                                    return mix0 + (size_t)(i >> 1) * S::MIX + 2 * (i & 1);
                                 },
-                                [&](int i) { return (i & 2) ? eA : eB; }, v, W_MIX);
+                                [&](int) { return eB; }, v, W_MIX);
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                const float* vj = v + 8 * u;
-                float m[4];
-                if (attn) {
+            for (int u = 0; u < 2; u++) {           // one scale per pair of sequences
+                float mx = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) m[i] = vj[i] * sigmoid_f(vj[4 + i]);
-                } else {
-                    const float ss = warp_sum(vj[0] * vj[0] + vj[1] * vj[1] + vj[2] * vj[2] + vj[3] * vj[3]);
-                    const float inv = rsqrtf(ss * (1.0f / S::LIN_DV) + S::EPS);
-                    m[0] = vj[0] * inv * gw.x * silu_f(vj[4]);
-                    m[1] = vj[1] * inv * gw.y * silu_f(vj[5]);
-                    m[2] = vj[2] * inv * gw.z * silu_f(vj[6]);
-                    m[3] = vj[3] * inv * gw.w * silu_f(vj[7]);
-                }
-                const float mx = fmaxf(fmaxf(fabsf(m[0]), fabsf(m[1])), fmaxf(fabsf(m[2]), fabsf(m[3])));
+                for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[8 * u + i]));
                 const float scale = fixed_scale24(warp_max(mx));
-                stage_pair_b(c.sm.xq, S::MIX, jj + u, k, m[0], m[1], scale);
-                stage_pair_b(c.sm.xq, S::MIX, jj + u, k + 2, m[2], m[3], scale);
-                if (c.lane == 0) c.sm.wsc_s[c.warp * NB + jj + u] = 1.0f / scale;
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    stage_pair_b(c.sm.xq, S::MIX, jj + 2 * u + i, k, v[8 * u + 4 * i], v[8 * u + 4 * i + 1], scale);
+                    stage_pair_b(c.sm.xq, S::MIX, jj + 2 * u + i, k + 2, v[8 * u + 4 * i + 2], v[8 * u + 4 * i + 3], scale);
+                }
+                if (c.lane == 0) c.sm.wsc_s[c.warp * 4 + (jj >> 1) + u] = 1.0f / scale;
             }
         }
         __syncwarp();
@@ -509,30 +515,31 @@ __device__ __forceinline__ bool run_layer_b(Ctx& c, const Params& P, const Layer
         int kb0, kb1;
         warp_kslice(S::INTER / 64, c.warp, kb0, kb1);
         const int e0 = kb0 * 64, e1 = kb1 * 64;
+        const int np = (e1 - e0) / 64;                           // 3 or 4 pairs per lane and sequence
+        // Two sequences per round (8 word pairs in flight).  Keeping the next round's loads in flight
+        // while this one is staged measured slower: the registers it takes end up as spills.
 #pragma unroll 1
         for (int jj = 0; jj < NB; jj += 2) {
             float v[16];
             const u64* act0 = P.actl + (size_t)jj * S::INTER + e0 + 2 * c.lane;
-            const int np = (e1 - e0) / 64;                       // 3 or 4 pairs per lane and sequence
             ll_wait_pairs_fn<8>(c,
                                 [&](int i) -> const u64* {
                                     if (jj + (i >> 2) >= nb || (i & 3) >= np) return nullptr;
                                     return act0 + (size_t)(i >> 2) * S::INTER + 64 * (i & 3);
                                 },
                                 [&](int) { return eD; }, v, W_ACT);
+            float mx = 0.f;
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
-                float mx = 0.f;
+            for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(v[i]));
+            const float scale = fixed_scale24(warp_max(mx));        // one scale for the pair of sequences
 #pragma unroll
-                for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[8 * u + i]));
-                const float scale = fixed_scale24(warp_max(mx));
+            for (int u = 0; u < 2; u++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const int k = e0 + 2 * c.lane + 64 * i;
                     if (k < e1) stage_pair_b(c.sm.xq, S::INTER, jj + u, k, v[8 * u + 2 * i], v[8 * u + 2 * i + 1], scale);
                 }
-                if (c.lane == 0) c.sm.wsc_s[c.warp * NB + jj + u] = 1.0f / scale;
-            }
+            if (c.lane == 0) c.sm.wsc_s[c.warp * 4 + (jj >> 1)] = 1.0f / scale;
         }
         __syncwarp();
         prof_stamp(c, op, 1);

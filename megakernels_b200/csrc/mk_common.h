@@ -9,7 +9,7 @@ constexpr int NCW = 16;                   // consumer warps per CTA
 constexpr int NCT = NCW * 32;             // consumer threads
 constexpr int NTHREADS = NCT + 32;        // + one producer warp
 constexpr int SLOT_BYTES = 32768;         // one ring slot: 32/16/9 int8 rows or 16/8/4 bf16 rows of K = 1024/2048/3584
-constexpr int NSTAGE = 6;                 // ring depth: 192 KB of weights in flight per SM
+constexpr int NSTAGE = 6;                 // ring depth of the bandwidth probe: 192 KB in flight per SM (the decode kernels choose their own)
 constexpr int MAX_LAYERS = 64;
 constexpr int MAX_ENGINES = 2;            // constant-memory parameter slots
 constexpr int KV_BLOCK = 64;              // positions per KV page
@@ -47,7 +47,7 @@ struct Qwen35_08B {
 };
 
 constexpr int MAX_BLOCKS = 512;                                    // KV pages per sequence (max_seq <= 32768)
-constexpr int SMEM_BYTES = NSTAGE * SLOT_BYTES + 3 * 2 * 3584 + NCW * 64 * 4 + MAX_BLOCKS * 4 + 2048 + 2048;   // == Geo<1>::SMEM == Geo<2>::SMEM
+constexpr int SMEM_BYTES = NSTAGE * SLOT_BYTES + 3 * 2 * 3584 + NCW * 64 * 4 + MAX_BLOCKS * 4 + 2048 + 2048;   // upper bound of the single-sequence kernels' dynamic shared memory
 
 // ---- device-side parameter block (one per engine, in constant memory) --------------------------
 struct LayerP {
@@ -66,6 +66,7 @@ struct LayerP {
     const float* dt_bias;
     const float* gdn_norm;
     float* conv_hist;
+    float* conv_hist_b;   // batched decoding: [sequence][head][q 128 | k 128 | v 128][CONV_RING]
     float* state;
     float* state_bak;
     const float* q_norm;

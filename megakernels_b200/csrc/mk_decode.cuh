@@ -237,6 +237,45 @@ __device__ __forceinline__ void ll_wait_pairs_fn(Ctx& c, Addr&& addr, Epoch&& ep
     }
 }
 
+// The two halves of `ll_wait_pairs_fn`, for callers that keep the next round's loads in flight while
+// they work on the current one: issue the loads; later, re-load what was not ready until all is.
+template <int N, class Addr>
+__device__ __forceinline__ void ll_issue_fn(Addr&& addr, u64 (&w)[2 * N]) {
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        w[2 * i] = w[2 * i + 1] = 0;
+        if (const u64* p = addr(i)) ll_load2(p, w[2 * i], w[2 * i + 1]);
+    }
+}
+template <int N, class Addr, class Epoch>
+__device__ __forceinline__ void ll_complete_fn(Ctx& c, Addr&& addr, Epoch&& epoch, u64 (&w)[2 * N], float (&v)[2 * N],
+                                               int where) {
+    Spin s;
+    while (true) {
+        bool ok = true;
+#pragma unroll
+        for (int i = 0; i < N; i++) {
+            const u64* p = addr(i);
+            const uint32_t e = epoch(i);
+            if (p && ((uint32_t)(w[2 * i] >> 32) != e || (uint32_t)(w[2 * i + 1] >> 32) != e)) {
+                ok = false;
+                ll_load2(p, w[2 * i], w[2 * i + 1]);
+            }
+        }
+        if (ok) break;
+        if (MK_SPIN_FAIL(c, s, where)) {
+            c.dead = true;
+            break;
+        }
+        poll_backoff(s.it);
+    }
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        v[2 * i] = __uint_as_float((uint32_t)w[2 * i]);
+        v[2 * i + 1] = __uint_as_float((uint32_t)w[2 * i + 1]);
+    }
+}
+
 // A CTA that had no part in the op it now waits for arrives early.  If all of its threads polled
 // right away, their loads would queue in front of the very stores they wait for.  Instead one warp
 // watches 32 words spread over the buffer, at a relaxed pace, and releases the CTA when all of them
@@ -260,13 +299,15 @@ __device__ __forceinline__ void gate_on_samples(Ctx& c, const u64* buf, int nwor
 }
 
 // Geometry that depends on how many tokens one pass over the weights serves (1: plain decode,
-// 2: a speculative cycle).  Two tokens need twice the input planes, so the ring gives up a stage.
+// 2: a speculative cycle).  Four ring stages (128 KB of weights in flight per SM) measured as fast as
+// six: what the ring does not take stays with the L1 cache, which the kernel's few spilled registers
+// and its read-only tables need.
 template <int T> struct Geo {
 #ifndef MK_NS1
-#define MK_NS1 6
+#define MK_NS1 4
 #endif
 #ifndef MK_NS2
-#define MK_NS2 5
+#define MK_NS2 4
 #endif
     static constexpr int NS = T == 1 ? MK_NS1 : MK_NS2;             // ring stages
     static constexpr int RING = NS * SLOT_BYTES;
@@ -393,6 +434,7 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
     }
     int ci[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
     float cf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const bool two = nr - b0 > 16;              // the second block has rows (projections that give a CTA 7 rows have none)
 #pragma unroll 2
     for (int kb = warp; kb < nkb; kb += NCW) {
         uint4 w[4], x = make_uint4(0, 0, 0, 0);
@@ -404,6 +446,7 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
         if (xlive) x = *reinterpret_cast<const uint4*>(xrow + kb * 64);
 #pragma unroll
         for (int b = 0; b < 2; b++) {           // two independent accumulator chains
+            if (b == 1 && !two) continue;
             if (Q8) {
                 mma_s8(ci[b], w[2 * b].x, w[2 * b + 1].x, w[2 * b].y, w[2 * b + 1].y, x.x, x.y);
                 mma_s8(ci[b], w[2 * b].z, w[2 * b + 1].z, w[2 * b].w, w[2 * b + 1].w, x.z, x.w);
@@ -835,6 +878,7 @@ struct AttnView {
     u64* mixl;              // mixer output words of that slot
     u64* part;              // split partials of that slot
     const int* bt;          // the sequence's block table (shared memory)
+    bool gate;              // publish o * sigmoid(gate) instead of o (otherwise the out-projection's prologue applies the gate)
 };
 
 template <class S, bool KVF32, int T>
@@ -857,6 +901,12 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
     float* vnew_s = knew_s + T * S::HD;                   // [T][256]
     float* sc_s = vnew_s + T * S::HD;                     // [T][4][ch] scores, then probabilities
     float* stat_s = c.sm.out_s;                           // [T][ m[4], l[4] ]
+    // sigmoid of the output gate of (token, head of the group, dim), for tasks that publish gated outputs
+    auto gate_of = [&](int tk, int head, int dim) {
+        if (!V.gate) return 1.0f;
+        return sigmoid_f(ll_wait(c, V.projl + (size_t)tk * S::PROJ_MAX + (size_t)(g * S::QPK + head) * 2 * S::HD + S::HD + dim,
+                                 e_proj, W_PROJ));
+    };
 
     const size_t kv_head_stride = (size_t)KV_BLOCK * S::HD;
     auto kv_elem = [&](int p) -> size_t {
@@ -1062,8 +1112,9 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
 #pragma unroll
         for (int tk = 0; tk < T; tk++) {
             u64* out = V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
-            ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
-            ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
+            ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp] * gate_of(tk, 2 * hp, d));
+            ll_store(out + (2 * hp + 1) * S::HD + d, e_out,
+                     acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1] * gate_of(tk, 2 * hp + 1, d));
         }
         // The appended K/V rows are read by other CTAs from the next step on.  They get there only
         // through words this CTA publishes after this fence, so the fence can sit off the critical path.
@@ -1090,8 +1141,9 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
         if (ns_t == 1) {                                             // everything this token sees is in split 0
             if (sp == 0) {
                 u64* out = V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD;
-                ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp]);
-                ll_store(out + (2 * hp + 1) * S::HD + d, e_out, acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1]);
+                ll_store(out + (2 * hp) * S::HD + d, e_out, acc[tk][0] / stat_s[tk * 8 + S::QPK + 2 * hp] * gate_of(tk, 2 * hp, d));
+                ll_store(out + (2 * hp + 1) * S::HD + d, e_out,
+                         acc[tk][1] / stat_s[tk * 8 + S::QPK + 2 * hp + 1] * gate_of(tk, 2 * hp + 1, d));
             }
             continue;
         }
@@ -1158,7 +1210,8 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
             Ls += __shfl_xor_sync(0xffffffffu, Ls, x);
             Os += __shfl_xor_sync(0xffffffffu, Os, x);
         }
-        if (live && sub == 0) ll_store(V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD + o, e_out, Os / Ls);
+        if (live && sub == 0)
+            ll_store(V.mixl + (size_t)tk * S::MIX + (size_t)(g * S::QPK) * S::HD + o, e_out, Os / Ls * gate_of(tk, h, o % S::HD));
     }
     __threadfence();      // K/V append before anything this CTA publishes later (see above)
     consumer_sync();      // scratch aliases the GEMV input planes that the next prologue writes
@@ -1186,12 +1239,9 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
         // the norm weights are requested before the wait so that their latency hides behind it
         const float2 nw = *reinterpret_cast<const float2*>(L.in_norm + 2 * c.tid);
         if (!x_in_regs) {
-            const u64* ptrs[T];
-            uint32_t eps[T];
             float v[2 * T];
-#pragma unroll
-            for (int j = 0; j < T; j++) { ptrs[j] = xbuf + (size_t)j * S::HID + 2 * c.tid; eps[j] = eA - 1; }
-            ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
+            const u64* base = xbuf + 2 * c.tid;
+            ll_wait_pairs_fn<T>(c, [&](int j) { return base + (size_t)j * S::HID; }, [&](int) { return eA - 1; }, v, W_X);
 #pragma unroll
             for (int j = 0; j < T; j++) { x[j][0] = v[2 * j]; x[j][1] = v[2 * j + 1]; }
         }
@@ -1204,7 +1254,7 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
     }
     // ---- B: mixer
     prof_stamp(c, op0 + 1, 0);
-    const AttnView view = {c.cta, c.grid, P.projl, P.mixl, P.attn_part, c.sm.bt_s};
+    const AttnView view = {c.cta, c.grid, P.projl, P.mixl, P.attn_part, c.sm.bt_s, false};
     const bool had_task = attn ? attn_op<S, KVF32, T>(c, P, L, view, pos, eA, eB, op0 + 1)
                                : gdn_op<S, T>(c, P, L, pos, eA, eB, op0 + 1, from_bak);
     prof_stamp(c, op0 + 1, 3);
@@ -1220,22 +1270,15 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
         const float4 gw = attn ? make_float4(0.f, 0.f, 0.f, 0.f)
                                : *reinterpret_cast<const float4*>(L.gdn_norm + (k % S::LIN_DV));
         {
-            const u64* ptrs[4 * T];
-            uint32_t eps[4 * T];
             float v[8 * T];
-#pragma unroll
-            for (int j = 0; j < T; j++) {
-                const u64* pj = P.projl + (size_t)j * S::PROJ_MAX;
-                const u64* aux = attn ? pj + (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD)   // sigmoid gate
-                                      : pj + S::Z_OFF + k;                                    // z
-                ptrs[4 * j] = P.mixl + (size_t)j * S::MIX + k;
-                ptrs[4 * j + 1] = ptrs[4 * j] + 2;
-                ptrs[4 * j + 2] = aux;
-                ptrs[4 * j + 3] = aux + 2;
-                eps[4 * j] = eps[4 * j + 1] = eB;
-                eps[4 * j + 2] = eps[4 * j + 3] = eA;
-            }
-            ll_wait_pairs<4 * T>(c, ptrs, eps, v, W_MIX);
+            // pair i: token i / 4; pairs 0, 1 of a token are mixer outputs, 2, 3 the sigmoid gate or z
+            const u64* mix0 = P.mixl + k;
+            const u64* aux0 = P.projl + (attn ? (k / S::HD) * 2 * S::HD + S::HD + (k % S::HD) : S::Z_OFF + k);
+            ll_wait_pairs_fn<4 * T>(c,
+                                    [&](int i) {
+                                        return ((i & 2) ? aux0 + (size_t)(i >> 2) * S::PROJ_MAX : mix0 + (size_t)(i >> 2) * S::MIX) + 2 * (i & 1);
+                                    },
+                                    [&](int i) { return (i & 2) ? eA : eB; }, v, W_MIX);
 #pragma unroll
             for (int j = 0; j < T; j++) {
                 const float* vj = v + 8 * j;
@@ -1282,12 +1325,9 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
         scale_prefetch(c, L.s_gu, r0, r1, false);
         const float2 nw = *reinterpret_cast<const float2*>(L.post_norm + 2 * c.tid);
         {
-            const u64* ptrs[T];
-            uint32_t eps[T];
             float v[2 * T];
-#pragma unroll
-            for (int j = 0; j < T; j++) { ptrs[j] = xbuf + (size_t)j * S::HID + 2 * c.tid; eps[j] = eC; }
-            ll_wait_pairs<T>(c, ptrs, eps, v, W_X);
+            const u64* base = xbuf + 2 * c.tid;
+            ll_wait_pairs_fn<T>(c, [&](int j) { return base + (size_t)j * S::HID; }, [&](int) { return eC; }, v, W_X);
 #pragma unroll
             for (int j = 0; j < T; j++) { x[j][0] = v[2 * j]; x[j][1] = v[2 * j + 1]; }
         }
@@ -1309,18 +1349,14 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
         float a[T][8];
         float mx[T], scale[T];
         {
-            const u64* ptrs[4 * T];
-            uint32_t eps[4 * T];
             float v[8 * T];
-#pragma unroll
-            for (int j = 0; j < T; j++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int k = 2 * c.tid + i * 2 * NCT;
-                    ptrs[4 * j + i] = k < S::INTER ? P.actl + (size_t)j * S::INTER + k : nullptr;
-                    eps[4 * j + i] = eD;
-                }
-            ll_wait_pairs<4 * T>(c, ptrs, eps, v, W_ACT);
+            const u64* act0 = P.actl + 2 * c.tid;
+            ll_wait_pairs_fn<4 * T>(c,
+                                    [&](int i) -> const u64* {
+                                        if (2 * c.tid + (i & 3) * 2 * NCT >= S::INTER) return nullptr;
+                                        return act0 + (size_t)(i >> 2) * S::INTER + (i & 3) * 2 * NCT;
+                                    },
+                                    [&](int) { return eD; }, v, W_ACT);
 #pragma unroll
             for (int j = 0; j < T; j++) {
                 mx[j] = 0.f;

@@ -168,15 +168,18 @@ class Megakernel:
                 rec["A_log"] = f32(w[p + "A_log"])
                 rec["dt_bias"] = f32(w[p + "dt_bias"])
                 rec["gdn_norm"] = f32(w[p + "norm.weight"])
-                hist = zeros(batch, self.GDN_TASKS, self.TASK_CHANNELS, ring)   # per sequence and recurrence task
+                hist = zeros(self.GDN_TASKS, self.TASK_CHANNELS, ring)   # per recurrence task (single-sequence launches)
                 st = zeros(batch, cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)   # [head][v][k]: the oracle's transposed
                 bak = zeros(cfg.lin_heads, cfg.lin_v_dim, cfg.lin_k_dim)
-                self.bconv_hist.append(hist)
+                self.conv_hist.append(hist)
                 self.bstate.append(st)
-                self.conv_hist.append(hist[0])            # sequence 0 is what the single-sequence launches use
-                self.state.append(st[0])
+                self.state.append(st[0])                  # sequence 0 is what the single-sequence launches use
                 self.state_bak.append(bak)
                 rec["conv_hist"], rec["state"], rec["state_bak"] = keep(hist), keep(st), keep(bak)
+                # batched launches keep the history per sequence and head: [q | k | v channels of the head]
+                bh = zeros(batch, cfg.lin_heads, 2 * cfg.lin_k_dim + cfg.lin_v_dim, ring)
+                self.bconv_hist.append(bh)
+                rec["conv_hist_b"] = keep(bh)
                 rec["kind"] = 0
             layer_vals += [rec[f] for f in F]
 
@@ -297,8 +300,9 @@ class Megakernel:
 
     def reset(self):
         """Start a new sequence (cached K/V need no clearing: positions are rewritten)."""
-        for t in self.bconv_hist + self.bstate + self.ll:
+        for t in self.conv_hist + self.bconv_hist + self.bstate + self.ll:
             t.zero_()
+        self._mode = None              # "single" or "batch": the two kinds of launch keep separate conv histories
         self.bpos = [0] * self.batch   # position of every sequence; `pos` is that of sequence 0
         self.attn_flag.zero_()
         self.attn_part.zero_()
@@ -329,6 +333,7 @@ class Megakernel:
             raise ValueError("need at least one input token")
         if n_generate < 1:
             raise ValueError("n_generate must be >= 1")
+        self._enter_mode("single")
         n_forced = len(tokens)
         n_steps = n_forced + n_generate - 1
         if self.pos + n_steps > self.max_seq:
@@ -398,6 +403,7 @@ class Megakernel:
             raise ValueError("every sequence needs at least one input token")
         if n_generate < 1:
             raise ValueError("n_generate must be >= 1")
+        self._enter_mode("batch")
         NBW = _lib.MAX_BATCH
         n_forced = [len(p) for p in prompts]
         n_total = [n + n_generate - 1 for n in n_forced]
@@ -454,6 +460,13 @@ class Megakernel:
         self.mtp_h = None
         return (result, result_logits) if return_logits else result
 
+    def _enter_mode(self, mode):
+        """Single-sequence and batched launches keep their conv histories in different layouts, so a
+        sequence cannot move between them: `reset()` in between."""
+        if self._mode not in (None, mode):
+            raise RuntimeError(f"this engine has {self._mode} state; call reset() before a {mode} launch")
+        self._mode = mode
+
     def prof_buffer(self):
         """Zeroed timestamp buffer for `run(prof=...)`: [grid, PROF_MAX_OPS, PROF_FIELDS] GPU nanoseconds
         (op entered, inputs staged, work done, outputs published), as `qwen_mk/engine.py:303-305`."""
@@ -508,6 +521,7 @@ class Megakernel:
         """
         if self.mtp is None:
             raise RuntimeError("construct the engine with mtp=True for speculative decoding")
+        self._enter_mode("single")
         n_cycles = min(n_generate, MAX_STEPS_PER_LAUNCH)
         if self.pos + 2 * n_cycles + 1 > self.max_seq:
             raise ValueError(f"sequence would exceed max_seq={self.max_seq}")
@@ -579,7 +593,11 @@ class Megakernel:
         reference decoder's `conv_hist`, `qwen_mk/reference.py:53,70-71`)."""
         c, ring = self.cfg, self.conv_hist[i].shape[-1]
         slots = [(self.bpos[seq] - 3 + j) % ring for j in range(3)]
-        h = self.bconv_hist[i][seq][:, :, slots]                 # [task, channel, 3]
+        if self._mode == "batch":
+            h = self.bconv_hist[i][seq][:, :, slots]             # [head, q | k | v channel, 3]
+            return torch.cat([h[:, : c.lin_k_dim].reshape(-1, 3), h[:, c.lin_k_dim: 2 * c.lin_k_dim].reshape(-1, 3),
+                              h[:, 2 * c.lin_k_dim:].reshape(-1, 3)])
+        h = self.conv_hist[i][:, :, slots]                       # [task, channel, 3]
         spt = c.lin_v_dim // self.GDN_SLICE                     # tasks per head
         out = torch.empty(c.conv_dim, 3, device=self.device)
         nqk = c.lin_heads * c.lin_k_dim
@@ -599,11 +617,12 @@ class Megakernel:
         return k, v
 
     def snapshot(self):
-        """Copy of the recurrent state (conv history + DeltaNet state) and the position."""
-        return [t.clone() for t in self.conv_hist + self.state], self.pos
+        """Copy of the recurrent state (conv histories + DeltaNet state of every sequence) and the positions."""
+        return [t.clone() for t in self.conv_hist + self.bconv_hist + self.bstate], list(self.bpos), self._mode
 
     def restore(self, snap):
-        tensors, pos = snap
-        for dst, src in zip(self.conv_hist + self.state, tensors):
+        tensors, pos, mode = snap
+        for dst, src in zip(self.conv_hist + self.bconv_hist + self.bstate, tensors):
             dst.copy_(src)
-        self.pos = pos
+        self.bpos = list(pos)
+        self._mode = mode
