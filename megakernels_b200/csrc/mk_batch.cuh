@@ -28,6 +28,16 @@
 namespace mk {
 
 constexpr int NB = 8;                       // sequences per pass = columns of one MMA
+// Cached K rows a warp, and cached V elements a thread, requests together in batched attention.  More
+// loads in flight (2 or 4 rows, 16 elements) measured 3 to 14 % slower per step: at 96 registers per
+// thread they turn into spills, and spills are served by L2 because shared memory leaves the L1
+// almost nothing.
+#ifndef MK_B_KU
+#define MK_B_KU 1
+#endif
+#ifndef MK_B_VU
+#define MK_B_VU 8
+#endif
 
 struct BatchArgs {
     const int* forced;                      // [steps][NB] prompt tokens, step-major
@@ -438,7 +448,7 @@ __device__ __forceinline__ bool run_layer_b(Ctx& c, const Params& P, const Layer
             const AttnView view = {c.cta - q * per, per, P.projl + (size_t)q * S::PROJ_MAX, P.mixl + (size_t)q * S::MIX,
                                    P.attn_part + (size_t)q * S::NKV * MAX_SPLITS * S::PART_STRIDE,
                                    c.sm.bt_s + q * (P.max_seq / KV_BLOCK), true};
-            had_task = attn_op<S, KVF32, 1>(c, P, L, view, A.pos0[q] + step, eA, eB, op0 + 1);
+            had_task = attn_op<S, KVF32, 1, MK_B_KU, MK_B_VU>(c, P, L, view, A.pos0[q] + step, eA, eB, op0 + 1);
         }
     } else {
         had_task = gdn_batch<S>(c, P, L, A, step, frozen, eA, eB, op0 + 1);

@@ -881,7 +881,10 @@ struct AttnView {
     bool gate;              // publish o * sigmoid(gate) instead of o (otherwise the out-projection's prologue applies the gate)
 };
 
-template <class S, bool KVF32, int T>
+// KU cached K rows per warp and VU cached V elements per thread are requested together before they are
+// used: 1 and 8 suit the short chunks of a sequence that has the whole grid; tasks that scan 64 or more
+// positions (several sequences sharing the grid) want more loads in flight.
+template <class S, bool KVF32, int T, int KU = 1, int VU = 8>
 __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView& V, int pos, uint32_t e_proj,
                         uint32_t e_out, int op) {
     static_assert(S::HD == 256 && S::QPK == 4 && NCW == 16 && S::ROT == 64, "thread mapping below");
@@ -1038,18 +1041,25 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
                 }
             }
         };
-        for (int p = p0 + c.warp; p < p1; p += NCW) {
-            float kk[8];
-            if (p >= pos) {
+        for (int pb = p0 + c.warp; pb < p1; pb += KU * NCW) {
+            float kk[KU][8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) kk[i] = knew_s[(p - pos) * S::HD + 8 * c.lane + i];
-            } else if (p == p0 + c.warp) {
+            for (int u = 0; u < KU; u++) {
+                const int p = pb + u * NCW;
+                if (p >= p1) continue;
+                if (p >= pos) {
 #pragma unroll
-                for (int i = 0; i < 8; i++) kk[i] = kpre[i];
-            } else {
-                load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kk);
+                    for (int i = 0; i < 8; i++) kk[u][i] = knew_s[(p - pos) * S::HD + 8 * c.lane + i];
+                } else if (p == p0 + c.warp) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) kk[u][i] = kpre[i];
+                } else {
+                    load8<KVF32>(L.k_cache, kv_elem(p) + 8 * c.lane, kk[u]);
+                }
             }
-            score(p, kk);
+#pragma unroll
+            for (int u = 0; u < KU; u++)
+                if (pb + u * NCW < p1) score(pb + u * NCW, kk[u]);
         }
     }
     consumer_sync();
@@ -1092,15 +1102,15 @@ __device__ bool attn_op(Ctx& c, const Params& P, const LayerP& L, const AttnView
             }
         }
         int i = PFV;
-        for (; i + 8 <= np; i += 8) {
-            float v[8];
+        for (; i + VU <= np; i += VU) {
+            float v[VU];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < VU; u++) {
                 const int p = p0 + i + u;
                 v[u] = p >= pos ? vnew_s[(p - pos) * S::HD + d] : load1<KVF32>(L.v_cache, kv_elem(p) + d);
             }
 #pragma unroll
-            for (int u = 0; u < 8; u++) accumulate(i + u, v[u]);
+            for (int u = 0; u < VU; u++) accumulate(i + u, v[u]);
         }
         for (; i < np; i++) {
             const int p = p0 + i;

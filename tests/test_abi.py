@@ -53,6 +53,27 @@ def test_struct_layouts(lib_built):
     assert a.spec.offset == 120 and a.spec_out.offset == 136 and ctypes.sizeof(a) == 152
 
 
+def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
+    """The ctypes mirror of mk_batch_args has the size and offsets the C compiler gives the header's struct."""
+    import shutil
+    import subprocess
+    b = _lib.BatchArgs
+    assert ctypes.sizeof(b) == 192 and b.n_total.offset == 40 and b.batch.offset == 104 and b.stop_ids.offset == 136
+    assert _lib.query("MAX_BATCH") == _lib.MAX_BATCH == 8
+    assert _lib.query("BATCH_SMEM_BYTES") <= 227 * 1024
+    if not shutil.which("gcc"):
+        return
+    src = tmp_path / "layout.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "mk_b200.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(mk_batch_args), offsetof(mk_batch_args, n_total), '
+                   'offsetof(mk_batch_args, batch), offsetof(mk_batch_args, stop_ids), sizeof(mk_launch_args), '
+                   'sizeof(mk_model_desc)); return 0; }\n')
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)], check=True)
+    got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
+    assert got == [192, 40, 104, 136, ctypes.sizeof(_lib.LaunchArgs), ctypes.sizeof(_lib.ModelDesc)]
+
+
 def test_constants(lib_built):
     assert _lib.query("N_THREADS") % 32 == 0
     assert _lib.query("SMEM_BYTES") <= 227 * 1024
@@ -71,4 +92,5 @@ def test_bad_arguments_are_refused_without_a_gpu(lib_built):
     with pytest.raises(_lib.MkError):
         _lib.check(lib.mk_plan_rows(10, 3, 0, 4, None, None))
     assert lib.mk_launch(None, None, None) == _lib.MK_ERR_BADARG
+    assert lib.mk_launch_batch(None, None, None) == _lib.MK_ERR_BADARG
     assert lib.mk_destroy(None) == _lib.MK_OK
