@@ -237,45 +237,6 @@ __device__ __forceinline__ void ll_wait_pairs_fn(Ctx& c, Addr&& addr, Epoch&& ep
     }
 }
 
-// The two halves of `ll_wait_pairs_fn`, for callers that keep the next round's loads in flight while
-// they work on the current one: issue the loads; later, re-load what was not ready until all is.
-template <int N, class Addr>
-__device__ __forceinline__ void ll_issue_fn(Addr&& addr, u64 (&w)[2 * N]) {
-#pragma unroll
-    for (int i = 0; i < N; i++) {
-        w[2 * i] = w[2 * i + 1] = 0;
-        if (const u64* p = addr(i)) ll_load2(p, w[2 * i], w[2 * i + 1]);
-    }
-}
-template <int N, class Addr, class Epoch>
-__device__ __forceinline__ void ll_complete_fn(Ctx& c, Addr&& addr, Epoch&& epoch, u64 (&w)[2 * N], float (&v)[2 * N],
-                                               int where) {
-    Spin s;
-    while (true) {
-        bool ok = true;
-#pragma unroll
-        for (int i = 0; i < N; i++) {
-            const u64* p = addr(i);
-            const uint32_t e = epoch(i);
-            if (p && ((uint32_t)(w[2 * i] >> 32) != e || (uint32_t)(w[2 * i + 1] >> 32) != e)) {
-                ok = false;
-                ll_load2(p, w[2 * i], w[2 * i + 1]);
-            }
-        }
-        if (ok) break;
-        if (MK_SPIN_FAIL(c, s, where)) {
-            c.dead = true;
-            break;
-        }
-        poll_backoff(s.it);
-    }
-#pragma unroll
-    for (int i = 0; i < N; i++) {
-        v[2 * i] = __uint_as_float((uint32_t)w[2 * i]);
-        v[2 * i + 1] = __uint_as_float((uint32_t)w[2 * i + 1]);
-    }
-}
-
 // A CTA that had no part in the op it now waits for arrives early.  If all of its threads polled
 // right away, their loads would queue in front of the very stores they wait for.  Instead one warp
 // watches 32 words spread over the buffer, at a relaxed pace, and releases the CTA when all of them
@@ -479,10 +440,11 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
 //   STREAM = true   (LM head, draft head): one barrier per chunk, warp `token` finishes that token's
 //                   rows of the chunk while the other warps move on.
 // A finishing warp calls sink(lane, row, token, value, valid) on all of its lanes; `value` already
-// carries the row's scale and the input's fixed-point scale.
+// carries the row's scale and the input's fixed-point scale.  A layer GEMV ends with one more barrier
+// after the sink (`tail_barrier`).
 template <bool Q8, int T, bool STREAM, class Sink>
 __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const float* __restrict__ row_scale,
-                                         Sink&& sink) {
+                                         Sink&& sink, bool tail_barrier = true) {
     constexpr int NS = Geo<T>::NS;
     const int rpc = SLOT_BYTES / rb;
     const int nkb = rb >> 6;
@@ -554,6 +516,11 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
             sink(c.lane, r0 + idx, tk, v * rs * c.sm.xscale_s[tk], idx < r1 - r0);
             MK_MARK(c, 11);
         }
+        // Without a barrier here the other warps run ahead into the next op's prologue and poll for its
+        // inputs; their loads then sit in this SM's memory pipeline in front of the stores the finishing
+        // warps are about to issue, and every CTA's outputs reach the others later (3 % of the step).
+        // A caller that follows up with a barrier of its own passes tail_barrier = false.
+        if (tail_barrier) consumer_sync();
     }
 }
 
@@ -1395,7 +1362,7 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
                 ll_store(xbuf + (size_t)tk * S::HID + row, eE, xn);
                 if (resid_out) resid_out[(size_t)tk * S::HID + row] = xn;
             }
-        });
+        }, false);
         prof_stamp(c, op, 3);
         failed = consumer_any(c.dead);
     }
