@@ -195,3 +195,28 @@ def test_bad_arguments_are_refused(tiny, lib_built):
         mk.run_batch([[1], []])
     with pytest.raises(ValueError):
         mk.run_batch([[1], [2]], n_generate=1000)
+
+
+def test_full_size_batch_against_the_reference_fixture(lib_built):
+    """Benchmark configuration 2 at full size (24 layers, vocab 151936, 512-token prompts), eight sequences:
+    sequence 0 carries the fixture's prompt and must reproduce the reference decoder's recorded greedy ids
+    and probe logits; the other sequences must equal the single-sequence kernel."""
+    import json
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "cfg2_int8.json")
+    g = json.load(open(path))
+    cfg = qwen35_08b(n_layers=g["n_layers"], vocab=g["vocab"])
+    w = make_weights(cfg, g["seed"], init=g["init"])
+    n_gen = len(g["ids"])
+    prompts = [g["prompt"]] + [make_prompt(cfg, len(g["prompt"]) - 7 * j, seed=500 + j) for j in range(1, 8)]
+    mk = engine(cfg, w, batch=8, max_seq=len(g["prompt"]) + n_gen + 8)
+    ids, logits = mk.run_batch(prompts, n_generate=n_gen, return_logits=True)
+    first = next((i for i, (x, y) in enumerate(zip(ids[0], g["ids"])) if x != y), None)
+    assert first is None, f"diverged at step {first}: reference top-2 gap there {g['top2_gap'][first]:.3e}"
+    probe = logits[0][:, g["probe_indices"]].cpu()
+    assert float((probe - torch.tensor(g["probe_logits"])).abs().max()) < LOGIT_TOL
+    for j in (3, 7):
+        mk.reset()
+        alone, alone_logits = mk.run(prompts[j], n_generate=n_gen, return_logits=True)
+        assert ids[j] == alone, j
+        assert float((logits[j] - alone_logits).abs().max()) < 1e-3
