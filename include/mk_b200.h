@@ -55,7 +55,7 @@ enum {
     MK_L_V_CACHE,
     MK_L_KIND,          /* 0 = Gated DeltaNet, 1 = gated full attention (a value, not a pointer) */
     MK_L_CONV_HIST_B,   /* fp32 [batch, 16 heads, 384 channels, 8]: conv history of batched decoding (0 if unused) */
-    MK_L_RESERVED1,
+    MK_L_W_DOWN_ROWS,   /* down-projection in the row-slice layout of the other matrices: the batched kernel's copy (0 if unused) */
     MK_LAYER_FIELDS
 };
 
@@ -81,6 +81,7 @@ enum {
     MK_G_MTP_FC, MK_G_MTP_FC_SCALE, MK_G_MTP_NORM_E, MK_G_MTP_NORM_H, MK_G_MTP_NORM,
     MK_G_DRAFT_HEAD, MK_G_DRAFT_SCALE, MK_G_DRAFT_IDS,
     MK_G_XML,           /* u64 [tokens, hidden] MTP residual stream                            */
+    MK_G_PARTL,         /* u64 [tokens, grid, hidden] partial down-projection sums of every CTA */
     MK_GLOBAL_FIELDS
 };
 
@@ -153,8 +154,8 @@ int mk_launch(mk_engine* e, const mk_launch_args* args, void* stream);
  * process whose memory pool has already claimed the whole device, a plug-in that is called at a
  * point where the host forbids allocation, a real-time loop that may not take the allocator's
  * lock.  For them the activation hand-off words of the kernel (the buffers a normal engine passes
- * as MK_G_XL, MK_G_PROJL, MK_G_MIXL, MK_G_ACTL, MK_G_LML and MK_G_ATTN_PART) live in one array that
- * is compiled into the library, MK_STATIC_SCRATCH_BYTES (3 MiB) per GPU that loads it, held until the
+ * as MK_G_XL, MK_G_PROJL, MK_G_MIXL, MK_G_ACTL, MK_G_LML, MK_G_ATTN_PART and MK_G_PARTL) live in one array that
+ * is compiled into the library, MK_STATIC_SCRATCH_BYTES (4 MiB) per GPU that loads it, held until the
  * process exits.  The caller still passes every input and output (weights, state, KV cache, status
  * words, the launch arguments); this function calls no cudaMalloc / cudaFree and no allocating
  * library routine.
@@ -165,7 +166,7 @@ int mk_launch(mk_engine* e, const mk_launch_args* args, void* stream);
  *  - Every call clears the array on `stream` before the kernel runs, because all calls (of all
  *    engines) share it and it keeps what the last call wrote.  Two calls that overlap on the GPU
  *    (different streams, or different engines at once) therefore race: serialise them. */
-#define MK_STATIC_SCRATCH_BYTES (3u << 20)
+#define MK_STATIC_SCRATCH_BYTES (4u << 20)
 int mk_launch_static(mk_engine* e, const mk_launch_args* args, void* stream);
 
 /* Batched decoding: up to MK_MAX_BATCH independent sequences share every pass over the weights

@@ -49,6 +49,7 @@ static void fill_layer(LayerP& L, const int64_t* f) {
     L.w_out = as_ptr<const uint8_t*>(f[MK_L_W_OUT]);
     L.w_gu = as_ptr<const uint8_t*>(f[MK_L_W_GU]);
     L.w_down = as_ptr<const uint8_t*>(f[MK_L_W_DOWN]);
+    L.w_down_rows = as_ptr<const uint8_t*>(f[MK_L_W_DOWN_ROWS]);
     L.s_in = as_ptr<const float*>(f[MK_L_S_IN]);
     L.s_out = as_ptr<const float*>(f[MK_L_S_OUT]);
     L.s_gu = as_ptr<const float*>(f[MK_L_S_GU]);
@@ -171,6 +172,7 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     p.draft_scale = as_ptr<const float*>(g[MK_G_DRAFT_SCALE]);
     p.draft_ids = as_ptr<const int*>(g[MK_G_DRAFT_IDS]);
     p.xml = as_ptr<unsigned long long*>(g[MK_G_XML]);
+    p.partl = as_ptr<unsigned long long*>(g[MK_G_PARTL]);
     p.n_layers = e->desc.n_layers;
     p.vocab = e->desc.vocab;
     p.max_seq = e->desc.max_seq;
@@ -179,7 +181,7 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     if (bad16(p.embed) || bad16(p.lm_head)) return fail(MK_ERR_BADARG, "embedding / LM head null or not 16-byte aligned");
     if (q8 && (!p.embed_scale || !p.lm_scale)) return fail(MK_ERR_BADARG, "int8 embedding / LM head without scales");
     if (!p.final_norm || !p.rope_cos || !p.rope_sin) return fail(MK_ERR_BADARG, "final norm / RoPE tables missing");
-    if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.actl) || bad16(p.lml))
+    if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.actl) || bad16(p.lml) || bad16(p.partl))
         return fail(MK_ERR_BADARG, "activation word buffers null or not 16-byte aligned");
     if (!p.attn_part || !p.attn_flag || !p.block_table || !p.status) return fail(MK_ERR_BADARG, "attention scratch / block table / status missing");
     MK_CUDA(cudaSetDevice(e->desc.device));
@@ -320,6 +322,7 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     const size_t o_act = off;   off = align256(off + sizeof(unsigned long long) * S::INTER);
     const size_t o_lml = off;   off = align256(off + sizeof(unsigned long long) * 2 * (size_t)grid);
     const size_t o_part = off;  off = align256(off + sizeof(unsigned long long) * (size_t)S::NKV * MAX_SPLITS * S::PART_STRIDE);
+    const size_t o_partl = off; off = align256(off + sizeof(unsigned long long) * (size_t)grid * S::HID);
     if (off > MK_STATIC_SCRATCH_BYTES)
         return fail(MK_ERR_BADARG, "mk_launch_static: this shape and a grid of %d CTAs need %zu bytes of hand-off words, the built-in array holds %u",
                     grid, off, (unsigned)MK_STATIC_SCRATCH_BYTES);
@@ -346,6 +349,7 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
         p.actl = reinterpret_cast<unsigned long long*>(base + o_act);
         p.lml = reinterpret_cast<unsigned long long*>(base + o_lml);
         p.attn_part = reinterpret_cast<unsigned long long*>(base + o_part);
+        p.partl = reinterpret_cast<unsigned long long*>(base + o_partl);
         MK_CUDA(cudaMemcpyToSymbol(c_params, &p, sizeof(Params), (size_t)pslot * sizeof(Params), cudaMemcpyHostToDevice));
         e->static_ready = true;
     }
@@ -416,8 +420,8 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
         return fail(MK_ERR_BADARG, "mk_launch_batch: epoch counter exhausted or zero; reset the engine");
     for (int l = 0; l < e->desc.n_layers; l++)
-        if (e->host.layer[l].kind == 0 && !e->host.layer[l].conv_hist_b)
-            return fail(MK_ERR_BADARG, "mk_launch_batch: layer %d has no batched conv history (MK_L_CONV_HIST_B)", l);
+        if ((e->host.layer[l].kind == 0 && !e->host.layer[l].conv_hist_b) || !e->host.layer[l].w_down_rows)
+            return fail(MK_ERR_BADARG, "mk_launch_batch: layer %d lacks the batched kernel's buffers (MK_L_CONV_HIST_B, MK_L_W_DOWN_ROWS)", l);
 
     BatchArgs A;
     memset(&A, 0, sizeof A);

@@ -408,7 +408,7 @@ __device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A) {
             pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID);
             pr.stream(L.w_out, S::HID, 1, S::MIX);
             pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID);
-            pr.stream(L.w_down, S::HID, 1, S::INTER);
+            pr.stream(L.w_down_rows, S::HID, 1, S::INTER);
         }
         if (s >= A.lm_from) pr.stream(P.lm_head, P.vocab, 1, S::HID);
     }

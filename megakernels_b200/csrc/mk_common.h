@@ -26,6 +26,7 @@ constexpr int PROF_FIELDS = 6;          // enter, staged, done, published, ring-
 #endif
 constexpr int PROF_MAX_OPS = MAX_LAYERS * OPS_PER_LAYER + 8;
 constexpr int SPEC_T = 2;
+constexpr int DOWN_K = 32;                  // columns of a CTA's down-projection slice (its SwiGLU outputs, padded)
 
 // ---- the 0.8B hybrid shape --------------------------------------------------------------------
 struct Qwen35_08B {
@@ -54,7 +55,8 @@ struct LayerP {
     const uint8_t* w_in;
     const uint8_t* w_out;
     const uint8_t* w_gu;
-    const uint8_t* w_down;
+    const uint8_t* w_down;        // single-sequence kernels: column slices per CTA in fragment order (pack_down_cols)
+    const uint8_t* w_down_rows;   // batched kernel: row slices per CTA (pack_rows)
     const float* s_in;
     const float* s_out;
     const float* s_gu;
@@ -104,6 +106,7 @@ struct Params {
     const float* draft_scale;
     const int* draft_ids;
     unsigned long long* xml;
+    unsigned long long* partl;    // [token][cta][hidden] partial down-projection sums
     int n_layers, vocab, max_seq, draft_vocab;
 };
 

@@ -42,6 +42,7 @@ struct Smem {
     u64* best_s;        // [NCW] block-reduction scratch for 64-bit keys
     float* scale_s;     // per-row scales: two 128-row buffers for layer GEMVs, then the streaming ring
     float* xscale_s;    // [T] power-of-two factors that undo the fixed-point scaling of the staged inputs
+    float* act_s;       // [T][DOWN_K] this CTA's SwiGLU outputs (entries past its slice stay zero)
     float* ssq_s;       // batched decoding: [sequence][NCW] per-warp sums of squares of the RMSNorm input staged last
     float* wsc_s;       // batched decoding: [NCW][sequence] inverse fixed-point scales of each warp's k-slice
     uint64_t* full;     // [ring stages]
@@ -597,7 +598,7 @@ __device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
         pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID * WB);
         pr.stream(L.w_out, S::HID, 1, S::MIX * WB);
         pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID * WB);
-        pr.stream(L.w_down, S::HID, 1, S::INTER * WB);
+        pr.stream(L.w_down, (S::HID / 16) * c.grid, S::HID / 16, 16 * DOWN_K * WB);   // this CTA's column slice: 64 tiles
     };
     for (int s = 0; s < A.n_steps && !pr.stop; s++) {
         for (int l = 0; l < P.n_layers && !pr.stop; l++) layer(P.layer[l]);
@@ -1311,58 +1312,151 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
         stage_rmsnorm<S, Q8, T>(c, x, nw, y);
         prof_stamp(c, op, 1);
         gemv_mma<Q8, T, false>(c, r0, r1, S::HID * WB, L.s_gu, [&](int lane, int row, int tk, float v, bool ok) {
-            // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane
+            // rows alternate gate, up; chunks hold whole pairs, so the partner is the next lane.  The
+            // SwiGLU outputs stay in this CTA: it multiplies them with its column slice of the
+            // down-projection itself.
             const float up = __shfl_down_sync(0xffffffffu, v, 1);
-            if (ok && !(lane & 1)) ll_store(P.actl + (size_t)tk * S::INTER + (row >> 1), eD, silu_f(v) * up);
+            if (ok && !(lane & 1)) c.sm.act_s[tk * DOWN_K + ((row - r0) >> 1)] = silu_f(v) * up;
         });
+        // ---- down-projection, split over K: 1024 partial sums from this CTA's <= 32 activations.
+        // One MMA covers a 16-row tile's whole K, so results leave the registers as hand-off words:
+        // no partial sums in shared memory, no barrier.  Every warp derives the B fragments itself.
+        {
+            constexpr int TILES = S::HID / 16, TILE_BYTES = 16 * DOWN_K * WB, TPC = SLOT_BYTES / TILE_BYTES;
+            static_assert(TPC % NCW == 0 && TILES % TPC == 0, "whole rounds of 16 tiles per ring chunk");
+            const int g = c.lane >> 2, t = c.lane & 3, tok = g >> 2, piece = g & 3;
+            uint32_t bf[Q8 ? 2 : 4] = {};       // B fragments of plane g = 4 * token + digit / piece
+            float inv_scale[T];
+#pragma unroll
+            for (int j = 0; j < T; j++) {
+                const float* a = c.sm.act_s + j * DOWN_K;
+                const float scale = Q8 ? fixed_scale(warp_max(fabsf(a[c.lane]))) : 1.0f;
+                inv_scale[j] = 1.0f / scale;
+                if (tok == j && piece < Planes<Q8>::N) {
+                    if (Q8) {
+#pragma unroll
+                        for (int hf = 0; hf < 2; hf++) {
+                            uint32_t pk = 0;
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const int q = __float2int_rn(a[16 * hf + 4 * t + i] * scale);
+                                const int d = piece < 3 ? ((q >> (7 * piece)) & 127) : (q >> 21);
+                                pk |= (uint32_t)(d & 255) << (8 * i);
+                            }
+                            bf[hf] = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int f = 0; f < 4; f++) {           // mma f / 2, low or high 8 columns
+                            uint32_t pk = 0;
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                float v = a[16 * (f >> 1) + 8 * (f & 1) + 2 * t + i];
+                                __nv_bfloat16 pb = __float2bfloat16_rn(v);
+#pragma unroll
+                                for (int d = 0; d < 2; d++)
+                                    if (d < piece) {
+                                        v -= __bfloat162float(pb);
+                                        pb = __float2bfloat16_rn(v);
+                                    }
+                                pk |= (uint32_t)__bfloat16_as_ushort(pb) << (16 * i);
+                            }
+                            bf[f] = pk;
+                        }
+                    }
+                }
+            }
+            const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);   // 128^(2 * (t & 1)) for the int8 digits
+            const float pw1 = pw0 * 128.f;
+            const int otok = t >> 1;                                                     // token whose sums this lane ends up with
+            const float os = inv_scale[otok < T ? otok : 0];
+            u64* out = P.partl + ((size_t)(otok < T ? otok : 0) * c.grid + c.cta) * S::HID;
+            for (int base = 0; base < TILES; base += TPC) {
+                const uint32_t n = c.cons_n++;
+                const int slot = (int)(n % Geo<T>::NS);
+                mbar_wait(c, &c.sm.full[slot], (n / Geo<T>::NS) & 1, W_FULL);
+                const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
+#pragma unroll
+                for (int i = 0; i < TPC / NCW; i++) {
+                    const int tile = c.warp + NCW * i;
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(buf + (size_t)tile * TILE_BYTES + c.lane * (16 * WB));
+                    float lo, hi;
+                    if (Q8) {
+                        int ci[4] = {0, 0, 0, 0};
+                        mma_s8(ci, w0.x, w0.y, w0.z, w0.w, bf[0], bf[1]);
+                        lo = (float)ci[0] * pw0 + (float)ci[1] * pw1;
+                        hi = (float)ci[2] * pw0 + (float)ci[3] * pw1;
+                    } else {
+                        const uint4 w1 = *reinterpret_cast<const uint4*>(buf + (size_t)tile * TILE_BYTES + c.lane * 32 + 16);
+                        float cf[4] = {0.f, 0.f, 0.f, 0.f};
+                        mma_bf16(cf, w0.x, w0.y, w0.z, w0.w, bf[0], bf[1]);
+                        mma_bf16(cf, w1.x, w1.y, w1.z, w1.w, bf[Q8 ? 0 : 2], bf[Q8 ? 1 : 3]);
+                        lo = cf[0] + cf[1];
+                        hi = cf[2] + cf[3];
+                    }
+                    lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+                    hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+                    if ((t & 1) == 0 && otok < T) {
+                        const int row = (base + tile) * 16 + g;
+                        ll_store(out + row, eD, lo * os);
+                        ll_store(out + row + 8, eD, hi * os);
+                    }
+                }
+                __syncwarp();
+                if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
+            }
+        }
         prof_stamp(c, op, 3);
     }
-    // ---- E: down-projection + residual
+    // ---- E: sum of the CTAs' partial down-projections + residual, for the rows this CTA owns
     bool failed;
     {
         const int op = op0 + 4;
         prof_stamp(c, op, 0);
-        scale_prefetch(c, L.s_down, xr0, xr1, false);
-        float a[T][8];
-        float mx[T], scale[T];
-        {
-            float v[8 * T];
-            const u64* act0 = P.actl + 2 * c.tid;
-            ll_wait_pairs_fn<4 * T>(c,
-                                    [&](int i) -> const u64* {
-                                        if (2 * c.tid + (i & 3) * 2 * NCT >= S::INTER) return nullptr;
-                                        return act0 + (size_t)(i >> 2) * S::INTER + (i & 3) * 2 * NCT;
-                                    },
-                                    [&](int) { return eD; }, v, W_ACT);
+        if (c.warp < xr1 - xr0) {
+            const int row = xr0 + c.warp;
+            const float rs = Q8 ? L.s_down[row] : 1.0f;         // requested before the wait
 #pragma unroll
             for (int j = 0; j < T; j++) {
-                mx[j] = 0.f;
+                // lane l takes CTAs l, l + 32, ...; fixed order, then the shuffle tree
+                constexpr int PER = 5;                          // grids of up to 160 CTAs
+                const u64* src = P.partl + (size_t)j * c.grid * S::HID + row;
+                u64 w[PER];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    a[j][i] = v[8 * j + i];
-                    mx[j] = fmaxf(mx[j], fabsf(a[j][i]));
+                for (int i = 0; i < PER; i++) {
+                    const int cta = c.lane + 32 * i;
+                    w[i] = cta < c.grid ? ll_load(src + (size_t)cta * S::HID) : 0;
+                }
+                Spin sp;
+                while (true) {
+                    bool ok = true;
+#pragma unroll
+                    for (int i = 0; i < PER; i++) {
+                        const int cta = c.lane + 32 * i;
+                        if (cta < c.grid && (uint32_t)(w[i] >> 32) != eD) {
+                            ok = false;
+                            w[i] = ll_load(src + (size_t)cta * S::HID);
+                        }
+                    }
+                    if (ok) break;
+                    if (MK_SPIN_FAIL(c, sp, W_ACT)) {
+                        c.dead = true;
+                        break;
+                    }
+                }
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < PER; i++)
+                    if (c.lane + 32 * i < c.grid) acc += __uint_as_float((uint32_t)w[i]);
+                const float tot = warp_sum(acc);
+                if (c.lane == 0) {
+                    const float xn = c.sm.xown[j * 16 + c.warp] + tot * rs;
+                    c.sm.xown[j * 16 + c.warp] = xn;
+                    ll_store(xbuf + (size_t)j * S::HID + row, eE, xn);
+                    if (resid_out) resid_out[(size_t)j * S::HID + row] = xn;
                 }
             }
         }
-        block_scale<Q8, T>(c, mx, scale);
-#pragma unroll
-        for (int j = 0; j < T; j++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int k = 2 * c.tid + i * 2 * NCT;
-                if (k < S::INTER)
-                    stage_pair<Q8>(c.sm.xq + (size_t)(4 * j) * (S::INTER * WB), S::INTER * WB, k, a[j][2 * i], a[j][2 * i + 1], scale[j]);
-            }
-        finish_stage<T>(c, scale);
-        prof_stamp(c, op, 1);
-        gemv_mma<Q8, T, false>(c, xr0, xr1, S::INTER * WB, L.s_down, [&](int, int row, int tk, float v, bool ok) {
-            if (ok) {
-                const float xn = c.sm.xown[tk * 16 + row - xr0] + v;
-                c.sm.xown[tk * 16 + row - xr0] = xn;
-                ll_store(xbuf + (size_t)tk * S::HID + row, eE, xn);
-                if (resid_out) resid_out[(size_t)tk * S::HID + row] = xn;
-            }
-        }, false);
         prof_stamp(c, op, 3);
         failed = consumer_any(c.dead);
     }
@@ -1394,12 +1488,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
+        c.sm.act_s = reinterpret_cast<float*>(p); p += SPEC_T * DOWN_K * 4;
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
     c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr; c.wait_acc = 0; c.cur_op = 0; c.gemv_n = 0;
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
+    if (c.tid < SPEC_T * DOWN_K) c.sm.act_s[c.tid] = 0.f;
     if (c.tid == 0) {
         for (int i = 0; i < NS; i++) {
             mbar_init(&c.sm.full[i], 1);

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from . import mtp as mtp_mod
 from .config import Config
-from .pack import as_bytes, pack_rows
+from .pack import as_bytes, pack_down_cols, pack_rows
 from .quant import is_gemv_weight, quantize_int8_rows, roundtrip_int8_rows
 
 # Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
@@ -129,7 +129,13 @@ class Megakernel:
             rec = dict.fromkeys(F, 0)
             gu = torch.stack([w[m + "mlp.gate_proj.weight"], w[m + "mlp.up_proj.weight"]], dim=1).reshape(-1, cfg.hidden)
             rec["w_gu"], rec["s_gu"] = mat(gu, unit=2)
-            rec["w_down"], rec["s_down"] = mat(w[m + "mlp.down_proj.weight"])
+            # the single-sequence kernels take the down-projection as column slices (the CTA that produces
+            # SwiGLU outputs multiplies them itself); the batched kernel takes row slices like every other matrix
+            dm, ds = plain(w[m + "mlp.down_proj.weight"])
+            rec["w_down"] = keep(pack_down_cols(dm, self.grid))
+            rec["s_down"] = keep(ds) if ds is not None else 0
+            if q8:      # run_batch is available on every int8 engine
+                rec["w_down_rows"] = keep(pack_rows(as_bytes(dm), 1, self.grid, slot_bytes))
             rec["in_norm"] = f32(w[m + "input_layernorm.weight"])
             rec["post_norm"] = f32(w[m + "post_attention_layernorm.weight"])
             return rec
@@ -190,7 +196,8 @@ class Megakernel:
         # flag-in-data activation buffers: (epoch << 32) | fp32 bits
         T = max(_lib.query("SPEC_T"), batch)   # token slots per hand-off buffer: a speculative cycle's two tokens, or one per sequence
         self.ll = [torch.zeros(n, **u64) for n in (T * cfg.hidden, T * proj_max, T * mix, T * cfg.intermediate,
-                                                   (T + 1) * 2 * self.grid, T * cfg.hidden)]
+                                                   (T + 1) * 2 * self.grid, T * cfg.hidden,
+                                                   _lib.query("SPEC_T") * self.grid * cfg.hidden)]
         max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
         self.attn_part = zeros(T * cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
         self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
@@ -210,6 +217,7 @@ class Megakernel:
                  lml=keep(self.ll[4]), attn_part=keep(self.attn_part), attn_flag=keep(self.attn_flag),
                  block_table=keep(self.block_table), status=keep(self.status))
         g["xml"] = keep(self.ll[5])
+        g["partl"] = keep(self.ll[6])
         self.mtp = self.draft_ids = None
         self.draft_vocab = 0
         mtp_vals = None

@@ -80,3 +80,45 @@ def as_bytes(w):
     """Row-major weight matrix (int8 or bf16) viewed as [N, row_bytes] uint8."""
     w = w.contiguous()
     return w.view(torch.uint8).view(w.shape[0], -1)
+
+
+# ---- column slices in tensor-core fragment order (the down-projection of the single-sequence kernel) ----
+# The CTA that computes SwiGLU outputs [a0, a1) multiplies them right away with columns [a0, a1) of the
+# down-projection and publishes 1024 partial sums, so it needs a column slice of the matrix, padded to
+# 32 columns.  The slice is stored as 16-row tiles in the order the MMA reads its first operand, one
+# 128-bit load per lane and instruction.
+DOWN_K = 32       # columns per slice, padded
+
+
+def down_col_range(inter, cta, grid):
+    """SwiGLU outputs [a0, a1) that CTA `cta` produces (its gate/up rows are 2*a0 .. 2*a1)."""
+    r0, r1 = plan_rows(2 * inter, 2, cta, grid)
+    return r0 // 2, r1 // 2
+
+
+def pack_down_cols(w, grid):
+    """[N, K] int8 or bf16 weights -> uint8 [grid * (N / 16) * tile_bytes]: per CTA its column slice as
+    N / 16 tiles of 16 rows x 32 columns in fragment order.
+
+    int8 (mma m16n8k32): lane (g, t) of a tile holds rows g and g + 8, columns 4t..4t+3 and 16+4t..16+4t+3,
+    as four 32-bit registers [row g | row g + 8] x [low columns | high columns] -> 16 bytes per lane.
+    bf16 (two mma m16n8k16 per tile): per instruction rows g, g + 8 and columns 2t, 2t+1 and 8+2t, 9+2t of
+    its 16 columns -> 16 bytes per lane and instruction, the two instructions of a tile back to back."""
+    n, k = w.shape
+    assert n % 16 == 0
+    tiles = n // 16
+    out = []
+    for c in range(grid):
+        a0, a1 = down_col_range(k, c, grid)
+        assert a1 - a0 <= DOWN_K
+        sl = torch.zeros(n, DOWN_K, dtype=w.dtype, device=w.device)
+        sl[:, : a1 - a0] = w[:, a0:a1]
+        if w.dtype == torch.int8:
+            # [tile][hi][g][khalf][t][byte] -> [tile][g][t][khalf][hi][byte]
+            x = sl.view(tiles, 2, 8, 2, 4, 4).permute(0, 2, 4, 3, 1, 5)
+        else:
+            assert w.dtype == torch.bfloat16
+            # [tile][hi][g][mma][khalf][t][elem] -> [tile][g][t][mma][khalf][hi][elem]
+            x = sl.view(tiles, 2, 8, 2, 2, 4, 2).permute(0, 2, 5, 3, 4, 1, 6)
+        out.append(x.contiguous().view(torch.uint8).reshape(-1))
+    return torch.cat(out)
