@@ -74,3 +74,55 @@ def test_bf16_three_piece_split_carries_24_bits():
     p2 = r2.to(torch.bfloat16)
     err = (p0.float() + p1.float() + p2.float() - x).abs()
     assert (err <= x.abs() * 2.0 ** -23).all()
+
+
+def test_down_col_slices_are_in_mma_fragment_order():
+    """Reading the packed column slices the way the tensor-core instruction reads its first operand
+    (lane (g, t): rows g, g + 8; int8: columns 4t..4t+3 and 16+4t..; bf16: per instruction columns 2t, 2t+1
+    and 8+2t, 9+2t) reproduces the plain matrix-vector product, summed over the CTAs' slices."""
+    import torch
+    from megakernels_b200.pack import down_col_range, pack_down_cols
+    torch.manual_seed(0)
+    n, k, grid = 32, 3584, 148
+    tiles = n // 16
+    w8 = torch.randint(-127, 128, (n, k), dtype=torch.int8)
+    x = torch.randint(-60, 60, (k,), dtype=torch.int64)
+    p = pack_down_cols(w8, grid)
+    assert p.numel() == grid * tiles * 512
+    acc = torch.zeros(n, dtype=torch.int64)
+    covered = 0
+    for c in range(grid):
+        a0, a1 = down_col_range(k, c, grid)
+        assert a0 == covered and a1 - a0 <= 32
+        covered = a1
+        xs = torch.zeros(32, dtype=torch.int64)
+        xs[: a1 - a0] = x[a0:a1]
+        sl = p[c * tiles * 512: (c + 1) * tiles * 512].view(torch.int8).view(tiles, 32, 4, 4).long()   # [tile][lane][register][byte]
+        for lane in range(32):
+            g, t = lane >> 2, lane & 3
+            lo, hi = xs[4 * t: 4 * t + 4], xs[16 + 4 * t: 16 + 4 * t + 4]
+            for tile in range(tiles):
+                r = sl[tile, lane]
+                acc[tile * 16 + g] += (r[0] * lo).sum() + (r[2] * hi).sum()
+                acc[tile * 16 + g + 8] += (r[1] * lo).sum() + (r[3] * hi).sum()
+    assert covered == k
+    assert torch.equal(acc, w8.long() @ x)
+    wb = torch.randn(n, k).to(torch.bfloat16)
+    xf = torch.randn(k, dtype=torch.float64)
+    p = pack_down_cols(wb, grid)
+    assert p.numel() == grid * tiles * 1024
+    accf = torch.zeros(n, dtype=torch.float64)
+    for c in range(grid):
+        a0, a1 = down_col_range(k, c, grid)
+        xs = torch.zeros(32, dtype=torch.float64)
+        xs[: a1 - a0] = xf[a0:a1]
+        sl = p[c * tiles * 1024: (c + 1) * tiles * 1024].view(torch.bfloat16).view(tiles, 32, 2, 4, 2).double()   # [tile][lane][instruction][register][element]
+        for lane in range(32):
+            g, t = lane >> 2, lane & 3
+            for m in range(2):
+                lo, hi = xs[16 * m + 2 * t: 16 * m + 2 * t + 2], xs[16 * m + 8 + 2 * t: 16 * m + 8 + 2 * t + 2]
+                for tile in range(tiles):
+                    r = sl[tile, lane, m]
+                    accf[tile * 16 + g] += (r[0] * lo).sum() + (r[2] * hi).sum()
+                    accf[tile * 16 + g + 8] += (r[1] * lo).sum() + (r[3] * hi).sum()
+    assert torch.allclose(accf, wb.double() @ xf, atol=1e-9)
