@@ -55,6 +55,7 @@ enum {
     MK_L_V_CACHE,
     MK_L_KIND,          /* 0 = Gated DeltaNet, 1 = gated full attention (a value, not a pointer) */
     MK_L_CONV_HIST_B,   /* fp32 [batch, 16 heads, 384 channels, 8]: conv history of batched decoding (0 if unused) */
+    MK_L_W_OUT_ROWS,    /* DeltaNet layers: out-projection in the row-slice layout, the batched kernel's copy (0 if unused) */
     MK_L_W_DOWN_ROWS,   /* down-projection in the row-slice layout of the other matrices: the batched kernel's copy (0 if unused) */
     MK_LAYER_FIELDS
 };

@@ -50,6 +50,7 @@ static void fill_layer(LayerP& L, const int64_t* f) {
     L.w_gu = as_ptr<const uint8_t*>(f[MK_L_W_GU]);
     L.w_down = as_ptr<const uint8_t*>(f[MK_L_W_DOWN]);
     L.w_down_rows = as_ptr<const uint8_t*>(f[MK_L_W_DOWN_ROWS]);
+    L.w_out_rows = as_ptr<const uint8_t*>(f[MK_L_W_OUT_ROWS]);
     L.s_in = as_ptr<const float*>(f[MK_L_S_IN]);
     L.s_out = as_ptr<const float*>(f[MK_L_S_OUT]);
     L.s_gu = as_ptr<const float*>(f[MK_L_S_GU]);
@@ -420,8 +421,8 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     if ((uint64_t)a->epoch_base + ops * (uint64_t)a->n_steps >= 0xFFFFFF00ull || a->epoch_base == 0)
         return fail(MK_ERR_BADARG, "mk_launch_batch: epoch counter exhausted or zero; reset the engine");
     for (int l = 0; l < e->desc.n_layers; l++)
-        if ((e->host.layer[l].kind == 0 && !e->host.layer[l].conv_hist_b) || !e->host.layer[l].w_down_rows)
-            return fail(MK_ERR_BADARG, "mk_launch_batch: layer %d lacks the batched kernel's buffers (MK_L_CONV_HIST_B, MK_L_W_DOWN_ROWS)", l);
+        if ((e->host.layer[l].kind == 0 && (!e->host.layer[l].conv_hist_b || !e->host.layer[l].w_out_rows)) || !e->host.layer[l].w_down_rows)
+            return fail(MK_ERR_BADARG, "mk_launch_batch: layer %d lacks the batched kernel's buffers (MK_L_CONV_HIST_B, MK_L_W_OUT_ROWS, MK_L_W_DOWN_ROWS)", l);
 
     BatchArgs A;
     memset(&A, 0, sizeof A);

@@ -406,7 +406,7 @@ __device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A) {
         for (int l = 0; l < P.n_layers && !pr.stop; l++) {
             const LayerP& L = P.layer[l];
             pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID);
-            pr.stream(L.w_out, S::HID, 1, S::MIX);
+            pr.stream(L.kind ? L.w_out : L.w_out_rows, S::HID, 1, S::MIX);
             pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID);
             pr.stream(L.w_down_rows, S::HID, 1, S::INTER);
         }

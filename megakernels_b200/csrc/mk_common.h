@@ -57,6 +57,7 @@ struct LayerP {
     const uint8_t* w_gu;
     const uint8_t* w_down;        // single-sequence kernels: column slices per CTA in fragment order (pack_down_cols)
     const uint8_t* w_down_rows;   // batched kernel: row slices per CTA (pack_rows)
+    const uint8_t* w_out_rows;    // batched kernel, DeltaNet layers: row slices (single-sequence kernels: w_out holds column slices per task)
     const float* s_in;
     const float* s_out;
     const float* s_gu;

@@ -43,6 +43,7 @@ struct Smem {
     float* scale_s;     // per-row scales: two 128-row buffers for layer GEMVs, then the streaming ring
     float* xscale_s;    // [T] power-of-two factors that undo the fixed-point scaling of the staged inputs
     float* act_s;       // [T][DOWN_K] this CTA's SwiGLU outputs (entries past its slice stay zero)
+    float* mix_s;       // [T][DOWN_K] this DeltaNet task's gated outputs (16 value columns, the rest zero)
     float* ssq_s;       // batched decoding: [sequence][NCW] per-warp sums of squares of the RMSNorm input staged last
     float* wsc_s;       // batched decoding: [NCW][sequence] inverse fixed-point scales of each warp's k-slice
     uint64_t* full;     // [ring stages]
@@ -596,7 +597,8 @@ __device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
     constexpr int WB = Q8 ? 1 : 2;  // bytes per weight
     auto layer = [&](const LayerP& L) {
         pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID * WB);
-        pr.stream(L.w_out, S::HID, 1, S::MIX * WB);
+        if (L.kind) pr.stream(L.w_out, S::HID, 1, S::MIX * WB);
+        else if (c.cta < S::GDN_TASKS) pr.stream(L.w_out, (S::HID / 16) * c.grid, S::HID / 16, 512);   // the task's column slice: 64 tiles
         pr.stream(L.w_gu, 2 * S::INTER, 2, S::HID * WB);
         pr.stream(L.w_down, (S::HID / 16) * c.grid, S::HID / 16, 16 * DOWN_K * WB);   // this CTA's column slice: 64 tiles
     };
@@ -686,12 +688,110 @@ __device__ __forceinline__ void load_embedding(const Params& P, int token, int t
     }
 }
 
+// ---- split-K projection of values that only this CTA holds -------------------------------------------
+// `act` ([T][DOWN_K] in shared memory, zero past the CTA's slice) times the CTA's column slice of a
+// matrix (S::HID / 16 tiles in fragment order out of the ring, see pack_col_slices): 1024 partial sums
+// per token, published as hand-off words `out[token * tok_stride + row]`.  One MMA covers a 16-row
+// tile's whole K, so results leave the registers directly: no partial sums in shared memory, no
+// barrier.  Every warp derives the B fragments itself.  KM = bf16 MMAs per tile (columns / 16); the
+// integer MMA always spans 32 columns.
+template <class S, bool Q8, int T, int KM>
+__device__ __forceinline__ void partial_cols(Ctx& c, const float* act, u64* out, size_t tok_stride, uint32_t epoch) {
+    constexpr int WB = Q8 ? 1 : 2;
+    constexpr int TILES = S::HID / 16, TILE_BYTES = Q8 ? 16 * DOWN_K : 16 * 16 * KM * WB, TPC = SLOT_BYTES / TILE_BYTES;
+    static_assert(TPC % NCW == 0 && TILES % TPC == 0, "whole rounds of 16 tiles per ring chunk");
+    const int g = c.lane >> 2, t = c.lane & 3, tok = g >> 2, piece = g & 3;
+    uint32_t bf[Q8 ? 2 : 2 * KM] = {};      // B fragments of plane g = 4 * token + digit / piece
+    float inv_scale[T];
+#pragma unroll
+    for (int j = 0; j < T; j++) {
+        const float* a = act + j * DOWN_K;
+        const float scale = Q8 ? fixed_scale(warp_max(fabsf(a[c.lane]))) : 1.0f;
+        inv_scale[j] = 1.0f / scale;
+        if (tok == j && piece < Planes<Q8>::N) {
+            if (Q8) {
+#pragma unroll
+                for (int hf = 0; hf < 2; hf++) {
+                    uint32_t pk = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int q = __float2int_rn(a[16 * hf + 4 * t + i] * scale);
+                        const int d = piece < 3 ? ((q >> (7 * piece)) & 127) : (q >> 21);
+                        pk |= (uint32_t)(d & 255) << (8 * i);
+                    }
+                    bf[hf] = pk;
+                }
+            } else {
+#pragma unroll
+                for (int f = 0; f < 2 * KM; f++) {      // mma f / 2, low or high 8 columns
+                    uint32_t pk = 0;
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        float v = a[16 * (f >> 1) + 8 * (f & 1) + 2 * t + i];
+                        __nv_bfloat16 pb = __float2bfloat16_rn(v);
+#pragma unroll
+                        for (int d = 0; d < 2; d++)
+                            if (d < piece) {
+                                v -= __bfloat162float(pb);
+                                pb = __float2bfloat16_rn(v);
+                            }
+                        pk |= (uint32_t)__bfloat16_as_ushort(pb) << (16 * i);
+                    }
+                    bf[f] = pk;
+                }
+            }
+        }
+    }
+    const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);   // 128^(2 * (t & 1)) for the int8 digits
+    const float pw1 = pw0 * 128.f;
+    const int otok = t >> 1;                                                     // token whose sums this lane ends up with
+    const float os = inv_scale[otok < T ? otok : 0];
+    u64* dst = out + (size_t)(otok < T ? otok : 0) * tok_stride;
+    for (int base = 0; base < TILES; base += TPC) {
+        const uint32_t n = c.cons_n++;
+        const int slot = (int)(n % Geo<T>::NS);
+        mbar_wait(c, &c.sm.full[slot], (n / Geo<T>::NS) & 1, W_FULL);
+        const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
+#pragma unroll
+        for (int i = 0; i < TPC / NCW; i++) {
+            const int tile = c.warp + NCW * i;
+            const uint8_t* wt = buf + (size_t)tile * TILE_BYTES + c.lane * (Q8 ? 16 : 16 * KM);
+            float lo, hi;
+            if (Q8) {
+                const uint4 w0 = *reinterpret_cast<const uint4*>(wt);
+                int ci[4] = {0, 0, 0, 0};
+                mma_s8(ci, w0.x, w0.y, w0.z, w0.w, bf[0], bf[1]);
+                lo = (float)ci[0] * pw0 + (float)ci[1] * pw1;
+                hi = (float)ci[2] * pw0 + (float)ci[3] * pw1;
+            } else {
+                float cf[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int m = 0; m < KM; m++) {
+                    const uint4 w0 = *reinterpret_cast<const uint4*>(wt + 16 * m);
+                    mma_bf16(cf, w0.x, w0.y, w0.z, w0.w, bf[Q8 ? 0 : 2 * m], bf[Q8 ? 1 : 2 * m + 1]);
+                }
+                lo = cf[0] + cf[1];
+                hi = cf[2] + cf[3];
+            }
+            lo += __shfl_xor_sync(0xffffffffu, lo, 1);
+            hi += __shfl_xor_sync(0xffffffffu, hi, 1);
+            if ((t & 1) == 0 && otok < T) {
+                const int row = (base + tile) * 16 + g;
+                ll_store(dst + row, epoch, lo * os);
+                ll_store(dst + row + 8, epoch, hi * os);
+            }
+        }
+        __syncwarp();
+        if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
+    }
+}
+
 // ---- Gated DeltaNet recurrence ------------------------------------------------------------------------
 // Task t < GDN_TASKS: head t / 8, value columns [16 * (t % 8), +16).  Warp w owns value column w of the
 // slice; a lane holds 4 consecutive key indices of that column's state row.  With two tokens the task
 // runs them one after the other: the state after the first token goes to `state_bak`, the state after
 // the second to `state`, and `from_bak` says which of the two the previous cycle left valid.
-template <class S, int T>
+template <class S, bool Q8, int T>
 __device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32_t e_proj, uint32_t e_out, int op,
                        bool from_bak) {
     static_assert(S::GDN_SLICE == NCW && S::LIN_DK == 128, "one warp per value column, 4 keys per lane");
@@ -700,8 +800,9 @@ __device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
     const int h = c.cta / SL, j = c.cta % SL;
     const int vcol = j * S::GDN_SLICE + c.warp;
     constexpr int NCH = 2 * S::LIN_DK + S::GDN_SLICE;           // 272 conv channels this task needs
-    constexpr int QS = NCH + 8;                                 // per-token stride of the scratch
-    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);           // per token: [q 128 | k 128 | v 16 | b | a]
+    constexpr int QS = NCH + 2 + S::GDN_SLICE + 6;              // per-token stride of the scratch
+    float* qkv_s = reinterpret_cast<float*>(c.sm.xq);           // per token: [q 128 | k 128 | v 16 | b | a | z 16]
+    float* osq = c.sm.red_s + (c.red_n++ & 1) * (2 * T * NCW);  // [token][warp] squared outputs
     const size_t soff = ((size_t)(h * S::LIN_DV + vcol) * S::LIN_DK) + 4 * c.lane;
     const float* sin = (T == 2 && from_bak) ? L.state_bak + soff : L.state + soff;
     const float4 st = *reinterpret_cast<const float4*>(sin);    // issued before the wait on purpose
@@ -745,12 +846,15 @@ __device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
             hist[(pos + tk) & (CONV_RING - 1)] = cur[tk];
             h3 = h2; h2 = h1; h1 = cur[tk];
         }
-    } else if (c.tid < NCH + 2) {
-        const int off = (c.tid == NCH ? S::B_OFF : S::A_OFF) + h;
+    } else if (c.tid < NCH + 2 + S::GDN_SLICE) {
+        // b, a of the head, then z of this task's value columns
+        const int off = c.tid == NCH ? S::B_OFF + h
+                                     : (c.tid == NCH + 1 ? S::A_OFF + h : S::Z_OFF + h * S::LIN_DV + j * S::GDN_SLICE + (c.tid - NCH - 2));
 #pragma unroll
         for (int tk = 0; tk < T; tk++)
             qkv_s[tk * QS + c.tid] = ll_wait(c, P.projl + (size_t)tk * S::PROJ_MAX + off, e_proj, W_PROJ);
     }
+    const float gw = L.gdn_norm[vcol];
     consumer_sync();
     prof_stamp(c, op, 1);
     float s0 = st.x, s1 = st.y, s2 = st.z, s3 = st.w;
@@ -778,10 +882,24 @@ __device__ bool gdn_op(Ctx& c, const Params& P, const LayerP& L, int pos, uint32
         float* sout = (T == 2 && tk == 0) ? L.state_bak + soff : L.state + soff;
         *reinterpret_cast<float4*>(sout) = make_float4(s0, s1, s2, s3);
         const float o = warp_sum(fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)))) * qs;
-        if (c.lane == 0) ll_store(P.mixl + (size_t)tk * S::MIX + h * S::LIN_DV + vcol, e_out, o);
+        // The elementwise part of the gated norm (weight, silu(z)) is applied here; the head's 1 / rms
+        // needs the squared outputs of the head's eight tasks and is applied by whoever sums the tasks'
+        // partial out-projections: this task publishes its sum of squares beside them.
+        if (c.lane == 0) {
+            c.sm.mix_s[tk * DOWN_K + c.warp] = o * gw * silu_f(qs_[NCH + 2 + c.warp]);
+            osq[tk * NCW + c.warp] = o * o;
+        }
     }
     prof_stamp(c, op, 2);
     consumer_sync();  // the scratch aliases the GEMV input vector that the next prologue writes
+    if (c.tid < T) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < NCW; w++) tot += osq[c.tid * NCW + w];
+        ll_store(P.mixl + (size_t)c.tid * S::MIX + c.cta, e_out, tot);
+    }
+    // out-projection, split over K: this task's 16 gated outputs times its column slice -> 1024 partial sums
+    partial_cols<S, Q8, T, 1>(c, c.sm.mix_s, P.partl + (size_t)c.cta * S::HID, (size_t)c.grid * S::HID, e_out);
     return true;
 }
 
@@ -1234,10 +1352,63 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
     prof_stamp(c, op0 + 1, 0);
     const AttnView view = {c.cta, c.grid, P.projl, P.mixl, P.attn_part, c.sm.bt_s, false};
     const bool had_task = attn ? attn_op<S, KVF32, T>(c, P, L, view, pos, eA, eB, op0 + 1)
-                               : gdn_op<S, T>(c, P, L, pos, eA, eB, op0 + 1, from_bak);
+                               : gdn_op<S, Q8, T>(c, P, L, pos, eA, eB, op0 + 1, from_bak);
     prof_stamp(c, op0 + 1, 3);
     // ---- C: out-projection + residual
-    {
+    if (!attn) {
+        // DeltaNet: the tasks have already multiplied their outputs with their column slices.  Warp r
+        // sums the 128 partial sums of owned row r, each weighted with its head's 1 / rms: lane l takes
+        // tasks l, l + 32, l + 64, l + 96, whose heads' eight tasks are eight consecutive lanes.
+        const int op = op0 + 2;
+        prof_stamp(c, op, 0);
+        static_assert(S::GDN_TASKS == 128 && S::LIN_DV / S::GDN_SLICE == 8, "four tasks per lane, eight per head");
+        if (c.warp < xr1 - xr0) {
+            const int row = xr0 + c.warp;
+            const float rs = Q8 ? L.s_out[row] : 1.0f;           // requested before the wait
+#pragma unroll
+            for (int j = 0; j < T; j++) {
+                const u64* psrc = P.partl + (size_t)j * c.grid * S::HID + row;
+                const u64* ssrc = P.mixl + (size_t)j * S::MIX;
+                u64 w[4], sw[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    w[i] = ll_load(psrc + (size_t)(c.lane + 32 * i) * S::HID);
+                    sw[i] = ll_load(ssrc + c.lane + 32 * i);
+                }
+                Spin sp;
+                while (true) {
+                    bool ok = true;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        if ((uint32_t)(w[i] >> 32) != eB) { ok = false; w[i] = ll_load(psrc + (size_t)(c.lane + 32 * i) * S::HID); }
+                        if ((uint32_t)(sw[i] >> 32) != eB) { ok = false; sw[i] = ll_load(ssrc + c.lane + 32 * i); }
+                    }
+                    if (ok) break;
+                    if (MK_SPIN_FAIL(c, sp, W_MIX)) {
+                        c.dead = true;
+                        break;
+                    }
+                }
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float hs = __uint_as_float((uint32_t)sw[i]);      // sum of squares over the head: 8 lanes
+                    hs += __shfl_xor_sync(0xffffffffu, hs, 1);
+                    hs += __shfl_xor_sync(0xffffffffu, hs, 2);
+                    hs += __shfl_xor_sync(0xffffffffu, hs, 4);
+                    acc += __uint_as_float((uint32_t)w[i]) * rsqrtf(hs * (1.0f / S::LIN_DV) + S::EPS);
+                }
+                const float tot = warp_sum(acc);
+                if (c.lane == 0) {
+                    const float xn = c.sm.xown[j * 16 + c.warp] + tot * rs;
+                    c.sm.xown[j * 16 + c.warp] = xn;
+                    ll_store(xbuf + (size_t)j * S::HID + row, eC, xn);
+                }
+            }
+        }
+        prof_stamp(c, op, 3);
+        consumer_sync();   // keep the other warps' polls for the next op behind these stores
+    } else {
         const int op = op0 + 2;
         prof_stamp(c, op, 0);
         scale_prefetch(c, L.s_out, xr0, xr1, false);
@@ -1318,94 +1489,8 @@ __device__ __forceinline__ bool run_layer(Ctx& c, const Params& P, const LayerP&
             const float up = __shfl_down_sync(0xffffffffu, v, 1);
             if (ok && !(lane & 1)) c.sm.act_s[tk * DOWN_K + ((row - r0) >> 1)] = silu_f(v) * up;
         });
-        // ---- down-projection, split over K: 1024 partial sums from this CTA's <= 32 activations.
-        // One MMA covers a 16-row tile's whole K, so results leave the registers as hand-off words:
-        // no partial sums in shared memory, no barrier.  Every warp derives the B fragments itself.
-        {
-            constexpr int TILES = S::HID / 16, TILE_BYTES = 16 * DOWN_K * WB, TPC = SLOT_BYTES / TILE_BYTES;
-            static_assert(TPC % NCW == 0 && TILES % TPC == 0, "whole rounds of 16 tiles per ring chunk");
-            const int g = c.lane >> 2, t = c.lane & 3, tok = g >> 2, piece = g & 3;
-            uint32_t bf[Q8 ? 2 : 4] = {};       // B fragments of plane g = 4 * token + digit / piece
-            float inv_scale[T];
-#pragma unroll
-            for (int j = 0; j < T; j++) {
-                const float* a = c.sm.act_s + j * DOWN_K;
-                const float scale = Q8 ? fixed_scale(warp_max(fabsf(a[c.lane]))) : 1.0f;
-                inv_scale[j] = 1.0f / scale;
-                if (tok == j && piece < Planes<Q8>::N) {
-                    if (Q8) {
-#pragma unroll
-                        for (int hf = 0; hf < 2; hf++) {
-                            uint32_t pk = 0;
-#pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const int q = __float2int_rn(a[16 * hf + 4 * t + i] * scale);
-                                const int d = piece < 3 ? ((q >> (7 * piece)) & 127) : (q >> 21);
-                                pk |= (uint32_t)(d & 255) << (8 * i);
-                            }
-                            bf[hf] = pk;
-                        }
-                    } else {
-#pragma unroll
-                        for (int f = 0; f < 4; f++) {           // mma f / 2, low or high 8 columns
-                            uint32_t pk = 0;
-#pragma unroll
-                            for (int i = 0; i < 2; i++) {
-                                float v = a[16 * (f >> 1) + 8 * (f & 1) + 2 * t + i];
-                                __nv_bfloat16 pb = __float2bfloat16_rn(v);
-#pragma unroll
-                                for (int d = 0; d < 2; d++)
-                                    if (d < piece) {
-                                        v -= __bfloat162float(pb);
-                                        pb = __float2bfloat16_rn(v);
-                                    }
-                                pk |= (uint32_t)__bfloat16_as_ushort(pb) << (16 * i);
-                            }
-                            bf[f] = pk;
-                        }
-                    }
-                }
-            }
-            const float pw0 = __uint_as_float((uint32_t)(127 + 14 * (t & 1)) << 23);   // 128^(2 * (t & 1)) for the int8 digits
-            const float pw1 = pw0 * 128.f;
-            const int otok = t >> 1;                                                     // token whose sums this lane ends up with
-            const float os = inv_scale[otok < T ? otok : 0];
-            u64* out = P.partl + ((size_t)(otok < T ? otok : 0) * c.grid + c.cta) * S::HID;
-            for (int base = 0; base < TILES; base += TPC) {
-                const uint32_t n = c.cons_n++;
-                const int slot = (int)(n % Geo<T>::NS);
-                mbar_wait(c, &c.sm.full[slot], (n / Geo<T>::NS) & 1, W_FULL);
-                const uint8_t* buf = c.sm.ring + (size_t)slot * SLOT_BYTES;
-#pragma unroll
-                for (int i = 0; i < TPC / NCW; i++) {
-                    const int tile = c.warp + NCW * i;
-                    const uint4 w0 = *reinterpret_cast<const uint4*>(buf + (size_t)tile * TILE_BYTES + c.lane * (16 * WB));
-                    float lo, hi;
-                    if (Q8) {
-                        int ci[4] = {0, 0, 0, 0};
-                        mma_s8(ci, w0.x, w0.y, w0.z, w0.w, bf[0], bf[1]);
-                        lo = (float)ci[0] * pw0 + (float)ci[1] * pw1;
-                        hi = (float)ci[2] * pw0 + (float)ci[3] * pw1;
-                    } else {
-                        const uint4 w1 = *reinterpret_cast<const uint4*>(buf + (size_t)tile * TILE_BYTES + c.lane * 32 + 16);
-                        float cf[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_bf16(cf, w0.x, w0.y, w0.z, w0.w, bf[0], bf[1]);
-                        mma_bf16(cf, w1.x, w1.y, w1.z, w1.w, bf[Q8 ? 0 : 2], bf[Q8 ? 1 : 3]);
-                        lo = cf[0] + cf[1];
-                        hi = cf[2] + cf[3];
-                    }
-                    lo += __shfl_xor_sync(0xffffffffu, lo, 1);
-                    hi += __shfl_xor_sync(0xffffffffu, hi, 1);
-                    if ((t & 1) == 0 && otok < T) {
-                        const int row = (base + tile) * 16 + g;
-                        ll_store(out + row, eD, lo * os);
-                        ll_store(out + row + 8, eD, hi * os);
-                    }
-                }
-                __syncwarp();
-                if (c.lane == 0 && !c.dead) mbar_arrive(&c.sm.empty[slot]);
-            }
-        }
+        // ---- down-projection, split over K: 1024 partial sums from this CTA's <= 32 activations
+        partial_cols<S, Q8, T, DOWN_K / 16>(c, c.sm.act_s, P.partl + (size_t)c.cta * S::HID, (size_t)c.grid * S::HID, eD);
         prof_stamp(c, op, 3);
     }
     // ---- E: sum of the CTAs' partial down-projections + residual, for the rows this CTA owns
@@ -1489,13 +1574,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const int pslot, co
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.act_s = reinterpret_cast<float*>(p); p += SPEC_T * DOWN_K * 4;
+        c.sm.mix_s = reinterpret_cast<float*>(p); p += SPEC_T * DOWN_K * 4;
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
     c.cons_n = 0; c.red_n = 0; c.dead = false; c.prof = nullptr; c.wait_acc = 0; c.cur_op = 0; c.gemv_n = 0;
     c.limit_ns = (u64)A.spin_limit_ns;
     c.status = P.status;
-    if (c.tid < SPEC_T * DOWN_K) c.sm.act_s[c.tid] = 0.f;
+    if (c.tid < SPEC_T * DOWN_K) c.sm.act_s[c.tid] = c.sm.mix_s[c.tid] = 0.f;
     if (c.tid == 0) {
         for (int i = 0; i < NS; i++) {
             mbar_init(&c.sm.full[i], 1);

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from . import mtp as mtp_mod
 from .config import Config
-from .pack import as_bytes, pack_down_cols, pack_rows
+from .pack import as_bytes, pack_down_cols, pack_out_cols, pack_rows
 from .quant import is_gemv_weight, quantize_int8_rows, roundtrip_int8_rows
 
 # Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
@@ -169,7 +169,13 @@ class Megakernel:
                 w_in = torch.cat([w[p + "in_proj_qkv.weight"], w[p + "in_proj_z.weight"],
                                   w[p + "in_proj_b.weight"], w[p + "in_proj_a.weight"]])
                 rec["w_in"], rec["s_in"] = mat(w_in)
-                rec["w_out"], rec["s_out"] = mat(w[p + "out_proj.weight"])
+                # a recurrence task multiplies its 16 outputs with its column slice of the out-projection
+                # itself; the batched kernel takes row slices like every other matrix
+                om, osc = plain(w[p + "out_proj.weight"])
+                rec["w_out"] = keep(pack_out_cols(om, self.GDN_TASKS, self.GDN_SLICE))
+                rec["s_out"] = keep(osc) if osc is not None else 0
+                if q8:      # run_batch is available on every int8 engine
+                    rec["w_out_rows"] = keep(pack_rows(as_bytes(om), 1, self.grid, slot_bytes))
                 rec["conv_w"] = f32(w[p + "conv1d.weight"].reshape(-1, cfg.conv_k))
                 rec["A_log"] = f32(w[p + "A_log"])
                 rec["dt_bias"] = f32(w[p + "dt_bias"])

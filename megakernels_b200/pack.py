@@ -96,29 +96,47 @@ def down_col_range(inter, cta, grid):
     return r0 // 2, r1 // 2
 
 
-def pack_down_cols(w, grid):
-    """[N, K] int8 or bf16 weights -> uint8 [grid * (N / 16) * tile_bytes]: per CTA its column slice as
-    N / 16 tiles of 16 rows x 32 columns in fragment order.
+def _fragment_tiles(sl):
+    """[N, kpad] int8 (kpad 32) or bf16 (kpad 16 or 32) -> bytes of its 16-row tiles in fragment order.
 
     int8 (mma m16n8k32): lane (g, t) of a tile holds rows g and g + 8, columns 4t..4t+3 and 16+4t..16+4t+3,
     as four 32-bit registers [row g | row g + 8] x [low columns | high columns] -> 16 bytes per lane.
-    bf16 (two mma m16n8k16 per tile): per instruction rows g, g + 8 and columns 2t, 2t+1 and 8+2t, 9+2t of
-    its 16 columns -> 16 bytes per lane and instruction, the two instructions of a tile back to back."""
-    n, k = w.shape
-    assert n % 16 == 0
+    bf16 (one mma m16n8k16 per 16 columns): per instruction rows g, g + 8 and columns 2t, 2t+1 and 8+2t,
+    9+2t of its 16 columns -> 16 bytes per lane and instruction, a tile's instructions back to back."""
+    n, kpad = sl.shape
     tiles = n // 16
+    if sl.dtype == torch.int8:
+        assert kpad == 32
+        # [tile][hi][g][khalf][t][byte] -> [tile][g][t][khalf][hi][byte]
+        x = sl.view(tiles, 2, 8, 2, 4, 4).permute(0, 2, 4, 3, 1, 5)
+    else:
+        assert sl.dtype == torch.bfloat16 and kpad % 16 == 0
+        # [tile][hi][g][mma][khalf][t][elem] -> [tile][g][t][mma][khalf][hi][elem]
+        x = sl.view(tiles, 2, 8, kpad // 16, 2, 4, 2).permute(0, 2, 5, 3, 4, 1, 6)
+    return x.contiguous().view(torch.uint8).reshape(-1)
+
+
+def pack_col_slices(w, ranges, kpad):
+    """Column slices [a0, a1) of `w` ([N, K] int8 or bf16), each zero-padded to `kpad` columns and stored as
+    N / 16 tiles in fragment order, one slice after the other."""
+    n = w.shape[0]
+    assert n % 16 == 0
     out = []
-    for c in range(grid):
-        a0, a1 = down_col_range(k, c, grid)
-        assert a1 - a0 <= DOWN_K
-        sl = torch.zeros(n, DOWN_K, dtype=w.dtype, device=w.device)
+    for a0, a1 in ranges:
+        assert 0 < a1 - a0 <= kpad
+        sl = torch.zeros(n, kpad, dtype=w.dtype, device=w.device)
         sl[:, : a1 - a0] = w[:, a0:a1]
-        if w.dtype == torch.int8:
-            # [tile][hi][g][khalf][t][byte] -> [tile][g][t][khalf][hi][byte]
-            x = sl.view(tiles, 2, 8, 2, 4, 4).permute(0, 2, 4, 3, 1, 5)
-        else:
-            assert w.dtype == torch.bfloat16
-            # [tile][hi][g][mma][khalf][t][elem] -> [tile][g][t][mma][khalf][hi][elem]
-            x = sl.view(tiles, 2, 8, 2, 2, 4, 2).permute(0, 2, 5, 3, 4, 1, 6)
-        out.append(x.contiguous().view(torch.uint8).reshape(-1))
+        out.append(_fragment_tiles(sl))
     return torch.cat(out)
+
+
+def pack_down_cols(w, grid):
+    """Down-projection [N, K]: per CTA the columns of the SwiGLU outputs it produces, padded to 32."""
+    return pack_col_slices(w, [down_col_range(w.shape[1], c, grid) for c in range(grid)], DOWN_K)
+
+
+def pack_out_cols(w, tasks, cols):
+    """DeltaNet out-projection [N, tasks * cols]: per recurrence task the `cols` value columns it owns
+    (int8: padded to the 32 columns of one integer MMA; bf16: exactly one 16-column MMA)."""
+    kpad = DOWN_K if w.dtype == torch.int8 else cols
+    return pack_col_slices(w, [(t * cols, (t + 1) * cols) for t in range(tasks)], kpad)
