@@ -37,7 +37,7 @@ L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per decode step, from the ncu captures
 # summarised under profiles/ (short launches at a short context, scaled by steps; the KV part grows with
 # context, the weight part does not): decode_kernel at batch 1, batch_kernel at batch 8.
-NCU_DRAM_BYTES_PER_STEP = {1: (10.512750e9 + 393.956352e6) / 16, 8: (13.618422e9 + 3.158837e9) / 16}
+NCU_DRAM_BYTES_PER_STEP = {1: (11.604932e9 + 394.075904e6) / 16, 8: (13.618422e9 + 3.158837e9) / 16}
 
 
 def measured_peak_gbs():
