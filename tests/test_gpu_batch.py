@@ -220,3 +220,31 @@ def test_full_size_batch_against_the_reference_fixture(lib_built):
         alone, alone_logits = mk.run(prompts[j], n_generate=n_gen, return_logits=True)
         assert ids[j] == alone, j
         assert float((logits[j] - alone_logits).abs().max()) < 1e-3
+
+
+def test_long_context_where_attention_chunks_grow(tiny, lib_built):
+    """With eight sequences each sequence has 18 CTAs for attention, so the positions one task scans grow
+    from 16 to 64 and 128 within the first thousand positions.  Ragged prompts of 500 to 900 tokens put the
+    sequences in different regimes in the same pass; every sequence must equal the single-sequence kernel,
+    and two of them the oracle."""
+    from oracle.decoder import pick_token
+    cfg, w = tiny
+    lengths = [900, 577, 640, 500, 833, 576, 705, 513]
+    prompts = prompts_for(cfg, lengths)
+    mk = engine(cfg, w, batch=8, max_seq=1024)
+    ids, logits = mk.run_batch(prompts, n_generate=12, return_logits=True)
+    for j, prompt in enumerate(prompts):
+        mk.reset()
+        alone, alone_logits = mk.run(prompt, n_generate=12, return_logits=True)
+        assert ids[j] == alone, j
+        assert float((logits[j] - alone_logits).abs().max()) < 1e-3
+    for j in (0, 5):
+        dec = oracle(cfg, w, max_seq=1024)
+        for t in prompts[j][:-1]:
+            dec.step(t)
+        ref = dec.step(prompts[j][-1])
+        for i, got in enumerate(ids[j]):
+            assert float((logits[j][i].cpu() - ref).abs().max()) < LOGIT_TOL
+            assert got == pick_token(ref), (j, i)
+            if i + 1 < len(ids[j]):
+                ref = dec.step(got)
