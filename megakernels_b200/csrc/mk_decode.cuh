@@ -317,8 +317,8 @@ __device__ __forceinline__ void consumer_sum_max(Ctx& c, float (&sum)[T], float 
 //   bf16 weights: x = p0 + p1 + p2 with three bf16 pieces (24 significant bits); bf16 MMAs with fp32
 //                 accumulation.
 // Plane 4 * token + piece of the staged input is MMA column 4 * token + piece, so one MMA serves every
-// plane of up to two tokens.  Each warp owns a k-slice (k-blocks warp, warp + 16, ...) of every row of
-// a chunk; per-warp partial sums meet in shared memory.
+// plane of up to two tokens.  Each warp owns a contiguous k-slice of every row of a chunk; per-warp
+// partial sums meet in shared memory.
 template <bool Q8> struct Planes { static constexpr int N = Q8 ? 4 : 3; };
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -398,8 +398,10 @@ __device__ __forceinline__ void mma_blocks(const uint8_t* buf, const uint8_t* xr
     int ci[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
     float cf[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     const bool two = nr - b0 > 16;              // the second block has rows (projections that give a CTA 7 rows have none)
+    // a contiguous k-slice per warp: exactly the inputs the warp staged itself (see `stage_rmsnorm`)
+    const int kb0 = nkb * warp / NCW, kb1 = nkb * (warp + 1) / NCW;
 #pragma unroll 2
-    for (int kb = warp; kb < nkb; kb += NCW) {
+    for (int kb = kb0; kb < kb1; kb++) {
         uint4 w[4], x = make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int q = 0; q < 4; q++) {
@@ -646,7 +648,9 @@ __device__ __forceinline__ void stage_rmsnorm(Ctx& c, const float (&x)[T][2], fl
         stage_pair<Q8>(c.sm.xq + (size_t)(4 * j) * RB, RB, k, y[j][0], y[j][1], scale);
         if (c.tid == 0) c.sm.xscale_s[j] = 1.0f / scale;
     }
-    consumer_sync();
+    // No block barrier: a warp stages elements [64 w, 64 w + 64), which is the k-slice it multiplies;
+    // the inverse scales are read after the barrier that follows the MMAs.
+    __syncwarp();
 }
 
 // For inputs that need no norm: per-token fixed-point scales from this thread's largest magnitudes
@@ -662,14 +666,15 @@ __device__ __forceinline__ void block_scale(Ctx& c, float (&mx)[T], float (&scal
 #pragma unroll
     for (int j = 0; j < T; j++) scale[j] = Q8 ? fixed_scale(mx[j]) : 1.0f;
 }
-// ... and the end of a staging phase: publish the inverse scales, make the planes visible.
+// ... and the end of a staging phase: publish the inverse scales.  The caller's threads staged 4
+// consecutive inputs each, so a warp wrote exactly the k-slice it multiplies: no block barrier.
 template <int T>
 __device__ __forceinline__ void finish_stage(Ctx& c, const float (&scale)[T]) {
     if (c.tid == 0) {
 #pragma unroll
         for (int j = 0; j < T; j++) c.sm.xscale_s[j] = 1.0f / scale[j];
     }
-    consumer_sync();
+    __syncwarp();
 }
 
 // Embedding row of `token` -> this thread's two residual elements.
