@@ -235,6 +235,25 @@ def report(mk, batch, kernel_ms, wall_s, step_ns, args, world, device):
     }
 
 
+def measure_cfg1(args, device):
+    """bf16 weights, one sequence, 32-token prompt + 128 greedy steps per bench step (one launch)."""
+    global PROMPT, GENERATE
+    from megakernels_b200.engine import Megakernel
+    saved = PROMPT, GENERATE
+    PROMPT, GENERATE = 32, 128
+    try:
+        cfg, w, prompt = build_model("bf16")
+        mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant="bf16", kv_dtype=args.kv_dtype, device=device)
+        kernel_ms, wall_s, _, step_ns, _ = measure(mk, 1, [prompt], args, 1, device)
+        r = report(mk, 1, kernel_ms, wall_s, step_ns, args, 1, device)
+        r["roofline"]["traffic"] = None          # no ncu capture of the bf16 kernel is committed
+        return {"workload": "bf16 weights, batch 1, 32-token prompt + 128 greedy steps", "value": r["value"], "unit": "tok/s",
+                "ms_per_step": r["ms_per_step"], "median_decode_step_us": r["median_decode_step_us"],
+                "bytes_per_decode_step": r["bytes_per_decode_step"], "e2e": r["e2e"], "roofline": r["roofline"]}
+    finally:
+        PROMPT, GENERATE = saved
+
+
 def main():
     global PROMPT, GENERATE
     ap = argparse.ArgumentParser()
@@ -247,6 +266,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="sequences of the headline measurement (1..8; bf16 weights: 1)")
     ap.add_argument("--no-batch1", action="store_true", help="skip the batch-1 measurement beside a batched headline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cfg1", action="store_true", help="skip the bf16 configuration-1 measurement reported beside the headline")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="shrink the case (profiling only)")
     ap.add_argument("--generate", type=int, default=GENERATE, help="shrink the case (profiling only)")
     args = ap.parse_args()
@@ -282,6 +302,13 @@ def main():
         single = report(mk, 1, k1, w1, s1, args, world, device)
         launches += l1
 
+    # configuration 1 of the benchmark definition beside it: bf16 weights, batch 1, 32-token prompt, 128 greedy steps
+    cfg1 = None
+    if world == 1 and args.quant == "int8" and not args.no_cfg1 and (PROMPT, GENERATE) == (512, 512):
+        del mk
+        torch.cuda.empty_cache()
+        cfg1 = measure_cfg1(args, device)
+
     if rank != 0:
         return
     out = {
@@ -301,6 +328,8 @@ def main():
                          "median_decode_step_us": single["median_decode_step_us"],
                          "bytes_per_decode_step": single["bytes_per_decode_step"], "e2e": single["e2e"],
                          "roofline": single["roofline"]}
+    if cfg1:
+        out["cfg1_bf16"] = cfg1
     if world == 1 and not args.no_cpu_baseline:
         n_prompt, n_decode = 32, 48
         rate = cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode)[0]
