@@ -15,7 +15,9 @@ from megakernels_b200.synth import make_mtp_weights, make_prompt, make_weights
 from oracle.decoder import Decoder, MtpHead, mix32, pick_token, sample_key
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-REFERENCE = os.environ.get("MK_REFERENCE_ROOT", "/root/reference")
+# the reference checkout, when there is one: MK_REFERENCE_ROOT, or a `reference` directory beside this repository
+REFERENCE = os.environ.get("MK_REFERENCE_ROOT",
+                           os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 SMALL = [p for p in sorted(glob.glob(os.path.join(GOLDEN, "*.json")))
          if json.load(open(p))["n_layers"] <= 8]
 
