@@ -330,6 +330,10 @@ def main():
                          "roofline": single["roofline"]}
     if cfg1:
         out["cfg1_bf16"] = cfg1
+    if world == 1:
+        # the library's own read-bandwidth probes on this GPU, beside the driver-measured peak the fractions use
+        from megakernels_b200 import bw
+        out["roofline"]["bw_probe_gbs"] = {m: round(bw.measure(m, gib=2.0, reps=3, device=device), 1) for m in bw.MODES}
     if world == 1 and not args.no_cpu_baseline:
         n_prompt, n_decode = 32, 48
         rate = cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode)[0]
