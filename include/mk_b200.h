@@ -3,7 +3,7 @@
  * One cooperative launch runs every layer of one or many decode steps of a hybrid
  * Gated-DeltaNet / gated-attention decoder, the LM head and the sampling rule.  The caller owns
  * every device buffer and passes raw device addresses; the library keeps only a small host-side
- * handle and copies the pointer tables into constant memory.
+ * handle that holds the pointer tables.
  *
  * Each entry point names the reference interface it replaces, by the file's path in the
  * reference project (SamuelReeder/megakernels).  Nothing here throws: every function returns an
@@ -96,6 +96,8 @@ typedef struct mk_model_desc {
     int32_t draft_vocab;  /* rows of the draft head (0: no MTP head)           */
     int32_t device;       /* CUDA device ordinal                               */
     int32_t grid;         /* CTAs the weights were packed for (0: one per SM)  */
+    int32_t max_batch;    /* sequences the per-sequence buffers were sized for (0 or 1: one);
+                             mk_launch_batch refuses a larger batch                     */
 } mk_model_desc;
 
 /* Per-launch arguments.  Replaces `Args` of qwen3.5-0.8b/csrc/megakernel.h:134-161 and the 26
@@ -134,8 +136,9 @@ typedef struct mk_launch_args {
 typedef struct mk_engine mk_engine;
 
 /* Create / destroy a handle.  The reference keeps its parameter block in one process-wide
- * __constant__ symbol (qwen3.5-0.8b/csrc/megakernel.cu:22,1280-1283), so two engines alias; a
- * handle owns one of MK_MAX_ENGINES constant-memory slots instead. */
+ * __constant__ symbol (qwen3.5-0.8b/csrc/megakernel.cu:22,1280-1283), so two engines alias; here the
+ * handle owns its block and every launch passes it to the kernel by value, so any number of engines
+ * can live side by side. */
 int mk_create(const mk_model_desc* desc, mk_engine** out);
 int mk_destroy(mk_engine* e);
 
@@ -207,6 +210,7 @@ typedef struct mk_batch_args {
     uint64_t out_info;               /* int32[8]: steps run, next epoch, bit mask of stopped sequences */
     uint64_t prof;
     int64_t spin_limit_ns;
+    int64_t pf_bytes;                /* L2 prefetch distance ahead of the shared-memory ring, per CTA */
 } mk_batch_args;
 int mk_launch_batch(mk_engine* e, const mk_batch_args* args, void* stream);
 

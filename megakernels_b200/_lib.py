@@ -39,7 +39,7 @@ class MkError(RuntimeError):
 
 class ModelDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
-                ("shape", "n_layers", "vocab", "max_seq", "quant", "kv_dtype", "draft_vocab", "device", "grid")]
+                ("shape", "n_layers", "vocab", "max_seq", "quant", "kv_dtype", "draft_vocab", "device", "grid", "max_batch")]
 
 
 class LaunchArgs(ctypes.Structure):
@@ -64,7 +64,8 @@ class BatchArgs(ctypes.Structure):
                 ("epoch_base", ctypes.c_uint32), ("seed", ctypes.c_uint32), ("inv_temperature", ctypes.c_float),
                 ("n_stop", ctypes.c_int32), ("prof_step", ctypes.c_int32), ("stop_ids", ctypes.c_uint64),
                 ("tokens_out", ctypes.c_uint64), ("logits_out", ctypes.c_uint64), ("step_ts", ctypes.c_uint64),
-                ("out_info", ctypes.c_uint64), ("prof", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64)]
+                ("out_info", ctypes.c_uint64), ("prof", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64),
+                ("pf_bytes", ctypes.c_int64)]
 
 
 _lib = None

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, os.environ.get("MK_B200_LIBNAME", "libmk_b200.so"))
 SOURCES = ["mk_api.cu"]
-HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", os.path.join("..", "..", "include", "mk_b200.h")]
+HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", "mk_batch.cuh", os.path.join("..", "..", "include", "mk_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
               "-shared", "-Xcompiler", "-fPIC"]
 

@@ -14,16 +14,13 @@ using namespace mk;
 
 struct mk_engine {
     mk_model_desc desc;
-    int slot;
     int n_sm;
     bool params_set;
-    Params host;
-    bool static_ready;   // mk_launch_static has written its parameter block for the current params
+    Params host;         // the parameter block; every launch passes it to the kernel by value
 };
 
 static thread_local char g_err[512] = "";
 static std::mutex g_mu;
-static bool g_slot_used[MAX_ENGINES] = {};
 
 static int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -97,23 +94,17 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
     if (d->kv_dtype != MK_KV_BF16 && d->kv_dtype != MK_KV_F32) return fail(MK_ERR_UNSUPPORTED, "mk_create: kv_dtype %d", d->kv_dtype);
     if (d->vocab < 1 || d->max_seq < 1 || d->max_seq % KV_BLOCK) return fail(MK_ERR_BADARG, "mk_create: vocab %d / max_seq %d (must be a multiple of %d)", d->vocab, d->max_seq, KV_BLOCK);
     if (d->max_seq > MAX_BLOCKS * KV_BLOCK) return fail(MK_ERR_BADARG, "mk_create: max_seq %d exceeds %d", d->max_seq, MAX_BLOCKS * KV_BLOCK);
+    if (d->max_batch < 0 || d->max_batch > MK_MAX_BATCH) return fail(MK_ERR_BADARG, "mk_create: max_batch %d out of [0, %d]", d->max_batch, (int)MK_MAX_BATCH);
+    if ((int64_t)(d->max_batch > 1 ? d->max_batch : 1) * (d->max_seq / KV_BLOCK) > MAX_BLOCKS)
+        return fail(MK_ERR_BADARG, "mk_create: %d sequences of %d positions need more than %d KV pages", d->max_batch, d->max_seq, MAX_BLOCKS);
     int n_sm = 0;
     MK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, d->device));
     if (d->grid < 0 || d->grid > n_sm) return fail(MK_ERR_BADARG, "mk_create: grid %d exceeds the %d SMs (every CTA must be resident)", d->grid, n_sm);
-    int slot = -1;
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        for (int i = 0; i < MAX_ENGINES; i++)
-            if (!g_slot_used[i]) { g_slot_used[i] = true; slot = i; break; }
-    }
-    if (slot < 0) return fail(MK_ERR_BADARG, "mk_create: all %d engine slots are in use", MAX_ENGINES);
     mk_engine* e = new mk_engine();
     e->desc = *d;
     if (e->desc.grid == 0) e->desc.grid = n_sm;
-    e->slot = slot;
     e->n_sm = n_sm;
     e->params_set = false;
-    e->static_ready = false;
     memset(&e->host, 0, sizeof e->host);
     *out = e;
     return MK_OK;
@@ -121,10 +112,6 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
 
 extern "C" int mk_destroy(mk_engine* e) {
     if (!e) return MK_OK;
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        g_slot_used[e->slot] = false;
-    }
     delete e;
     return MK_OK;
 }
@@ -185,14 +172,12 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.actl) || bad16(p.lml) || bad16(p.partl))
         return fail(MK_ERR_BADARG, "activation word buffers null or not 16-byte aligned");
     if (!p.attn_part || !p.attn_flag || !p.block_table || !p.status) return fail(MK_ERR_BADARG, "attention scratch / block table / status missing");
-    MK_CUDA(cudaSetDevice(e->desc.device));
-    MK_CUDA(cudaMemcpyToSymbol(c_params, &p, sizeof(Params), (size_t)e->slot * sizeof(Params), cudaMemcpyHostToDevice));
     e->params_set = true;
-    e->static_ready = false;
     return MK_OK;
 }
 
-typedef void (*kernel_fn)(const int, const Args);
+typedef void (*kernel_fn)(const Params, const Args);
+static_assert(sizeof(Params) + sizeof(Args) + 64 <= 32764, "the parameter block travels as a kernel argument");
 static_assert(Geo<1>::SMEM <= SMEM_BYTES && Geo<2>::SMEM <= SMEM_BYTES, "MK_Q_SMEM_BYTES reports the largest kernel");
 
 // Dynamic shared memory of the kernel variant: what is not requested stays with the L1 cache.
@@ -227,6 +212,9 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
         if (a->start_pos < 0 || (int64_t)a->start_pos + a->n_steps > e->desc.max_seq)
             return fail(MK_ERR_BADARG, "mk_launch: sequence would exceed max_seq=%d", e->desc.max_seq);
         if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch: lm_from out of range");
+        // a step past the prompt reduces the previous step's LM-head keys: that step must have run the LM head
+        if (a->n_steps > a->n_forced && a->lm_from > a->n_forced - 1)
+            return fail(MK_ERR_BADARG, "mk_launch: lm_from %d > n_forced - 1 = %d while %d steps feed predicted tokens", a->lm_from, a->n_forced - 1, a->n_steps - a->n_forced);
         if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch: tokens_out / out_info missing");
     }
     if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch: stop ids missing");
@@ -274,8 +262,7 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     MK_CUDA(cudaSetDevice(e->desc.device));
     kernel_fn fn = pick_kernel(e->desc, spec);
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel_smem(spec)));
-    int slot = e->slot;
-    void* kargs[] = {&slot, &A};
+    void* kargs[] = {&e->host, &A};
     MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, kernel_smem(spec),
                                         static_cast<cudaStream_t>(stream)));
     return MK_OK;
@@ -299,6 +286,8 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     if (a->start_pos < 0 || (int64_t)a->start_pos + a->n_steps > e->desc.max_seq)
         return fail(MK_ERR_BADARG, "mk_launch_static: sequence would exceed max_seq=%d", e->desc.max_seq);
     if (a->lm_from < 0 || a->lm_from > a->n_steps) return fail(MK_ERR_BADARG, "mk_launch_static: lm_from out of range");
+    if (a->n_steps > a->n_forced && a->lm_from > a->n_forced - 1)
+        return fail(MK_ERR_BADARG, "mk_launch_static: lm_from %d > n_forced - 1 = %d while predicted tokens are fed", a->lm_from, a->n_forced - 1);
     if (!a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch_static: tokens_out / out_info missing");
     if (a->n_stop < 0 || (a->n_stop > 0 && !a->stop_ids)) return fail(MK_ERR_BADARG, "mk_launch_static: stop ids missing");
     const int grid = a->grid > 0 ? a->grid : e->desc.grid;
@@ -341,19 +330,15 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     }
     unsigned char* base = g_static_addr[dev];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int pslot = MAX_ENGINES + e->slot;
-    if (!e->static_ready) {
-        Params p = e->host;
-        p.xl = reinterpret_cast<unsigned long long*>(base + o_xl);
-        p.projl = reinterpret_cast<unsigned long long*>(base + o_proj);
-        p.mixl = reinterpret_cast<unsigned long long*>(base + o_mix);
-        p.actl = reinterpret_cast<unsigned long long*>(base + o_act);
-        p.lml = reinterpret_cast<unsigned long long*>(base + o_lml);
-        p.attn_part = reinterpret_cast<unsigned long long*>(base + o_part);
-        p.partl = reinterpret_cast<unsigned long long*>(base + o_partl);
-        MK_CUDA(cudaMemcpyToSymbol(c_params, &p, sizeof(Params), (size_t)pslot * sizeof(Params), cudaMemcpyHostToDevice));
-        e->static_ready = true;
-    }
+    // the engine's parameter block with the hand-off words redirected into the array
+    Params p = e->host;
+    p.xl = reinterpret_cast<unsigned long long*>(base + o_xl);
+    p.projl = reinterpret_cast<unsigned long long*>(base + o_proj);
+    p.mixl = reinterpret_cast<unsigned long long*>(base + o_mix);
+    p.actl = reinterpret_cast<unsigned long long*>(base + o_act);
+    p.lml = reinterpret_cast<unsigned long long*>(base + o_lml);
+    p.attn_part = reinterpret_cast<unsigned long long*>(base + o_part);
+    p.partl = reinterpret_cast<unsigned long long*>(base + o_partl);
     // the array keeps the previous call's words (and their epochs): everything must start at zero
     MK_CUDA(cudaMemsetAsync(base, 0, off, st));
 
@@ -380,15 +365,14 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     A.prof_step = a->prof_step;
     kernel_fn fn = pick_kernel(e->desc);
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kernel_smem(false)));
-    int slot = pslot;
-    void* kargs[] = {&slot, &A};
+    void* kargs[] = {&p, &A};
     MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, kernel_smem(false), st));
     return MK_OK;
 }
 
 // ---- batched decoding ---------------------------------------------------------------------------------
 static_assert(MK_MAX_BATCH == NB, "header and kernel agree on the batch width");
-typedef void (*batch_kernel_fn)(const int, const BatchArgs);
+typedef void (*batch_kernel_fn)(const Params, const BatchArgs);
 
 extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* stream) {
     typedef Qwen35_08B S;
@@ -396,6 +380,9 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch_batch: mk_set_params has not succeeded on this engine");
     if (e->desc.quant != MK_QUANT_INT8) return fail(MK_ERR_UNSUPPORTED, "mk_launch_batch: batched decoding is built for int8 weights only");
     if (a->batch < 1 || a->batch > NB) return fail(MK_ERR_BADARG, "mk_launch_batch: batch %d out of [1, %d]", a->batch, NB);
+    if (a->batch > (e->desc.max_batch > 1 ? e->desc.max_batch : 1))
+        return fail(MK_ERR_BADARG, "mk_launch_batch: batch %d, but the engine's buffers were sized for %d sequence(s) (mk_model_desc.max_batch)",
+                    a->batch, e->desc.max_batch > 1 ? e->desc.max_batch : 1);
     if (a->n_steps < 1 || !a->forced || !a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch_batch: need n_steps >= 1, a token list, tokens_out and out_info");
     if ((int64_t)a->batch * (e->desc.max_seq / KV_BLOCK) > MAX_BLOCKS)
         return fail(MK_ERR_BADARG, "mk_launch_batch: %d sequences of %d positions need more than %d KV pages", a->batch, e->desc.max_seq, MAX_BLOCKS);
@@ -434,6 +421,7 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     A.out_info = as_ptr<int*>(a->out_info);
     A.prof = as_ptr<unsigned long long*>(a->prof);
     A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
+    A.pf_bytes = a->pf_bytes;
     for (int j = 0; j < NB; j++) {
         A.n_forced[j] = j < a->batch ? a->n_forced[j] : 0;
         A.n_total[j] = j < a->batch ? a->n_total[j] : 0;
@@ -451,8 +439,7 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     MK_CUDA(cudaSetDevice(e->desc.device));
     batch_kernel_fn fn = e->desc.kv_dtype == MK_KV_F32 ? batch_kernel<S, true> : batch_kernel<S, false>;
     MK_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, GeoB::SMEM));
-    int slot = e->slot;
-    void* kargs[] = {&slot, &A};
+    void* kargs[] = {&e->host, &A};
     MK_CUDA(cudaLaunchCooperativeKernel((const void*)fn, dim3(grid), dim3(NTHREADS), kargs, GeoB::SMEM,
                                         static_cast<cudaStream_t>(stream)));
     return MK_OK;

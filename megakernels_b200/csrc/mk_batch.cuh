@@ -48,6 +48,7 @@ struct BatchArgs {
     int* out_info;
     unsigned long long* prof;
     long long spin_limit_ns;
+    long long pf_bytes;                     // L2 prefetch distance ahead of the ring, per CTA (0: off)
     int n_forced[NB];
     int n_total[NB];                        // steps sequence j takes part in; it is frozen afterwards
     int pos0[NB];
@@ -400,8 +401,8 @@ __device__ bool gdn_batch(Ctx& c, const Params& P, const LayerP& L, const BatchA
 // The weight stream of the batched kernel: the four GEMVs of every layer, then the LM head from
 // step `lm_from` on.
 template <class S>
-__device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A) {
-    Producer<GeoB::NS> pr(c);
+__device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A, bool prefetch) {
+    Producer<GeoB::NS> pr(c, prefetch, A.pf_bytes);
     for (int s = 0; s < A.n_steps && !pr.stop; s++) {
         for (int l = 0; l < P.n_layers && !pr.stop; l++) {
             const LayerP& L = P.layer[l];
@@ -567,10 +568,9 @@ __device__ __forceinline__ bool run_layer_b(Ctx& c, const Params& P, const Layer
 
 // ---- the kernel ------------------------------------------------------------------------------------------
 template <class S, bool KVF32>
-__global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const int pslot, const __grid_constant__ BatchArgs A) {
+__global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const __grid_constant__ Params P, const __grid_constant__ BatchArgs A) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     constexpr int NS = GeoB::NS;
-    const Params& P = c_params[pslot];
     Ctx c;
     {
         uint8_t* p = smem_raw;
@@ -590,6 +590,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const int pslot, con
         c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
+        c.sm.pf_pos = reinterpret_cast<volatile u64*>(p); p += 8;
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
@@ -604,6 +605,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const int pslot, con
         }
         *c.sm.abort_flag = 0;
         *c.sm.quit_flag = 0;
+        *c.sm.pf_pos = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -611,7 +613,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const int pslot, con
     __syncthreads();
 
     if (c.warp == NCW) {
-        if (c.lane == 0) producer_batch<S>(c, P, A);
+        if (c.lane == 0) producer_batch<S>(c, P, A, false);
+        else if (c.lane == 1 && A.pf_bytes > 0) producer_batch<S>(c, P, A, true);
         return;
     }
 

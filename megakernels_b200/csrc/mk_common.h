@@ -11,7 +11,6 @@ constexpr int NTHREADS = NCT + 32;        // + one producer warp
 constexpr int SLOT_BYTES = 32768;         // one ring slot: 32/16/9 int8 rows or 16/8/4 bf16 rows of K = 1024/2048/3584
 constexpr int NSTAGE = 6;                 // ring depth of the bandwidth probe: 192 KB in flight per SM (the decode kernels choose their own)
 constexpr int MAX_LAYERS = 64;
-constexpr int MAX_ENGINES = 2;            // constant-memory parameter slots
 constexpr int KV_BLOCK = 64;              // positions per KV page
 constexpr int CONV_RING = 8;              // conv history slots, indexed by position & 7
 constexpr int MAX_SPLITS = 128;           // attention split-K chunks per KV head (buffer sizing)
@@ -50,7 +49,7 @@ struct Qwen35_08B {
 constexpr int MAX_BLOCKS = 512;                                    // KV pages per sequence (max_seq <= 32768)
 constexpr int SMEM_BYTES = NSTAGE * SLOT_BYTES + 3 * 2 * 3584 + NCW * 64 * 4 + MAX_BLOCKS * 4 + 2048 + 2048;   // upper bound of the single-sequence kernels' dynamic shared memory
 
-// ---- device-side parameter block (one per engine, in constant memory) --------------------------
+// ---- device-side parameter block (one per engine, passed to every launch as a kernel argument) ---
 struct LayerP {
     const uint8_t* w_in;
     const uint8_t* w_out;

@@ -257,7 +257,7 @@ class Megakernel:
 
         desc = _lib.ModelDesc(shape=_lib.MK_SHAPE_QWEN35_08B, n_layers=cfg.n_layers, vocab=cfg.vocab,
                               max_seq=self.max_seq, quant=_lib.MK_QUANT[quant], kv_dtype=_lib.MK_KV[kv_dtype],
-                              draft_vocab=self.draft_vocab, device=device.index, grid=self.grid)
+                              draft_vocab=self.draft_vocab, device=device.index, grid=self.grid, max_batch=batch)
         self._h = ctypes.c_void_p()
         _lib.check(self.lib.mk_create(ctypes.byref(desc), ctypes.byref(self._h)))
         lv, gv = _lib.i64_array(layer_vals), _lib.i64_array([g[f] for f in _lib.GLOBAL_FIELDS])
@@ -442,7 +442,7 @@ class Megakernel:
                            inv_temperature=1.0 / temperature if temperature > 0 else 0.0, n_stop=len(stop_ids),
                            prof_step=prof_step, stop_ids=stops.data_ptr(), tokens_out=out.data_ptr(),
                            logits_out=ptr(logits), step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof),
-                           spin_limit_ns=self.spin_limit_ns)
+                           spin_limit_ns=self.spin_limit_ns, pf_bytes=self.pf_bytes)
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(self.lib.mk_launch_batch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
         self.launches += 1

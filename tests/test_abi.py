@@ -47,7 +47,7 @@ def test_field_order_matches_header(lib_built):
 
 
 def test_struct_layouts(lib_built):
-    assert ctypes.sizeof(_lib.ModelDesc) == 36
+    assert ctypes.sizeof(_lib.ModelDesc) == 40
     a = _lib.LaunchArgs
     assert a.stop_ids.offset == 40 and a.prof_step.offset == 96 and a.pf_bytes.offset == 104
     assert a.spec.offset == 120 and a.spec_out.offset == 136 and ctypes.sizeof(a) == 152
@@ -58,7 +58,7 @@ def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
     import shutil
     import subprocess
     b = _lib.BatchArgs
-    assert ctypes.sizeof(b) == 192 and b.n_total.offset == 40 and b.batch.offset == 104 and b.stop_ids.offset == 136
+    assert ctypes.sizeof(b) == 200 and b.pf_bytes.offset == 192 and b.n_total.offset == 40 and b.batch.offset == 104 and b.stop_ids.offset == 136
     assert _lib.query("MAX_BATCH") == _lib.MAX_BATCH == 8
     assert _lib.query("BATCH_SMEM_BYTES") <= 227 * 1024
     if not shutil.which("gcc"):
@@ -71,7 +71,7 @@ def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
-    assert got == [192, 40, 104, 136, ctypes.sizeof(_lib.LaunchArgs), ctypes.sizeof(_lib.ModelDesc)]
+    assert got == [200, 40, 104, 136, ctypes.sizeof(_lib.LaunchArgs), ctypes.sizeof(_lib.ModelDesc)]
 
 
 def test_constants(lib_built):
@@ -91,6 +91,14 @@ def test_bad_arguments_are_refused_without_a_gpu(lib_built):
     assert lib.mk_create(ctypes.byref(desc), ctypes.byref(h)) == _lib.MK_ERR_UNSUPPORTED
     with pytest.raises(_lib.MkError):
         _lib.check(lib.mk_plan_rows(10, 3, 0, 4, None, None))
+    # per-sequence buffers: a batch capacity outside [0, 8], or more KV pages than one launch maps, is refused at creation
+    for kw in (dict(max_batch=9), dict(max_batch=-1), dict(max_batch=8, max_seq=8192)):
+        d = dict(shape=_lib.MK_SHAPE_QWEN35_08B, n_layers=4, vocab=4096, max_seq=64, quant=1, kv_dtype=1, draft_vocab=0,
+                 device=0, grid=0, max_batch=0)
+        d.update(kw)
+        desc = _lib.ModelDesc(**d)
+        assert lib.mk_create(ctypes.byref(desc), ctypes.byref(h)) == _lib.MK_ERR_BADARG, kw
+        assert b"max_batch" in lib.mk_last_error() or b"KV pages" in lib.mk_last_error()
     assert lib.mk_launch(None, None, None) == _lib.MK_ERR_BADARG
     assert lib.mk_launch_batch(None, None, None) == _lib.MK_ERR_BADARG
     assert lib.mk_destroy(None) == _lib.MK_OK

@@ -175,6 +175,18 @@ def test_errors(tiny, lib_built):
     with pytest.raises(_lib.MkError, match="layer pointer count"):
         _lib.check(mk.lib.mk_set_params(mk._h, _lib.i64_array([0] * 5), 5, None, 0, _lib.i64_array([0]), 1))
     assert mk.run([1, 2, 3]) is not None                    # the engine is still usable afterwards
+    # a launch whose fed-back steps would wait for LM-head keys that no step publishes is refused, not run into its timeout
+    import ctypes
+    a = _lib.LaunchArgs(forced=mk.status.data_ptr(), n_forced=2, n_steps=4, lm_from=3, start_pos=0, epoch_base=mk.epoch,
+                        tokens_out=mk.status.data_ptr(), out_info=mk.status.data_ptr(), grid=mk.grid)
+    assert mk.lib.mk_launch(mk._h, ctypes.byref(a), None) == _lib.MK_ERR_BADARG
+    assert b"lm_from" in mk.lib.mk_last_error()
+    # so is a batched launch of more sequences than the engine's per-sequence buffers were sized for
+    del mk                                                  # the library has two engine slots
+    one = engine(cfg, w, quant="int8", max_seq=64)
+    b = _lib.BatchArgs(batch=2, n_steps=1)
+    assert one.lib.mk_launch_batch(one._h, ctypes.byref(b), None) == _lib.MK_ERR_BADARG
+    assert b"sized for 1" in one.lib.mk_last_error()
     with pytest.raises(ValueError):
         engine(qwen35_08b(n_layers=2).with_(hidden=2048), w)
 
