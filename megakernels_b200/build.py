@@ -14,10 +14,11 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, os.environ.get("MK_B200_LIBNAME", "libmk_b200.so"))
-SOURCES = ["mk_api.cu"]
-HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", "mk_batch.cuh", os.path.join("..", "..", "include", "mk_b200.h")]
+SOURCES = ["mk_api.cu", "mk_stage_api.cu"]
+HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", "mk_batch.cuh", "mk_stage.cuh", "mk_stage_ops.cuh",
+           os.path.join("..", "..", "include", "mk_b200.h"), os.path.join("..", "..", "include", "mk_stage.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
-              "-shared", "-Xcompiler", "-fPIC"]
+              "-Xcompiler", "-fPIC"]
 
 
 def stale():
@@ -34,17 +35,32 @@ def build(force=False, verbose=False):
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
     csrc = os.path.join(HERE, "csrc")
-    cmd = [nvcc, *NVCC_FLAGS, *shlex.split(os.environ.get("MK_B200_DEFINES", "")), "-o", LIB,
-           *[os.path.join(csrc, s) for s in SOURCES]]
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    defines = shlex.split(os.environ.get("MK_B200_DEFINES", ""))
+    # one object per translation unit, compiled side by side, then one link
+    jobs = []
+    for src in SOURCES:
+        obj = os.path.join(objdir, os.path.basename(LIB) + "." + src[:-3] + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, *defines, "-c", "-o", obj, os.path.join(csrc, src)]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+            print(" ".join(cmd))
+        jobs.append((obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    log = ""
+    failed = False
+    for obj, proc in jobs:
+        text, _ = proc.communicate()
+        log += text
+        failed |= proc.returncode != 0
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-        print(" ".join(cmd))
-    out = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose:
-        print(out.stdout, out.stderr)
-    if out.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + out.stdout + out.stderr)
+        print(log)
+    if failed:
+        raise RuntimeError("nvcc failed:\n" + log)
+    link = subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *[o for o, _ in jobs]],
+                          capture_output=True, text=True)
+    if link.returncode != 0:
+        raise RuntimeError("link failed:\n" + link.stdout + link.stderr)
     return LIB
 
 

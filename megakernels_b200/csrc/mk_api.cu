@@ -29,6 +29,11 @@ static int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+// text behind mk_last_error() for the library's other translation units
+int mk_set_error(int code, const char* text) {
+    snprintf(g_err, sizeof g_err, "%s", text);
+    return code;
+}
 #define MK_CUDA(call)                                                                      \
     do {                                                                                   \
         cudaError_t err__ = (call);                                                        \
