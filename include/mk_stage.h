@@ -219,7 +219,7 @@ typedef struct mk_stage_args {
     uint64_t barrier_base;   /* value of the counter when the launch starts; the host carries it   */
     uint64_t status;         /* int32[4]: first wait that ran out: code, site, CTA, thread         */
     int64_t spin_limit_ns;   /* bound on every device-side wait; 0 = 2 s                           */
-    uint64_t prof;           /* optional u64[n_stages][8]: GPU ns of CTA 0 in the last step, per stage:
+    uint64_t prof;           /* optional u64[n_stages][8]: GPU ns of CTA `prof_cta` in the last step, per stage:
                                 entered, input staged, work done, barrier passed                  */
     /* tensor parallelism: every rank runs the same program on its shard; row-parallel GEMVs with
      * ALLREDUCE push their partial tiles into every rank's mailbox with plain peer stores and poll
@@ -229,8 +229,11 @@ typedef struct mk_stage_args {
     uint64_t mailbox[MKS_MAX_RANKS];   /* every rank's mailbox as this device addresses it         */
     uint64_t ar_base;        /* all-reduce sequence number before this launch (the host carries it)*/
     int32_t grid;            /* CTAs, 0 = one per SM                                               */
-    int32_t reserved;
+    int32_t prof_cta;        /* the CTA whose timestamps go to `prof`; -1: every CTA, prof is u64[grid][n_stages][8] */
     int64_t pf_bytes;        /* L2 prefetch distance ahead of the shared-memory ring, per CTA (0: off) */
+    int32_t xs_bytes;        /* shared staging area the program needs (mk_stage_scratch_bytes; 0: the maximum);
+                                what it leaves of the SM's shared memory becomes ring slots (2..4 per warp) */
+    int32_t reserved2;
 } mk_stage_args;
 
 /* Launch.  Asynchronous on `stream`. */
@@ -239,6 +242,9 @@ int mk_stage_launch(const mk_stage_args* args, void* stream);
 /* Checks a host copy of a program against the kernel's structural limits (ring slot, input staging
  * area, MMA columns, mailbox size) before it is uploaded; MK_ERR_BADARG names the stage. */
 int mk_stage_validate(const mk_stage_desc* program, int n_stages, int batch);
+
+/* Bytes of shared staging area `program` needs at `batch` sequences (for mk_stage_args.xs_bytes). */
+int64_t mk_stage_scratch_bytes(const mk_stage_desc* program, int n_stages, int batch);
 
 /* Barriers and all-reduces one step of `program` (host copy) performs: what the caller adds to
  * barrier_base / ar_base per step. */

@@ -34,17 +34,17 @@
 namespace mks {
 using namespace mk;
 
-constexpr int SLOT_BYTES = 4608;                  // one ring slot: 8 tile steps of 512 bytes + scales
+constexpr int SLOT_BYTES = 4352;                  // one ring slot: 8 tile steps of 512 bytes + 256 bytes of scales
 constexpr int XS_BYTES = 50176;                   // staged GEMV input: 8 columns x 3072 fp16 + padding; also mixer scratch
 constexpr int MAX_GROUPS = 72;                    // routed experts of one step (8 x 8) + shared / dense groups
 constexpr int MISC_BYTES = 8192;
 constexpr int SMEM_TOTAL = 232448;                // 227 KB
-constexpr int RING_DEPTH = 2;                     // ring slots per consumer warp
-constexpr int NS = 16 * RING_DEPTH;               // ring slots: every consumer warp has its own
+constexpr int MAX_RING_DEPTH = 4;                 // ring slots per consumer warp: 2..4, as many as the launch's input staging area leaves room for
+constexpr int NS = 16 * MAX_RING_DEPTH;           // ring slots (upper bound): every consumer warp has its own
 constexpr int ATTN_MAX_CHUNK = 256;               // positions per attention task (score buffer)
 constexpr int MAILBOX_TILES = 1024;               // output tiles of a row-parallel GEMV one all-reduce can carry
 constexpr int MAILBOX_BYTES = 2 * MAILBOX_TILES * MKS_MAX_RANKS * 128 * 8 + 2 * MKS_MAX_RANKS * MKS_MAX_BATCH * 16;
-static_assert((size_t)NS * SLOT_BYTES + XS_BYTES + MISC_BYTES <= SMEM_TOTAL, "shared memory of one SM");
+static_assert((size_t)16 * 2 * SLOT_BYTES + XS_BYTES + MISC_BYTES <= SMEM_TOTAL, "shared memory of one SM");
 
 // wait sites (status[1])
 enum { WS_FULL = 101, WS_EMPTY, WS_BARRIER, WS_ROUTE, WS_DRAIN, WS_MAILBOX, WS_KEYS };
@@ -64,6 +64,9 @@ struct Args {
     unsigned long long* mailbox[MKS_MAX_RANKS];
     unsigned long long ar_base;
     long long pf_bytes;      // L2 prefetch distance ahead of the ring, per CTA (0: off)
+    int prof_cta;            // the CTA whose timestamps go to `prof`
+    int xs_bytes;            // input staging / mixer scratch area of this launch
+    int ring_depth;          // ring slots per consumer warp
 };
 
 // Everything the threads of a CTA share lives in shared memory, behind the ring and the input staging
@@ -78,7 +81,7 @@ struct Shared {
     unsigned long long* prof;      // this stage's timestamp row (CTA 0, last step) or null
     mk_stage_desc desc[2];         // this stage's record and the next one's
     Args A;                        // the launch arguments
-    float red[17 * 8];             // block-reduction scratch
+    float red[16 + 17 * 8];        // block-reduction scratch
     float xinv[8];                 // factor that undoes the power-of-two scaling of a staged column
     float rstd[8];                 // 1/rms of the staged input
     int tok_s[8];
@@ -92,8 +95,9 @@ struct Shared {
     volatile int abort_flag;
     volatile unsigned route_seq;
     int flag;
-    __device__ __forceinline__ uint8_t* xs() { return reinterpret_cast<uint8_t*>(this) - XS_BYTES; }
-    __device__ __forceinline__ uint8_t* ring() { return reinterpret_cast<uint8_t*>(this) - XS_BYTES - (size_t)NS * SLOT_BYTES; }
+    // dynamic shared memory: [this block | staging area of A.xs_bytes | 16 x A.ring_depth ring slots]
+    __device__ __forceinline__ uint8_t* xs() { return reinterpret_cast<uint8_t*>(this) + MISC_BYTES; }
+    __device__ __forceinline__ uint8_t* ring() { return reinterpret_cast<uint8_t*>(this) + MISC_BYTES + A.xs_bytes; }
 };
 static_assert(sizeof(Shared) <= MISC_BYTES, "the shared block fits its area");
 
@@ -143,7 +147,7 @@ __device__ __noinline__ u64 spin_slow2(volatile int* abort_flag, int* status, u6
 
 // Wait of a whole warp for one barrier phase.  The warp leaves together: a lane that returned alone
 // would never reach the `__syncwarp` the others go on to.
-__device__ __forceinline__ bool mbar_wait2(Shared& S, Mut& mu, uint64_t* b, uint32_t parity, int where) {
+__device__ __forceinline__ bool mbar_wait2(Shared& S, uint64_t* b, uint32_t parity, int where) {
     Spin2 s;
     bool fail = false;
 #pragma unroll 1
@@ -151,10 +155,7 @@ __device__ __forceinline__ bool mbar_wait2(Shared& S, Mut& mu, uint64_t* b, uint
         const bool ok = mbar_try_wait(b, parity);
         if (__all_sync(0xffffffffu, ok)) return true;
         if (!ok && MKS_SPIN_FAIL(S, s, where)) fail = true;
-        if (__any_sync(0xffffffffu, fail)) {
-            mu.dead = true;
-            return false;
-        }
+        if (__any_sync(0xffffffffu, fail)) return false;       // the abort flag is set: the stage loop stops at its next check
     }
 }
 
@@ -214,13 +215,15 @@ __device__ __forceinline__ uint32_t cvt_s8x2(uint32_t bx, uint32_t sel) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// (not `volatile`: the instruction has no effect beyond its outputs, and the compiler must be free to interleave
+// independent accumulator chains -- a warp issues in order, and a dependent MMA behind its producer stalls it)
 __device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
@@ -244,9 +247,21 @@ __device__ __forceinline__ Gemv gemv_geometry(const Shared& S, const mk_stage_de
     g.chunk_steps = d.i[MKS_I_CHUNK_STEPS];
     g.chunk_bytes = d.i[MKS_I_CHUNK_BYTES];
     g.n_chunks = g.unit_steps / g.chunk_steps;
-    const unsigned U = (unsigned)(g.G * g.S * g.T);            // < 2^24: U * grid fits 32 bits
-    g.u0 = (int)(U * (unsigned)cta_() / (unsigned)grid_());
-    g.u1 = (int)(U * (unsigned)(cta_() + 1) / (unsigned)grid_());
+    const unsigned P = (unsigned)(g.G * g.S), grid = (unsigned)grid_(), cta = (unsigned)cta_();
+    if (P <= grid) {
+        // every CTA stays inside one panel (one staged input): panel p gets the CTAs [ceil(p grid / P), ceil((p + 1) grid / P))
+        // and they share its T tiles evenly.  A CTA that straddled two panels would stage its input twice and
+        // keep the whole grid waiting at the stage's barrier.
+        const unsigned p = cta * P / grid;
+        const unsigned c0 = (p * grid + P - 1) / P, c1 = ((p + 1) * grid + P - 1) / P;
+        const unsigned n = c1 - c0, k = cta - c0;
+        g.u0 = (int)(p * (unsigned)g.T + (unsigned)g.T * k / n);
+        g.u1 = (int)(p * (unsigned)g.T + (unsigned)g.T * (k + 1) / n);
+    } else {
+        const unsigned U = P * (unsigned)g.T;                      // < 2^24: U * grid fits 32 bits
+        g.u0 = (int)(U * cta / grid);
+        g.u1 = (int)(U * (cta + 1) / grid);
+    }
     return g;
 }
 // Weight bytes of group `grp`: experts of a routed stage come from the routing list, the shared expert last.
@@ -270,7 +285,7 @@ __device__ __forceinline__ const float* group_row_scale(const Shared& S, const m
 // lane needs about a quarter of a microsecond of dependent instructions per copy, which caps one SM at a few
 // chunks per microsecond -- a sixth of its share of the HBM stream.
 //
-// Every consumer warp has its own RING_DEPTH slots.  A slot is therefore filled and drained by the same pair
+// Every consumer warp has its own ring_depth slots.  A slot is therefore filled and drained by the same pair
 // (lane j, warp j) in strict alternation, and a waiter is never more than one phase ahead of its barrier:
 // with slots shared between warps a fast warp could ask for the next-but-one phase of a slot that still
 // served another warp, and a parity wait cannot tell that phase from the one before it.
@@ -304,8 +319,9 @@ struct Cursor {
 __device__ __noinline__ void producer_main(Shared& S, const Args& A) {
     const int lane = lane_();
     const u64 policy = policy_evict_first();
+    const uint32_t depth = (uint32_t)A.ring_depth;
     uint32_t q = 0;              // chunks this lane has issued: chunk q of consumer warp `lane` lives in slot
-                                 // lane * RING_DEPTH + q % RING_DEPTH, phase q / RING_DEPTH
+                                 // lane * depth + q % depth, phase q / depth
     Cursor c;
     c.step = 0; c.si = -1; c.u0 = c.u1 = c.pu = c.pend = c.r0 = 0; c.ch = 0; c.routes = 0;
     c.have = false; c.done = lane >= NCW;
@@ -367,8 +383,8 @@ __device__ __noinline__ void producer_main(Shared& S, const Args& A) {
             }
         }
         if (c.have) {
-            const int slot = lane * RING_DEPTH + (int)(q % RING_DEPTH);
-            const bool is_free = q < (uint32_t)RING_DEPTH || mbar_try_wait(&S.empty[slot], ((q / RING_DEPTH) - 1) & 1);
+            const int slot = lane * (int)depth + (int)(q % depth);
+            const bool is_free = q < depth || mbar_try_wait(&S.empty[slot], ((q / depth) - 1) & 1);
             if (is_free) {
                 // self-check: the copy must stay inside the matrix the record describes
                 const size_t off = (size_t)(c.src - c.wg) + (size_t)c.ch * c.chunk_bytes;
@@ -402,12 +418,12 @@ __device__ __noinline__ void producer_main(Shared& S, const Args& A) {
     }
     // before the CTA may exit every copy that was issued must have landed (not abortable: the copies write shared memory)
     if (lane < NCW) {
-        const uint32_t first = q > (uint32_t)RING_DEPTH ? q - RING_DEPTH : 0;
+        const uint32_t first = q > depth ? q - depth : 0;
 #pragma unroll 1
         for (uint32_t i = first; i < q; i++) {
             uint32_t it = 0;
             u64 t0 = 0;
-            while (!mbar_try_wait(&S.full[lane * RING_DEPTH + (int)(i % RING_DEPTH)], (i / RING_DEPTH) & 1)) {
+            while (!mbar_try_wait(&S.full[lane * (int)depth + (int)(i % depth)], (i / depth) & 1)) {
                 if (((++it) & 1023u) == 0) {
                     const u64 now = globaltimer();
                     if (!t0) t0 = now;
@@ -463,14 +479,30 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     request(0);
     if (norm) {
         // 1/rms of every sequence from the 16-element sums of squares of the whole input vector
-        const int K = d.i[MKS_I_K_TOTAL];
+        // (every thread asks for its share of every sequence's sums at once: one L2 round trip, fixed summation order)
+        const int K = d.i[MKS_I_K_TOTAL], n16 = K / 16;
         const float* ssq = reinterpret_cast<const float*>(d.p[MKS_P_X_SSQ]);
-        if (warp_() < M) {
+        float part[MKS_MAX_BATCH];
+#pragma unroll
+        for (int m = 0; m < MKS_MAX_BATCH; m++) {
+            part[m] = 0.f;
+            if (m < M) {
+#pragma unroll 2
+                for (int j = tid_(); j < n16; j += NCT) part[m] += ldcg_f(ssq + (size_t)m * n16 + j);
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MKS_MAX_BATCH; m++)
+            if (m < M) {
+                const float v = warp_sum(part[m]);
+                if (lane_() == 0) S.red[16 + warp_() * MKS_MAX_BATCH + m] = v;
+            }
+        consumer_sync();
+        if (tid_() < M) {
             float s = 0.f;
-#pragma unroll 1
-            for (int j = lane_(); j < K / 16; j += 32) s += ldcg_f(ssq + (size_t)warp_() * (K / 16) + j);
-            s = warp_sum(s);
-            if (lane_() == 0) S.rstd[warp_()] = rsqrtf(s / (float)K + d.f[MKS_F_EPS]);
+#pragma unroll
+            for (int w = 0; w < NCW; w++) s += S.red[16 + w * MKS_MAX_BATCH + tid_()];
+            S.rstd[tid_()] = rsqrtf(s / (float)K + d.f[MKS_F_EPS]);
         }
     }
     consumer_sync();
@@ -621,19 +653,25 @@ struct Best2 {
     u64 k0 = 0, k1 = 0;
 };
 
+// The hot loop is a function of its own with a handful of scalar arguments: inlined into the stage function it
+// shared that function's register budget (96 with 17 warps resident) and spilled inside the loop, and spilled
+// registers of 544 threads do not fit the L1 that the shared-memory carve-out leaves.
+struct UnitGeo {
+    int n_chunks, chunk_steps;
+};
 template <int FMT>
-__device__ __forceinline__ void unit_steps(Shared& S, Mut& mu, const mk_stage_desc& d, const Gemv& gm, uint32_t chunk0,
-                                           const uint8_t* xcol, bool col_live, float (&acc)[4]) {
+__device__ __noinline__ float4 unit_steps(Shared& S, UnitGeo gm, uint32_t chunk0, const uint8_t* xcol, bool col_live, bool blocks) {
     constexpr int MMAS = FMT == MKS_FMT_MXFP4 ? 4 : (FMT == MKS_FMT_BF16 ? 1 : 2);
     const int g = lane_() >> 2, t = lane_() & 3;
-    const bool blocks = FMT == MKS_FMT_FP8 && d.i[MKS_I_BLOCK_SCALES] != 0;
-    float tmp[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};    // two chains: consecutive MMAs never wait for each other
+    float tmp[4] = {0.f, 0.f, 0.f, 0.f}, tmp2[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t depth = (uint32_t)S.A.ring_depth;
     int kstep = 0;                                            // tile step inside the unit
 #pragma unroll 1
     for (int ch = 0; ch < gm.n_chunks; ch++) {
         const uint32_t qq = chunk0 + (uint32_t)ch;               // this warp's chunk counter
-        const int slot = warp_() * RING_DEPTH + (int)(qq % RING_DEPTH);
-        if (!mbar_wait2(S, mu, &S.full[slot], (qq / RING_DEPTH) & 1, WS_FULL)) return;
+        const int slot = warp_() * (int)depth + (int)(qq % depth);
+        if (!mbar_wait2(S, &S.full[slot], (qq / depth) & 1, WS_FULL)) break;
         const uint8_t* sl = S.ring() + (size_t)slot * SLOT_BYTES;
         const uint8_t* sc_base = sl + gm.chunk_steps * 512;
 #pragma unroll 4
@@ -641,29 +679,55 @@ __device__ __forceinline__ void unit_steps(Shared& S, Mut& mu, const mk_stage_de
             const uint4 wq = *reinterpret_cast<const uint4*>(sl + st * 512 + lane_() * 16);
             const uint8_t* xk = xcol + (size_t)kstep * (MMAS * 16) * 2 + t * 8;
             if (FMT == MKS_FMT_MXFP4) {
+                // The conversion unit (cvt ... e2m1x2) is the scarcest pipe of this loop, so only half of the
+                // values go through it.  The 32 columns of scale group 0 (MMAs 0 and 1) arrive with their bits
+                // pre-arranged by the packer: every 32-bit word yields four f16x2 registers with shifts and masks
+                // alone (sign at bit 15, the three magnitude bits at 11..9 of each half: the value times 2^-14,
+                // which the group's scale takes back).  Scale group 1 (MMAs 2 and 3) keeps plain nibbles.
                 const uint32_t scw = *reinterpret_cast<const uint32_t*>(sc_base + st * 32 + g * 4);
-                float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+                float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};      // scale group 0: MMAs 0, 1
+                float u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};      // scale group 1: MMAs 2, 3
+                uint2 b[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const uint32_t lo = j < 2 ? wq.x : wq.y, hi = j < 2 ? wq.z : wq.w;     // row g, row g + 8
-                    const int sh = (j & 1) * 16;
-                    uint32_t a[4];
-                    a[0] = cvt_e2m1x2(lo >> sh);
-                    a[2] = cvt_e2m1x2(lo >> (sh + 8));
-                    a[1] = cvt_e2m1x2(hi >> sh);
-                    a[3] = cvt_e2m1x2(hi >> (sh + 8));
-                    uint2 b = make_uint2(0u, 0u);
-                    if (col_live) b = *reinterpret_cast<const uint2*>(xk + j * 32);
-                    if (j < 2) mma_f16(t0, a, b.x, b.y);
-                    else mma_f16(t1, a, b.x, b.y);
+                    b[j] = make_uint2(0u, 0u);
+                    if (col_live) b[j] = *reinterpret_cast<const uint2*>(xk + j * 32);
                 }
-                // e8m0 scales: bytes [row g: group 0, group 1, row g + 8: group 0, group 1]
-                const float s00 = __uint_as_float((scw & 0xFFu) << 23), s01 = __uint_as_float(((scw >> 8) & 0xFFu) << 23);
-                const float s10 = __uint_as_float(((scw >> 16) & 0xFFu) << 23), s11 = __uint_as_float((scw >> 24) << 23);
-                acc[0] = fmaf(t0[0], s00, acc[0]); acc[1] = fmaf(t0[1], s00, acc[1]);
-                acc[2] = fmaf(t0[2], s10, acc[2]); acc[3] = fmaf(t0[3], s10, acc[3]);
-                acc[0] = fmaf(t1[0], s01, acc[0]); acc[1] = fmaf(t1[1], s01, acc[1]);
-                acc[2] = fmaf(t1[2], s11, acc[2]); acc[3] = fmaf(t1[3], s11, acc[3]);
+                {
+                    const uint32_t lo = wq.x, hi = wq.z;                  // row g, row g + 8
+                    uint32_t a[4];
+                    a[0] = lo & 0x8E008E00u;
+                    a[1] = hi & 0x8E008E00u;
+                    a[2] = (lo << 3) & 0x8E008E00u;
+                    a[3] = (hi << 3) & 0x8E008E00u;
+                    mma_f16(t0, a, b[0].x, b[0].y);
+                    a[0] = ((lo << 1) & 0x80008000u) | ((lo << 6) & 0x0E000E00u);
+                    a[1] = ((hi << 1) & 0x80008000u) | ((hi << 6) & 0x0E000E00u);
+                    a[2] = ((lo << 2) & 0x80008000u) | ((lo << 9) & 0x0E000E00u);
+                    a[3] = ((hi << 2) & 0x80008000u) | ((hi << 9) & 0x0E000E00u);
+                    mma_f16(t1, a, b[1].x, b[1].y);
+                }
+                {
+                    const uint32_t lo = wq.y, hi = wq.w;
+                    uint32_t a[4];
+                    a[0] = cvt_e2m1x2(lo);
+                    a[2] = cvt_e2m1x2(lo >> 8);
+                    a[1] = cvt_e2m1x2(hi);
+                    a[3] = cvt_e2m1x2(hi >> 8);
+                    mma_f16(u0, a, b[2].x, b[2].y);
+                    a[0] = cvt_e2m1x2(lo >> 16);
+                    a[2] = cvt_e2m1x2(lo >> 24);
+                    a[1] = cvt_e2m1x2(hi >> 16);
+                    a[3] = cvt_e2m1x2(hi >> 24);
+                    mma_f16(u1, a, b[3].x, b[3].y);
+                }
+                // e8m0 scales: bytes [row g: group 0, group 1, row g + 8: group 0, group 1]; group 0 also takes 2^14
+                const float s00 = __uint_as_float(((scw & 0xFFu) + 14u) << 23), s01 = __uint_as_float(((scw >> 8) & 0xFFu) << 23);
+                const float s10 = __uint_as_float((((scw >> 16) & 0xFFu) + 14u) << 23), s11 = __uint_as_float((scw >> 24) << 23);
+                acc[0] = fmaf(t0[0] + t1[0], s00, acc[0]); acc[1] = fmaf(t0[1] + t1[1], s00, acc[1]);
+                acc[2] = fmaf(t0[2] + t1[2], s10, acc[2]); acc[3] = fmaf(t0[3] + t1[3], s10, acc[3]);
+                acc[0] = fmaf(u0[0] + u1[0], s01, acc[0]); acc[1] = fmaf(u0[1] + u1[1], s01, acc[1]);
+                acc[2] = fmaf(u0[2] + u1[2], s11, acc[2]); acc[3] = fmaf(u0[3] + u1[3], s11, acc[3]);
             } else if (FMT == MKS_FMT_FP8) {
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
@@ -675,15 +739,16 @@ __device__ __forceinline__ void unit_steps(Shared& S, Mut& mu, const mk_stage_de
                     a[3] = cvt_e4m3x2(hi >> 16);
                     uint2 b = make_uint2(0u, 0u);
                     if (col_live) b = *reinterpret_cast<const uint2*>(xk + j * 32);
-                    if (blocks) mma_f16(tmp, a, b.x, b.y);
-                    else mma_f16(acc, a, b.x, b.y);
+                    if (blocks) mma_f16(j == 0 ? tmp : tmp2, a, b.x, b.y);
+                    else mma_f16(j == 0 ? acc : acc2, a, b.x, b.y);
                 }
                 if (blocks && (kstep & 3) == 3) {
                     // one scale per 128 k for rows 0-7 of the tile and one for rows 8-15 (a GLU tile pairs two matrices)
                     const float2 bs = *reinterpret_cast<const float2*>(sc_base + (st >> 2) * 8);
-                    acc[0] = fmaf(tmp[0], bs.x, acc[0]); acc[1] = fmaf(tmp[1], bs.x, acc[1]);
-                    acc[2] = fmaf(tmp[2], bs.y, acc[2]); acc[3] = fmaf(tmp[3], bs.y, acc[3]);
+                    acc[0] = fmaf(tmp[0] + tmp2[0], bs.x, acc[0]); acc[1] = fmaf(tmp[1] + tmp2[1], bs.x, acc[1]);
+                    acc[2] = fmaf(tmp[2] + tmp2[2], bs.y, acc[2]); acc[3] = fmaf(tmp[3] + tmp2[3], bs.y, acc[3]);
                     tmp[0] = tmp[1] = tmp[2] = tmp[3] = 0.f;
+                    tmp2[0] = tmp2[1] = tmp2[2] = tmp2[3] = 0.f;
                 }
             } else if (FMT == MKS_FMT_INT8) {
                 const uint32_t x0 = wq.x ^ 0x80808080u, x1 = wq.y ^ 0x80808080u, x2 = wq.z ^ 0x80808080u, x3 = wq.w ^ 0x80808080u;
@@ -697,18 +762,20 @@ __device__ __forceinline__ void unit_steps(Shared& S, Mut& mu, const mk_stage_de
                     a[3] = cvt_s8x2(hi, 0x4342);
                     uint2 b = make_uint2(0u, 0u);
                     if (col_live) b = *reinterpret_cast<const uint2*>(xk + j * 32);
-                    mma_f16(acc, a, b.x, b.y);
+                    mma_f16(j == 0 ? acc : acc2, a, b.x, b.y);
                 }
             } else {
                 uint32_t a[4] = {wq.x, wq.z, wq.y, wq.w};                 // row g: (x, y), row g + 8: (z, w)
                 uint2 b = make_uint2(0u, 0u);
                 if (col_live) b = *reinterpret_cast<const uint2*>(xk);
-                mma_bf16(acc, a, b.x, b.y);
+                if (st & 1) mma_bf16(acc2, a, b.x, b.y);
+                else mma_bf16(acc, a, b.x, b.y);
             }
         }
         __syncwarp();
         if (lane_() == 0) mbar_arrive(&S.empty[slot]);
     }
+    return make_float4(acc[0] + acc2[0], acc[1] + acc2[1], acc[2] + acc2[2], acc[3] + acc2[3]);
 }
 
 __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc& d, const Args& A, u64& ar_seq) {
@@ -744,12 +811,18 @@ __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc&
                 const uint8_t* xcol = S.xs() + (size_t)g * stride;
                 const bool live = g < ncols;
                 const uint32_t chunk0 = mu.chunk_n;
+                UnitGeo ug;
+                ug.n_chunks = gm.n_chunks;
+                ug.chunk_steps = gm.chunk_steps;
+                const bool blocks = d.i[MKS_I_BLOCK_SCALES] != 0;
+                float4 r;
                 switch (fmt) {
-                    case MKS_FMT_MXFP4: unit_steps<MKS_FMT_MXFP4>(S, mu, d, gm, chunk0, xcol, live, acc); break;
-                    case MKS_FMT_FP8: unit_steps<MKS_FMT_FP8>(S, mu, d, gm, chunk0, xcol, live, acc); break;
-                    case MKS_FMT_INT8: unit_steps<MKS_FMT_INT8>(S, mu, d, gm, chunk0, xcol, live, acc); break;
-                    default: unit_steps<MKS_FMT_BF16>(S, mu, d, gm, chunk0, xcol, live, acc); break;
+                    case MKS_FMT_MXFP4: r = unit_steps<MKS_FMT_MXFP4>(S, ug, chunk0, xcol, live, blocks); break;
+                    case MKS_FMT_FP8: r = unit_steps<MKS_FMT_FP8>(S, ug, chunk0, xcol, live, blocks); break;
+                    case MKS_FMT_INT8: r = unit_steps<MKS_FMT_INT8>(S, ug, chunk0, xcol, live, blocks); break;
+                    default: r = unit_steps<MKS_FMT_BF16>(S, ug, chunk0, xcol, live, blocks); break;
                 }
+                acc[0] = r.x; acc[1] = r.y; acc[2] = r.z; acc[3] = r.w;
                 // undo the input scaling, fold the second piece's columns onto the first
                 acc[0] *= S.xinv[2 * t]; acc[2] *= S.xinv[2 * t];
                 acc[1] *= S.xinv[2 * t + 1]; acc[3] *= S.xinv[2 * t + 1];
@@ -784,16 +857,25 @@ __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc&
                     if (finish) {
                         fence_acq_rel_gpu();
                         acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                        // eight partial tiles are requested at a time, then added in arrival-slot order
 #pragma unroll 1
-                        for (int a = 0; a < arrivals; a++) {
-                            const float4 v = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)cidx * arrivals + a) * 128) + lane_());
-                            float c0 = 1.f, c1 = 1.f;
-                            if (reduce_groups) {
-                                c0 = S.coef[(a / gm.S) * 8 + 2 * t];
-                                c1 = S.coef[(a / gm.S) * 8 + 2 * t + 1];
-                            }
-                            acc[0] = fmaf(v.x, c0, acc[0]); acc[1] = fmaf(v.y, c1, acc[1]);
-                            acc[2] = fmaf(v.z, c0, acc[2]); acc[3] = fmaf(v.w, c1, acc[3]);
+                        for (int a0 = 0; a0 < arrivals; a0 += 8) {
+                            float4 v[8];
+#pragma unroll
+                            for (int u = 0; u < 8; u++)
+                                if (a0 + u < arrivals)
+                                    v[u] = __ldcg(reinterpret_cast<const float4*>(part + ((size_t)cidx * arrivals + a0 + u) * 128) + lane_());
+#pragma unroll
+                            for (int u = 0; u < 8; u++)
+                                if (a0 + u < arrivals) {
+                                    float c0 = 1.f, c1 = 1.f;
+                                    if (reduce_groups) {
+                                        c0 = S.coef[((a0 + u) / gm.S) * 8 + 2 * t];
+                                        c1 = S.coef[((a0 + u) / gm.S) * 8 + 2 * t + 1];
+                                    }
+                                    acc[0] = fmaf(v[u].x, c0, acc[0]); acc[1] = fmaf(v[u].y, c1, acc[1]);
+                                    acc[2] = fmaf(v[u].z, c0, acc[2]); acc[3] = fmaf(v[u].w, c1, acc[3]);
+                                }
                         }
                     }
                 } else if (reduce_groups) {

@@ -69,7 +69,8 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
             if (QPK < 1 || QPK > 8 || QPK + 2 > NCW) return sfail(MK_ERR_BADARG, "stage %d: %d query heads per KV head", s, QPK);
             if (HD != 256 && HD != 512) return sfail(MK_ERR_BADARG, "stage %d: head dim %d", s, HD);
             if (CP < 16 || CP > ATTN_MAX_CHUNK) return sfail(MK_ERR_BADARG, "stage %d: %d positions per task", s, CP);
-            if ((long long)(QPK * HD + 2 * HD + QPK * CP + 2 * QPK + 4) * 4 > XS_BYTES) return sfail(MK_ERR_BADARG, "stage %d: attention scratch does not fit", s);
+            if ((long long)(QPK * HD + 2 * HD + QPK * CP + QPK * ATTN_MAX_CHUNKS + 2 * QPK + CP + 4) * 4 > XS_BYTES) return sfail(MK_ERR_BADARG, "stage %d: attention scratch does not fit", s);
+            if (d.i[MKS_I_MAX_CHUNKS] < 1 || d.i[MKS_I_MAX_CHUNKS] > ATTN_MAX_CHUNKS) return sfail(MK_ERR_BADARG, "stage %d: %d split records per head (at most %d)", s, d.i[MKS_I_MAX_CHUNKS], ATTN_MAX_CHUNKS);
         } else if (d.op == MKS_OP_GDN) {
             if (d.i[MKS_I_NKH] < 1 || d.i[MKS_I_NVH] % d.i[MKS_I_NKH]) return sfail(MK_ERR_BADARG, "stage %d: DeltaNet heads", s);
         } else if (d.op == MKS_OP_ROUTE) {
@@ -81,6 +82,29 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
         }
     }
     return MK_OK;
+}
+
+// Bytes of the shared staging area a program needs at `batch` sequences: the widest staged GEMV input or
+// the largest mixer scratch.  What is left of the SM's shared memory becomes ring slots.
+static int64_t scratch_bytes(const mk_stage_desc* prog, int n_stages, int batch) {
+    int64_t need = 4096;
+    for (int s = 0; s < n_stages; s++) {
+        const mk_stage_desc& d = prog[s];
+        int64_t b = 0;
+        if (d.op == MKS_OP_GEMV) {
+            const int stride = ((d.i[MKS_I_KC] * 2 + 127) / 128) * 128 + 32;
+            b = (int64_t)stride * batch * d.i[MKS_I_PIECES];
+        } else if (d.op == MKS_OP_ATTN) {
+            const int QPK = d.i[MKS_I_NQ] / d.i[MKS_I_NKV], HD = d.i[MKS_I_HD], CP = d.i[MKS_I_CHUNK_POS];
+            b = (int64_t)(QPK * HD + 2 * HD + QPK * CP + QPK * ATTN_MAX_CHUNKS + 2 * QPK + CP + 4) * 4;
+        }
+        need = b > need ? b : need;
+    }
+    return (need + 127) / 128 * 128;
+}
+extern "C" int64_t mk_stage_scratch_bytes(const mk_stage_desc* prog, int n_stages, int batch) {
+    if (!prog || n_stages < 1 || batch < 1 || batch > MKS_MAX_BATCH) return -1;
+    return scratch_bytes(prog, n_stages, batch);
 }
 
 extern "C" int mk_stage_count(const mk_stage_desc* prog, int n_stages, int64_t* barriers, int64_t* allreduces) {
@@ -97,7 +121,7 @@ extern "C" int mk_stage_count(const mk_stage_desc* prog, int n_stages, int64_t* 
 
 extern "C" int64_t mk_stage_query(int what) {
     switch (what) {
-        case MKS_Q_SMEM_BYTES: return (int64_t)NS * mks::SLOT_BYTES + XS_BYTES + MISC_BYTES;
+        case MKS_Q_SMEM_BYTES: return SMEM_TOTAL;
         case MKS_Q_N_THREADS: return mks::NTHREADS;
         case MKS_Q_SLOT_BYTES: return mks::SLOT_BYTES;
         case MKS_Q_XS_BYTES: return XS_BYTES;
@@ -109,7 +133,6 @@ extern "C" int64_t mk_stage_query(int what) {
     }
 }
 static_assert(sizeof(mk_stage_desc) == 288, "descriptor layout");
-static_assert(NS * 16 + 8 * 8 + (17 * 8 + 8 + 8 + 8 + 8 + 64 + 64 + MAX_GROUPS * 8 + MAX_GROUPS + 8 + 4) * 4 + 8 + 2 * 288 <= MISC_BYTES, "misc area");
 
 extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     if (!a) return sfail(MK_ERR_BADARG, "mk_stage_launch: null argument");
@@ -148,8 +171,17 @@ extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     for (int r = 0; r < MKS_MAX_RANKS; r++) A.mailbox[r] = reinterpret_cast<unsigned long long*>(a->mailbox[r]);
     A.ar_base = a->ar_base;
     A.pf_bytes = a->pf_bytes;
+    A.prof_cta = a->prof_cta;
+    // shared memory: the staging area the program needs (the caller computes it with mk_stage_scratch_bytes), the rest ring slots
+    const int xs = a->xs_bytes > 0 ? (a->xs_bytes + 127) / 128 * 128 : XS_BYTES;
+    if (xs > XS_BYTES) return sfail(MK_ERR_BADARG, "mk_stage_launch: staging area of %d bytes exceeds %d", xs, XS_BYTES);
+    int depth = (SMEM_TOTAL - MISC_BYTES - xs) / (16 * mks::SLOT_BYTES);
+    depth = depth > MAX_RING_DEPTH ? MAX_RING_DEPTH : depth;
+    if (depth < 2) return sfail(MK_ERR_BADARG, "mk_stage_launch: no room for two ring slots per warp");
+    A.xs_bytes = xs;
+    A.ring_depth = depth;
 
-    const int smem = (int)mk_stage_query(MKS_Q_SMEM_BYTES);
+    const int smem = MISC_BYTES + xs + 16 * depth * mks::SLOT_BYTES;
     MKS_CUDA(cudaFuncSetAttribute(stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     void* kargs[] = {&A};
     MKS_CUDA(cudaLaunchCooperativeKernel((const void*)stage_kernel, dim3(grid), dim3(mks::NTHREADS), kargs, smem, static_cast<cudaStream_t>(stream)));

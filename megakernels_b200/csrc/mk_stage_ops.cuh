@@ -249,6 +249,11 @@ __device__ void head_prepare(Shared& S, Mut& mu, const float* src, float* dst, i
     __syncwarp();
 }
 
+// Latency, not bandwidth, decides this stage (a task reads a few hundred KB): every loop over cached positions
+// asks for several rows before it uses the first, the page-table lookups are done once per task into shared
+// memory, and the merge first turns the chunks' (max, sum) pairs into weights in shared memory.
+constexpr int ATTN_MAX_CHUNKS = 256;      // split records per (sequence, kv head)
+
 template <bool KVF32>
 __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc& d) {
     const int NQ = d.i[MKS_I_NQ], NKV = d.i[MKS_I_NKV], HD = d.i[MKS_I_HD], ROT = d.i[MKS_I_ROT];
@@ -272,13 +277,15 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
     const bool q_bf16 = d.i[MKS_I_Q_BF16] != 0;
     const int esz = KVF32 ? 4 : 2;
     const int rec = QPK * (HD + 2);                            // floats of one chunk's partial record
+    const int max_chunks = d.i[MKS_I_MAX_CHUNKS];
     // shared scratch
-    float* q_s = reinterpret_cast<float*>(S.xs());               // [QPK][HD]
+    float* q_s = reinterpret_cast<float*>(S.xs());             // [QPK][HD]
     float* kn_s = q_s + QPK * HD;                              // [HD] the new K row
     float* vn_s = kn_s + HD;                                   // [HD] the new V row
-    float* sc_s = vn_s + HD;                                   // [QPK][CP]
-    float* stat_s = sc_s + QPK * CP;                           // [QPK][2]
-    int* flag_s = reinterpret_cast<int*>(stat_s + 2 * QPK);
+    float* sc_s = vn_s + HD;                                   // [QPK][CP] scores, then probabilities
+    float* wn_s = sc_s + QPK * CP;                             // [QPK][chunks] merge weights
+    float* stat_s = wn_s + QPK * ATTN_MAX_CHUNKS;              // [QPK][2]
+    uint32_t* row_s = reinterpret_cast<uint32_t*>(stat_s + 2 * QPK);   // [CP] element offset of each position's cache row
     // chunks per sequence: the longest context decides the task grid
     int maxn = 1;
 #pragma unroll 1
@@ -301,7 +308,8 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
         const float* cs = cosT + (size_t)pos * pairs;
         const float* sn = sinT + (size_t)pos * pairs;
         const bool has_new = last == n;
-        // 1. queries (warps 0..QPK-1), new K (warp QPK), new V (warp QPK + 1)
+        const int ncached = has_new ? np - 1 : np;             // positions of the chunk that come from the cache
+        // 1. queries (warps 0..QPK-1), new K (warp QPK), new V (warp QPK + 1), cache row offsets (the other warps)
         if (warp_() < QPK) {
             const int hq = kvh * QPK + warp_();
             head_prepare(S, mu, y + q_off + (size_t)hq * q_hs, q_s + warp_() * HD, HD, qn, norm_off, true, eps, cs, sn, pairs, pair_dist, q_bf16);
@@ -310,50 +318,76 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
         } else if (has_new && warp_() == QPK + 1) {
             const float* vsrc = v_off >= 0 ? y + v_off + (size_t)kvh * HD : y + k_off + (size_t)kvh * HD;
             head_prepare(S, mu, vsrc, vn_s, HD, nullptr, 0.f, d.i[MKS_I_V_NORM] != 0, eps, nullptr, nullptr, 0, 0, !KVF32);
+        } else if (warp_() >= QPK + 2) {
+#pragma unroll 1
+            for (int i = tid_() - (QPK + 2) * 32; i < np; i += NCT - (QPK + 2) * 32) {
+                const int p = first + i;
+                const int page = __ldg(bt + (size_t)m * maxpages + p / 64);
+                const uint32_t off = (uint32_t)((((size_t)page * NKV + kvh) * 64 + (p & 63)) * HD);
+                row_s[i] = off;
+                // ask the L2 for the rows now: the weight stream between two attention stages has pushed the cache's
+                // pages out of the TLBs, and the first touch of a page costs several microseconds
+                if (i < ncached) {
+#pragma unroll 1
+                    for (int b = 0; b < HD * esz; b += 128) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)off * esz + b));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)off * esz + b));
+                    }
+                }
+            }
         }
         consumer_sync();
         if (has_new && warp_() >= QPK && warp_() < QPK + 2) {
             // append the new row to the paged cache
-            const int page = __ldg(bt + (size_t)m * maxpages + pos / 64);
-            const size_t row = (((size_t)page * NKV + kvh) * 64 + (pos & 63)) * HD;
             const float* srcv = warp_() == QPK ? kn_s : vn_s;
-            uint8_t* dst = (warp_() == QPK ? kc : vc) + row * esz;
+            uint8_t* dst = (warp_() == QPK ? kc : vc) + (size_t)row_s[np - 1] * esz;
 #pragma unroll 1
             for (int i = lane_(); i < HD; i += 32) {
                 if (KVF32) reinterpret_cast<float*>(dst)[i] = srcv[i];
                 else reinterpret_cast<__nv_bfloat16*>(dst)[i] = __float2bfloat16_rn(srcv[i]);
             }
         }
-        // 2. scores: a warp takes every 16th position, a lane 8 (or 16) dims of the K row
+        prof_mark(S, 4);
+        // 2. scores: a warp takes every 16th position, four at a time; a lane 8 dims of every 256 of the K row
 #pragma unroll 1
-        for (int p = first + warp_(); p < last; p += NCW) {
-            const bool fresh = p == pos;
-            const int page = fresh ? 0 : __ldg(bt + (size_t)m * maxpages + p / 64);
-            const uint8_t* row = kc + ((((size_t)page * NKV + kvh) * 64 + (p & 63)) * HD) * esz;
+        for (int i = warp_(); i < np; i += NCW) {
 #pragma unroll 1
             for (int e = lane_() * 8; e < HD; e += 256) {
                 float kv[8];
-                if (fresh) {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) kv[i] = kn_s[e + i];
+                if (i < ncached) {
+                    load8<KVF32>(kc + (size_t)row_s[i] * esz, e, kv);
                 } else {
-                    load8<KVF32>(row, e, kv);
-                }
-#pragma unroll 1
-                for (int hq = 0; hq < QPK; hq++) {
-                    const float* q = q_s + hq * HD + e;
-                    float dot = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 8; i++) dot = fmaf(q[i], kv[i], dot);
-                    dot = warp_sum(dot);
-                    if (lane_() == 0) {
-                        float* dst = sc_s + hq * CP + (p - first);
-                        *dst = e < 256 ? dot * scale : *dst + dot * scale;      // head dims beyond 256 come in a second turn
+                    for (int x = 0; x < 8; x++) kv[x] = kn_s[e + x];
+                }
+                // all heads' partial dots first, then their warp sums side by side (independent shuffles overlap)
+                float dot[8];
+#pragma unroll
+                for (int hq = 0; hq < 8; hq++) {
+                    dot[hq] = 0.f;
+                    if (hq < QPK) {
+                        const float* q = q_s + hq * HD + e;
+#pragma unroll
+                        for (int x = 0; x < 8; x++) dot[hq] = fmaf(q[x], kv[x], dot[hq]);
                     }
+                }
+#pragma unroll
+                for (int o = 16; o; o >>= 1)
+#pragma unroll
+                    for (int hq = 0; hq < 8; hq++)
+                        if (hq < QPK) dot[hq] += __shfl_xor_sync(0xffffffffu, dot[hq], o);
+                if (lane_() < QPK) {
+                    float mine = 0.f;
+#pragma unroll
+                    for (int hq = 0; hq < 8; hq++)
+                        if (hq == lane_()) mine = dot[hq];
+                    float* dst = sc_s + lane_() * CP + i;
+                    *dst = e < 256 ? mine * scale : *dst + mine * scale;      // head dims beyond 256 come in a second turn
                 }
             }
         }
         consumer_sync();
+        prof_mark(S, 5);
         // 3. per head: maximum, exponentials, sum
         if (warp_() < QPK) {
             float* sc = sc_s + warp_() * CP;
@@ -364,9 +398,9 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
             float l = 0.f;
 #pragma unroll 1
             for (int i = lane_(); i < np; i += 32) {
-                const float e = __expf(sc[i] - mx);
-                sc[i] = e;
-                l += e;
+                const float ex = __expf(sc[i] - mx);
+                sc[i] = ex;
+                l += ex;
             }
             l = warp_sum(l);
             if (lane_() == 0) {
@@ -377,7 +411,7 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
         consumer_sync();
         // 4. P x V: warp w owns dims [16 w, 16 w + 16) of every 256; lane = (query head, group of 4 dims), so a
         //    lane adds up its four outputs over all positions and nothing is reduced across lanes
-        float* prec = part + ((size_t)(m * NKV + kvh) * d.i[MKS_I_MAX_CHUNKS] + ch) * rec;
+        float* prec = part + ((size_t)(m * NKV + kvh) * max_chunks + ch) * rec;
         {
             const int hq = lane_() >> 2, e4 = (lane_() & 3) * 4;
 #pragma unroll 1
@@ -386,24 +420,24 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
                 if (hq < QPK) {
                     const float* pr = sc_s + hq * CP;
-#pragma unroll 4
-                    for (int p = first; p < last; p++) {
+#pragma unroll 8
+                    for (int i = 0; i < ncached; i++) {
+                        const uint8_t* row = vc + (size_t)row_s[i] * esz;
                         float v0, v1, v2, v3;
-                        if (p == pos) {
-                            v0 = vn_s[e0]; v1 = vn_s[e0 + 1]; v2 = vn_s[e0 + 2]; v3 = vn_s[e0 + 3];
+                        if (KVF32) {
+                            const float4 qv = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + e0));
+                            v0 = qv.x; v1 = qv.y; v2 = qv.z; v3 = qv.w;
                         } else {
-                            const int page = __ldg(bt + (size_t)m * maxpages + p / 64);
-                            const uint8_t* row = vc + ((((size_t)page * NKV + kvh) * 64 + (p & 63)) * HD) * esz;
-                            if (KVF32) {
-                                const float4 q = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + e0));
-                                v0 = q.x; v1 = q.y; v2 = q.z; v3 = q.w;
-                            } else {
-                                const uint2 q = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(row) + e0));
-                                v0 = bf_lo(q.x); v1 = bf_hi(q.x); v2 = bf_lo(q.y); v3 = bf_hi(q.y);
-                            }
+                            const uint2 qv = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(row) + e0));
+                            v0 = bf_lo(qv.x); v1 = bf_hi(qv.x); v2 = bf_lo(qv.y); v3 = bf_hi(qv.y);
                         }
-                        const float w = pr[p - first];
+                        const float w = pr[i];
                         a0 = fmaf(w, v0, a0); a1 = fmaf(w, v1, a1); a2 = fmaf(w, v2, a2); a3 = fmaf(w, v3, a3);
+                    }
+                    if (has_new) {
+                        const float w = pr[np - 1];
+                        a0 = fmaf(w, vn_s[e0], a0); a1 = fmaf(w, vn_s[e0 + 1], a1);
+                        a2 = fmaf(w, vn_s[e0 + 2], a2); a3 = fmaf(w, vn_s[e0 + 3], a3);
                     }
                     __stcg(reinterpret_cast<float4*>(prec + hq * HD + e0), make_float4(a0, a1, a2, a3));
                 }
@@ -413,6 +447,7 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
         // 5. arrival; the last chunk merges
         fence_acq_rel_gpu();
         consumer_sync();
+        prof_mark(S, 6);
         if (tid_() == 0) {
             const unsigned old = atomicAdd(cnt + m * NKV + kvh, 1u);
             const int is_last = (int)(old + 1u == (unsigned)nch);
@@ -420,28 +455,53 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
                 cnt[m * NKV + kvh] = 0u;
                 fence_acq_rel_gpu();
             }
-            *flag_s = is_last;
+            S.flag = is_last;
         }
         consumer_sync();
-        if (*flag_s) {
-            const float* pbase = part + ((size_t)(m * NKV + kvh) * d.i[MKS_I_MAX_CHUNKS]) * rec;
+        if (S.flag) {
+            const float* pbase = part + ((size_t)(m * NKV + kvh) * max_chunks) * rec;
+            // weights of the chunks: w[hq][j] = exp(max_j - max) / sum_j' exp(max_j' - max) l_j'
 #pragma unroll 1
-            for (int idx = tid_(); idx < QPK * HD; idx += NCT) {
-                const int hq = idx / HD, dd = idx % HD;
+            for (int i = tid_(); i < QPK * nch; i += NCT) {
+                const int hq = i / nch, j = i - hq * nch;
+                wn_s[hq * ATTN_MAX_CHUNKS + j] = ldcg_f(pbase + (size_t)j * rec + QPK * HD + 2 * hq);
+            }
+            consumer_sync();
+            if (warp_() < QPK) {
+                float* w = wn_s + warp_() * ATTN_MAX_CHUNKS;
                 float mx = -3.0e38f;
 #pragma unroll 1
-                for (int j = 0; j < nch; j++) mx = fmaxf(mx, ldcg_f(pbase + (size_t)j * rec + QPK * HD + 2 * hq));
-                float num = 0.f, den = 0.f;
+                for (int j = lane_(); j < nch; j += 32) mx = fmaxf(mx, w[j]);
+                mx = warp_max(mx);
+                float den = 0.f;
 #pragma unroll 1
-                for (int j = 0; j < nch; j++) {
-                    const float w = __expf(ldcg_f(pbase + (size_t)j * rec + QPK * HD + 2 * hq) - mx);
-                    num = fmaf(w, ldcg_f(pbase + (size_t)j * rec + hq * HD + dd), num);
-                    den = fmaf(w, ldcg_f(pbase + (size_t)j * rec + QPK * HD + 2 * hq + 1), den);
+                for (int j = lane_(); j < nch; j += 32) {
+                    const float ex = __expf(w[j] - mx);
+                    w[j] = ex;
+                    den += ex * ldcg_f(pbase + (size_t)j * rec + QPK * HD + 2 * warp_() + 1);
                 }
-                float o = num / den;
+                den = warp_sum(den);
+                __syncwarp();
+#pragma unroll 1
+                for (int j = lane_(); j < nch; j += 32) w[j] = w[j] / den;
+            }
+            consumer_sync();
+#pragma unroll 1
+            for (int idx = tid_(); idx < QPK * (HD / 4); idx += NCT) {
+                const int hq = idx / (HD / 4), dd = (idx - hq * (HD / 4)) * 4;
+                const float* w = wn_s + hq * ATTN_MAX_CHUNKS;
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll 8
+                for (int j = 0; j < nch; j++) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(pbase + (size_t)j * rec + hq * HD + dd));
+                    o0 = fmaf(w[j], v.x, o0); o1 = fmaf(w[j], v.y, o1); o2 = fmaf(w[j], v.z, o2); o3 = fmaf(w[j], v.w, o3);
+                }
                 const int hfull = kvh * QPK + hq;
-                if (gate_off >= 0) o *= sigmoid_f(ldcg_f(y + q_off + (size_t)hfull * q_hs + gate_off + dd));
-                __stcg(Y2 + (size_t)m * d.i[MKS_I_A_Y2_STRIDE] + (size_t)hfull * HD + dd, o);
+                if (gate_off >= 0) {
+                    const float4 g = __ldcg(reinterpret_cast<const float4*>(y + q_off + (size_t)hfull * q_hs + gate_off + dd));
+                    o0 *= sigmoid_f(g.x); o1 *= sigmoid_f(g.y); o2 *= sigmoid_f(g.z); o3 *= sigmoid_f(g.w);
+                }
+                __stcg(reinterpret_cast<float4*>(Y2 + (size_t)m * d.i[MKS_I_A_Y2_STRIDE] + (size_t)hfull * HD + dd), make_float4(o0, o1, o2, o3));
             }
         }
         consumer_sync();
@@ -530,7 +590,7 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
 // ---- the kernel ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constant__ Args A_in) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Shared& S = *reinterpret_cast<Shared*>(smem_raw + (size_t)NS * SLOT_BYTES + XS_BYTES);
+    Shared& S = *reinterpret_cast<Shared*>(smem_raw);
     Mut mu;
     mu.chunk_n = 0; mu.dead = false;
     {
@@ -580,21 +640,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
         consumer_sync();
 #pragma unroll 1
         for (int si = 0; si < A.n_stages; si++) {
-#ifndef MKS_EXP_NOANY
             if (consumer_any(mu.dead || S.abort_flag != 0)) {
                 failed = true;
                 break;
             }
-#endif
-#ifdef MKS_EXP_NODESC
-            const mk_stage_desc& d = A.prog[si];
-            uint32_t next_word = 0;
-#else
             const mk_stage_desc& d = S.desc[cur];
             uint32_t next_word = 0;
             if (tid_() < DESC_WORDS) next_word = __ldg(reinterpret_cast<const uint32_t*>(&A.prog[si + 1 < A.n_stages ? si + 1 : 0]) + tid_());
-#endif
-            if (tid_() == 0) S.prof = (A.prof && cta_() == 0 && step == A.n_steps - 1) ? A.prof + (size_t)si * PROF_FIELDS : nullptr;
+            if (tid_() == 0) {
+                // prof_cta >= 0: that CTA's rows [stage][8]; prof_cta < 0: every CTA's rows [cta][stage][8]
+                if (A.prof && step == A.n_steps - 1 && (A.prof_cta < 0 || cta_() == A.prof_cta))
+                    S.prof = A.prof + ((A.prof_cta < 0 ? (size_t)cta_() * A.n_stages : 0) + si) * PROF_FIELDS;
+                else
+                    S.prof = nullptr;
+            }
             prof_mark(S, 0);
             switch (d.op) {
                 case MKS_OP_EMBED: embed_stage(S, mu, d, A, step, (uint32_t)(A.bar_base / grid_() + bar_n) + 1u); break;

@@ -13,7 +13,7 @@ def __getattr__(name):
     if name == "Engine":
         from .runner import Engine
         return Engine
-    if name == "SynthWeights":
-        from .synth import SynthWeights
-        return SynthWeights
+    if name in ("SynthWeights", "make_prompt"):
+        from . import synth
+        return getattr(synth, name)
     raise AttributeError(name)

@@ -53,11 +53,11 @@ class StageArgs(ctypes.Structure):
                 ("tokens_out", ctypes.c_uint64), ("barrier", ctypes.c_uint64), ("barrier_base", ctypes.c_uint64),
                 ("status", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64), ("prof", ctypes.c_uint64),
                 ("tp", ctypes.c_int32), ("rank", ctypes.c_int32), ("mailbox", ctypes.c_uint64 * MAX_RANKS),
-                ("ar_base", ctypes.c_uint64), ("grid", ctypes.c_int32), ("reserved", ctypes.c_int32),
-                ("pf_bytes", ctypes.c_int64)]
+                ("ar_base", ctypes.c_uint64), ("grid", ctypes.c_int32), ("prof_cta", ctypes.c_int32),
+                ("pf_bytes", ctypes.c_int64), ("xs_bytes", ctypes.c_int32), ("reserved2", ctypes.c_int32)]
 
 
-STAGE_EXPORTS = ["mk_stage_launch", "mk_stage_validate", "mk_stage_count", "mk_stage_query", "mk_peer_alloc", "mk_peer_open",
+STAGE_EXPORTS = ["mk_stage_launch", "mk_stage_validate", "mk_stage_count", "mk_stage_query", "mk_stage_scratch_bytes", "mk_peer_alloc", "mk_peer_open",
                  "mk_peer_close", "mk_peer_free"]
 STAGE_QUERIES = ["SMEM_BYTES", "N_THREADS", "SLOT_BYTES", "XS_BYTES", "DESC_BYTES", "MAX_GROUPS", "MAILBOX_BYTES", "ATTN_MAX_CHUNK"]
 
@@ -75,12 +75,14 @@ def lib():
         L.mk_stage_count.argtypes = [P(StageDesc), ctypes.c_int, P(ctypes.c_int64), P(ctypes.c_int64)]
         L.mk_stage_query.argtypes = [ctypes.c_int]
         L.mk_stage_query.restype = ctypes.c_int64
+        L.mk_stage_scratch_bytes.argtypes = [P(StageDesc), ctypes.c_int, ctypes.c_int]
+        L.mk_stage_scratch_bytes.restype = ctypes.c_int64
         L.mk_peer_alloc.argtypes = [ctypes.c_int, ctypes.c_int64, P(ctypes.c_uint64), P(ctypes.c_uint8)]
         L.mk_peer_open.argtypes = [ctypes.c_int, P(ctypes.c_uint8), P(ctypes.c_uint64)]
         L.mk_peer_close.argtypes = [ctypes.c_uint64]
         L.mk_peer_free.argtypes = [ctypes.c_uint64]
         for name in STAGE_EXPORTS:
-            if name != "mk_stage_query":
+            if name not in ("mk_stage_query", "mk_stage_scratch_bytes"):
                 getattr(L, name).restype = ctypes.c_int
         _bound = True
     return L

@@ -20,8 +20,13 @@ into one tile, so that one lane holds a gate / up pair).  The reference's AMD ti
 import torch
 
 FMT_BF16, FMT_MXFP4, FMT_FP8, FMT_INT8 = 0, 1, 2, 3
+# Bit positions of the pre-arranged MXFP4 words (scale group 0): register k of a word holds two values, the sign
+# of the low one at MXFP4_SIGN_BIT[k], its three magnitude bits from MXFP4_MAG_BIT[k] up; the high one 16 bits higher.
+# Register k is rebuilt as ((w << (15 - sign)) & 0x80008000) | ((w << (9 - mag)) & 0x0E000E00).
+MXFP4_SIGN_BIT = (15, 12, 14, 13)
+MXFP4_MAG_BIT = (9, 6, 3, 0)
 STEP_K = {FMT_BF16: 16, FMT_MXFP4: 64, FMT_FP8: 32, FMT_INT8: 32}
-SLOT_BYTES = 4608
+SLOT_BYTES = 4352
 
 
 def pick_chunk_steps(unit_steps, fmt, block_scaled=False):
@@ -92,7 +97,21 @@ def pack_matrix(fmt, splits, w, scales=None, block_scales=None, row_order=None):
         x = _pad_rows(w, T * 16)
         v = _steps_view(x, splits, 64).reshape(T, 2, 8, splits, unit_steps, 4, 4, 2, 2)    # t h g s st j q slp nib
         v = v.permute(3, 0, 4, 2, 6, 1, 5, 7, 8).contiguous()                                # s t st g q h j slp nib
-        body = (v[..., 0] | (v[..., 1] << 4)).reshape(splits, T, nch, cs * 512)
+        plain = (v[..., 0] | (v[..., 1] << 4))                                               # s t st g q h j slp: one byte per nibble pair
+        # scale group 0 (j = 0, 1) goes out with its bits pre-arranged for shift-and-mask conversion: register
+        # k = 2 j + slp of a word takes nib 0 in its low half and nib 1 in its high half
+        c = v[..., :2, :, :].to(torch.int64)                                                 # s t st g q h j(2) slp nib
+        word = torch.zeros(c.shape[:-3], dtype=torch.int64, device=c.device)
+        for j in range(2):
+            for slp in range(2):
+                k = 2 * j + slp
+                for nib in range(2):
+                    code = c[..., j, slp, nib]
+                    word |= ((code >> 3) << (MXFP4_SIGN_BIT[k] + 16 * nib)) | ((code & 7) << (MXFP4_MAG_BIT[k] + 16 * nib))
+        arranged = torch.stack([(word >> (8 * i)) & 0xFF for i in range(4)], dim=-1).to(torch.uint8)   # s t st g q h 4
+        lane = torch.cat([arranged, plain[..., 2:, :].reshape(plain.shape[:-2] + (4,))], dim=-1)       # s t st g q h 8: word of group 0, word of group 1
+        # the kernel's 128-bit read is (row g: group 0, group 1, row g + 8: group 0, group 1): h is already outside
+        body = lane.reshape(splits, T, nch, cs * 512)
         sc = _pad_rows(scales, T * 16).reshape(T, 2, 8, splits, unit_steps, 2)               # t h g s st grp
         extra = sc.permute(3, 0, 4, 2, 1, 5).contiguous().reshape(splits, T, nch, cs * 32)   # s t st g h grp
     else:
@@ -142,7 +161,15 @@ def unpack_matrix(packed, meta, K):
                             row = t * 16 + g + 8 * half
                             hb = b[half * 8: half * 8 + 8]
                             if fmt == FMT_MXFP4:
-                                for j in range(4):
+                                word = int.from_bytes(bytes(hb[:4].tolist()), "little")
+                                for j in range(2):                                  # scale group 0: pre-arranged bits
+                                    for slp in range(2):
+                                        r = 2 * j + slp
+                                        for nib in range(2):
+                                            sgn = (word >> (MXFP4_SIGN_BIT[r] + 16 * nib)) & 1
+                                            mag = (word >> (MXFP4_MAG_BIT[r] + 16 * nib)) & 7
+                                            out[row, k0 + 16 * j + 4 * q + 2 * slp + nib] = lut[mag | (sgn << 3)]
+                                for j in range(2, 4):                               # scale group 1: plain nibbles
                                     for slp in range(2):
                                         byte = int(hb[2 * j + slp])
                                         k = k0 + 16 * j + 4 * q + 2 * slp

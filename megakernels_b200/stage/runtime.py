@@ -143,6 +143,7 @@ class Runtime:
         nb, na = ctypes.c_int64(), ctypes.c_int64()
         _lib.check(self.lib.mk_stage_count(host, len(program.stages), ctypes.byref(nb), ctypes.byref(na)))
         self.barriers_per_step, self.allreduces_per_step = nb.value, na.value
+        self.xs_bytes = int(self.lib.mk_stage_scratch_bytes(host, len(program.stages), self.M))
         raw = bytes(host)
         self.program_dev = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
         self.n_stages = len(program.stages)
@@ -162,7 +163,7 @@ class Runtime:
             if t.dtype == torch.int32:
                 t.zero_()
 
-    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None):
+    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None, prof_cta=0):
         """`n_stages` runs only a prefix of the program (one step; for stage-by-stage checks in tests)."""
         full = n_stages is None
         n_stages = self.n_stages if full else n_stages
@@ -172,7 +173,7 @@ class Runtime:
                         tokens_out=tokens_out.data_ptr() if tokens_out is not None else 0, barrier=self.bar.data_ptr(),
                         barrier_base=self.bar_base, status=self.status.data_ptr(), spin_limit_ns=self.spin_limit_ns,
                         prof=prof.data_ptr() if prof is not None else 0, tp=self.tp, rank=self.rank, ar_base=self.ar_base,
-                        grid=self.grid, pf_bytes=self.pf_bytes)
+                        grid=self.grid, pf_bytes=self.pf_bytes, prof_cta=prof_cta, xs_bytes=self.xs_bytes)
         if self.tp > 1:
             for r in range(self.tp):
                 a.mailbox[r] = self.mailbox.addresses[r]
