@@ -1,21 +1,24 @@
-"""Decode throughput of the megakernel on the benchmark's int8 0.8B configuration.
+"""Decode throughput of the megakernels on the benchmark's configurations.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--batch B]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...        (N = 2, 4, 8)
 
-Workload (configuration 2 of the benchmark definition): the 0.8B Gated-DeltaNet / attention hybrid,
-vocab 151936, int8 per-channel weights quantised from seeded N(0, 0.02) bf16 weights; every sequence
-has a 512-token uniform-random prompt already in its recurrent state and KV cache, then takes 512
-greedy decode steps.  The configuration is measured at batch 8 (the headline value: eight sequences
-per pass over the weights, `Megakernel.run_batch`) and at batch 1 (reported beside it under
-"batch1": the single-sequence kernel, `Megakernel.run`).  One bench "step" is one such generation of
-512 tokens per sequence: one kernel launch.  Synthetic weights and prompts stand in for the
-checkpoint and text the reference measures on.
+Headline workload (configuration 3 of the benchmark definition, the one the multi-GPU axis of the metric
+exists for): the 27B dense Gated-DeltaNet / gated-attention hybrid with MXFP4 weights (64 layers, hidden 5120,
+vocabulary 248320, untied bf16 LM head), quantised from seeded N(0, 0.02) weights; `batch` sequences (8 by
+default) whose 2048-token prompts have gone through the kernel, bf16 KV cache; one bench "step" is 256 greedy
+decode steps of every sequence in ONE kernel launch per GPU.  With --gpus N the model is sharded over N
+tensor-parallel ranks (strong scaling: the same job on more GPUs); the partial sums of the row-parallel
+projections are all-reduced inside the kernel through peer memory, NCCL only reduces the timings.
 
-The 0.8B model is not sharded: with --gpus N every rank runs an independent replica (weak scaling)
-and the value is the sum over ranks divided by the slowest rank's time.
+Beside the headline, on one GPU, the line carries the same measurement at batch 1 (`cfg3_batch1`), the 0.8B
+hybrid with int8 weights at batch 8 and batch 1 with a speculative-cycle leg (`cfg2_int8`), the 0.8B with bf16
+weights at batch 1 (`cfg1_bf16`), and a CPU baseline.  Synthetic weights and prompts stand in for the checkpoints
+and text the reference measures on.
 
-`--impl reference` times the CPU restatement of the reference's own PyTorch decoder (oracle/) on the
-host cores, on a bounded sample of the same workload.
+`--impl reference` times the CPU restatement of the reference's own PyTorch decoder for the same model
+(oracle/) on the host cores, on a bounded sample of the workload: a few full-width layers plus the LM head,
+scaled to the model's depth.
 """
 
 import argparse
@@ -31,13 +34,14 @@ sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
 
-METRIC = "decode tok/s at batch 8 and batch 1 (0.8B hybrid, int8 per-channel, 512-token prompt + 512 greedy steps)"
-PROMPT, GENERATE = 512, 512
-L2_BYTES = 126e6
+METRIC = "decode tok/s at batch 8 and batch 1, and fraction of the HBM roofline (27B MXFP4 hybrid at TP 1/2/4/8; 0.8B hybrids beside it)"
+CFG3_PROMPT, CFG3_GENERATE = 2048, 256
+PROMPT, GENERATE = 512, 512               # configuration 2 (0.8B int8)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per decode step, from the ncu captures
-# summarised under profiles/ (short launches at a short context, scaled by steps; the KV part grows with
-# context, the weight part does not): decode_kernel at batch 1, batch_kernel at batch 8.
+# summarised under profiles/ (short launches at a 64-token context; the weight part does not grow with
+# context, the KV part does): decode_kernel at batch 1, batch_kernel at batch 8.
 NCU_DRAM_BYTES_PER_STEP = {1: (11.604932e9 + 394.075904e6) / 16, 8: (13.618422e9 + 3.158837e9) / 16}
+NCU_CONTEXT = 64
 
 
 def measured_peak_gbs():
@@ -83,11 +87,195 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def bytes_per_step(mk, batch):
+def dist_env():
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    return rank, world, int(os.environ.get("LOCAL_RANK", rank))
+
+
+def aggregate(local_ms, local_tokens, world, device):
+    """(max time over ranks in ms, tokens summed over ranks).  Works on gloo/CPU tensors too."""
+    import torch.distributed as dist
+    if world == 1:
+        return local_ms, local_tokens
+    t = torch.tensor([local_ms], dtype=torch.float64, device=device)
+    n = torch.tensor([local_tokens], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.all_reduce(n, op=dist.ReduceOp.SUM)
+    return float(t), float(n)
+
+
+def roofline(bytes_per_launch, launch_s, kernel, traffic=None, **extra):
+    peak, kind = measured_peak_gbs()
+    achieved = bytes_per_launch / launch_s / 1e9
+    r = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+         "peak_kind": f"of {kind}", "frac_of_8TBs": achieved / 8000.0, "traffic": traffic,
+         "algorithmic_bytes_per_launch": bytes_per_launch, "kernel": kernel}
+    r.update(extra)
+    return r
+
+
+# ======================================================================================================
+# configuration 3: the 27B MXFP4 hybrid on the stage-machine megakernel, TP 1/2/4/8
+# ======================================================================================================
+def cfg3_config(batch, layers, tp):
+    """The `config` object both arms print: the same workload, named the same way."""
+    return {"workload": f"27B dense hybrid ({layers} layers, hidden 5120, FFN 17408, vocab 248320), MXFP4 weights + bf16 LM head, "
+                        f"batch {batch}, tensor parallel over {tp} GPU(s)",
+            "batch": batch, "prompt_tokens": CFG3_PROMPT, "decode_steps_per_bench_step": CFG3_GENERATE, "kv_dtype": "bf16",
+            "parallelism": f"tp{tp}",
+            "l2": "weights streamed per decode step (15.9 GB at TP 1) exceed the 126 MB L2; no flush needed"}
+
+
+class Cfg3:
+    """One rank's engine with the prompt context in place."""
+
+    def __init__(self, args, ctx, batch, PK=None):
+        from megakernels_b200.qwen27b import tp as TP
+        from megakernels_b200.qwen27b.dims import FULL
+        from megakernels_b200.qwen27b.synth import SynthWeights, make_prompt
+        self.ctx, self.batch, self.layers = ctx, batch, args.layers
+        self.prompt, self.generate = args.cfg3_prompt, args.cfg3_generate
+        shape = FULL.with_(layers=args.layers) if args.layers != FULL.layers else FULL
+        if PK is None:
+            # drawn on the GPU: 27 G normals on the host would take minutes; every rank draws the same values
+            W = SynthWeights(shape, layers=args.layers, seed=0, device=ctx.device, draw_device=ctx.device, keep_dequant=False)
+            PK = TP.packed(ctx, W)
+            del W
+            torch.cuda.empty_cache()
+        self.PK = PK
+        eng = TP.engine(ctx, PK, batch, maxlen=self.prompt + self.generate + 64, spin_limit_ms=10000)
+        self.eng = TP.raw(eng)
+        prompts = [make_prompt(shape.vocab, self.prompt, seed=j) for j in range(batch)]
+        if ctx.tp > 1:
+            torch.distributed.barrier()
+        self.eng.prefill(prompts)                      # the prompt goes through the kernel: one launch, `prompt` steps
+        torch.cuda.synchronize()
+        self.eng.check()
+        self.snap = [t.clone() for t in (self.eng.conv, self.eng.ssm, self.eng.pos)]
+        self.first = self.eng.rt.tok[:batch].clone()   # the greedy choice after the prompt
+        self.host_tok = torch.empty(batch, dtype=torch.int32).pin_memory()
+        self.host_tok.copy_(self.first.cpu())
+        self.host_ids = torch.empty(self.generate, batch, dtype=torch.int32).pin_memory()
+        self.launches = 0
+
+    def restore(self):
+        # positions past the prompt are simply written again, so the KV cache needs no copy
+        for dst, src in zip((self.eng.conv, self.eng.ssm, self.eng.pos), self.snap):
+            dst.copy_(src)
+
+    def one_step(self):
+        """One generation end to end: token ids from pinned host memory, one launch, chosen ids back to the host."""
+        stream = torch.cuda.current_stream()
+        self.restore()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tok = self.host_tok.to(self.ctx.device, non_blocking=True)
+        e0.record(stream)
+        ids = self.eng.generate(tok, self.generate)
+        e1.record(stream)
+        self.host_ids.copy_(ids, non_blocking=True)
+        self.launches += 1
+        return e0, e1
+
+    def measure(self, steps, warmup, sampler=None):
+        world = self.ctx.tp
+
+        def barrier():
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(warmup):
+            self.one_step()
+        torch.cuda.synchronize()
+        self.eng.check()
+        if sampler:
+            sampler.start()
+        barrier()
+        wall0 = time.perf_counter()
+        events = [self.one_step() for _ in range(steps)]
+        barrier()
+        wall_s = time.perf_counter() - wall0
+        clocks = sampler.stop() if sampler else None
+        self.eng.check()
+        kernel_ms = sum(a.elapsed_time(b) for a, b in events)
+        return kernel_ms, wall_s, clocks
+
+    def report(self, kernel_ms, wall_s, steps):
+        dev = self.ctx.device
+        world = self.ctx.tp
+        tokens = steps * self.generate * self.batch
+        # every rank computes every token: the job's tokens are counted once, the time is the slowest rank's
+        total_ms, _ = aggregate(kernel_ms, 0, world, dev)
+        e2e_ms, _ = aggregate(wall_s * 1e3, 0, world, dev)
+        bps = self.eng.bytes_per_step(self.prompt + self.generate // 2)
+        launch_s = kernel_ms / steps / 1e3
+        return {"value": tokens / (total_ms / 1e3), "ms_per_step": total_ms / steps,
+                "median_decode_step_us": total_ms / steps / self.generate * 1e3,
+                "bytes_per_decode_step_per_gpu": bps,
+                "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * self.batch,
+                        "d2h_bytes_per_step": 4 * self.batch * self.generate},
+                "roofline": roofline(bps * self.generate, launch_s, "mks::stage_kernel",
+                                     note="per GPU: this rank's weight shard, DeltaNet state and KV cache; at TP > 1 the step also "
+                                          "waits for the peers' partial sums")}
+
+
+def cfg3_cpu_rate(batch, n_layers=4, reps=2, vocab=None, fmt="bf16"):
+    """tok/s of the CPU decoder (oracle/qwen27b.py, the restated reference) for the 27B model, estimated from a
+    bounded sample: `n_layers` full-width layers (one pattern period: 3 DeltaNet + 1 attention) and the LM head are
+    timed and scaled to 64 layers.  The weights are bf16 (the decoder sees dequantised matrices either way)."""
+    from megakernels_b200.qwen27b.dims import FULL
+    from megakernels_b200.qwen27b.synth import SynthWeights
+    from oracle import qwen27b as O
+    torch.set_num_threads(os.cpu_count())
+    shape = FULL.with_(layers=n_layers)
+    W = SynthWeights(shape, layers=n_layers, seed=0, fmt=fmt, device="cpu")
+    st = O.State(shape, batch, 64, layers=n_layers)
+    tok = torch.arange(batch) * 977 % shape.vocab
+    body, head = [], []
+    for _ in range(reps + 1):
+        t0 = time.perf_counter()
+        h = O.step(shape, W, tok, st, layers=n_layers, lm_head=False)
+        t1 = time.perf_counter()
+        x = O.rms0(h, W["model.language_model.norm.weight"], shape.eps)
+        logits = x.to(torch.bfloat16).float() @ W["lm_head.weight"].float().t()
+        t2 = time.perf_counter()
+        tok = logits.argmax(-1)
+        body.append(t1 - t0)
+        head.append(t2 - t1)
+    step_s = statistics.mean(body[1:]) * (FULL.layers / n_layers) + statistics.mean(head[1:])
+    return batch / step_s, step_s, f"{n_layers} full-width layers (3 DeltaNet + 1 attention) and the LM head timed on a short context, " \
+                                   f"scaled to {FULL.layers} layers; bf16-valued weights in fp32 arithmetic, batch {batch}"
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    rates = []
+    sample = ""
+    for _ in range(max(1, min(args.steps, 3))):
+        rate, step_s, sample = cfg3_cpu_rate(args.batch, reps=1)
+        rates.append(rate)
+    value = statistics.mean(rates)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * args.batch * CFG3_GENERATE / value, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": cfg3_config(args.batch, args.layers, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ======================================================================================================
+# configurations 1 and 2: the 0.8B hybrid on the shape-specialised megakernels (one GPU)
+# ======================================================================================================
+def bytes_per_step(mk, batch, kv_bytes_per_pos=None):
     """Algorithmic bytes one decode step must move: every weight once, and per sequence the DeltaNet
     state read and written and the KV cache read at the average context of the generation."""
     body, head = mk.weight_bytes
-    kv = mk.kv_bytes_per_pos() * (PROMPT + GENERATE // 2)
+    per_pos = kv_bytes_per_pos if kv_bytes_per_pos is not None else mk.kv_bytes_per_pos()
+    kv = per_pos * (PROMPT + GENERATE // 2)
     return body + head + batch * (mk.state_bytes() + kv)
 
 
@@ -117,55 +305,9 @@ def cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode, reps=1):
     return rates
 
 
-def dist_env():
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    return rank, world, int(os.environ.get("LOCAL_RANK", rank))
-
-
-def aggregate(local_ms, local_tokens, world, device):
-    """(max time over ranks in ms, tokens summed over ranks).  Works on gloo/CPU tensors too."""
-    import torch.distributed as dist
-    if world == 1:
-        return local_ms, local_tokens
-    t = torch.tensor([local_ms], dtype=torch.float64, device=device)
-    n = torch.tensor([local_tokens], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dist.all_reduce(n, op=dist.ReduceOp.SUM)
-    return float(t), float(n)
-
-
-def workload_config(quant, batch, kv_dtype, vocab, layers):
-    """The `config` object both arms print: the same workload, named the same way."""
-    return {"workload": f"qwen3.5-0.8b hybrid ({layers} layers, hidden 1024, vocab {vocab}), "
-                        f"{quant} weights, batch {batch}, replicas only",
-            "batch": batch, "prompt_tokens": PROMPT, "decode_steps_per_bench_step": GENERATE, "kv_dtype": kv_dtype,
-            "l2": "weights streamed per decode step (0.65 GB int8) exceed the 126 MB L2; no flush needed"}
-
-
-def run_reference(args):
-    rank, world, _ = dist_env()
-    if rank != 0:
-        return
-    cfg, w, prompt = build_model("int8")
-    n_prompt, n_decode = 32, 16
-    rates = cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode, reps=args.warmup + args.steps)[args.warmup:]
-    value = statistics.mean(rates)
-    sample = f"{n_prompt}-token prompt then {n_decode} greedy decode steps per bench step, full depth and vocabulary"
-    print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * n_decode / value, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": dict(workload_config("int8", args.batch, "fp32", cfg.vocab, cfg.n_layers),
-                       note="the CPU decoder takes the sequences of a batch one after another: its tok/s does not depend on the batch"),
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
-        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
-
-
-def measure(mk, batch, prompts, args, world, device, sampler=None):
+def measure(mk, batch, prompts, args, spec=False):
     """Time `args.steps` generations of GENERATE tokens per sequence at `batch` sequences.  Returns
-    (kernel ms summed over the steps, wall seconds, launches, per-decode-step ns, clock record)."""
+    (kernel ms summed over the steps, wall seconds, launches, per-decode-step ns, last run's info)."""
     stream = torch.cuda.current_stream()
     if batch == 1:
         last = [mk.prefill(prompts[0])]           # the prompt goes through the kernel, one token per step
@@ -174,17 +316,17 @@ def measure(mk, batch, prompts, args, world, device, sampler=None):
             mk.run_batch([p[i: min(i + 512, PROMPT - 1)] for p in prompts[:batch]])
         last = [p[-1] for p in prompts[:batch]]
     snap = mk.snapshot()
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
+    info = {}
 
     def one_step(timing=False):
         mk.restore(snap)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        if batch == 1:
+        if spec:
+            got, _ = mk.run_spec(last[0], last[0], GENERATE)     # any first draft is valid; it costs at most its cycle
+            info["cycles"] = len(mk.last_cycles)
+            ids = [got]
+        elif batch == 1:
             ids = [mk.run(last, n_generate=GENERATE, timing=timing)]
         else:
             ids = mk.run_batch([[t] for t in last], n_generate=GENERATE, timing=timing)
@@ -193,46 +335,79 @@ def measure(mk, batch, prompts, args, world, device, sampler=None):
 
     for _ in range(args.warmup):
         ids, _, _ = one_step()
-    assert len(ids) == batch and all(len(x) == GENERATE for x in ids)
-    # ---- timed region: kernel time with inputs resident (CUDA events on the launching stream)
-    if sampler:
-        sampler.start()
-    barrier()
+    assert len(ids) == batch and all(len(x) >= GENERATE for x in ids)
+    torch.cuda.synchronize()
     launches0 = mk.launches
     wall0 = time.perf_counter()
     kernel_events, step_ns = [], []
     for _ in range(args.steps):
-        ids, e0, e1 = one_step(timing=True)
+        ids, e0, e1 = one_step(timing=not spec)
         kernel_events.append((e0, e1))
-        step_ns += mk.last_step_ns
-    barrier()
+        if not spec:
+            step_ns += mk.last_step_ns
+    torch.cuda.synchronize()
     wall_s = time.perf_counter() - wall0
-    clocks = sampler.stop() if sampler else None
     kernel_ms = [a.elapsed_time(b) for a, b in kernel_events]      # launch + readback of one generation
-    return sum(kernel_ms), wall_s, mk.launches - launches0, step_ns, clocks
+    return sum(kernel_ms), wall_s, mk.launches - launches0, step_ns, info
 
 
-def report(mk, batch, kernel_ms, wall_s, step_ns, args, world, device):
-    """Throughput, end-to-end throughput and roofline of one measured batch size."""
+def report(mk, batch, kernel_ms, wall_s, step_ns, args):
+    """Throughput, end-to-end throughput and roofline of one measured batch size of the 0.8B model."""
     tokens = args.steps * GENERATE * batch
-    total_ms, total_tokens = aggregate(kernel_ms, tokens, world, device)
-    e2e_ms, _ = aggregate(wall_s * 1e3, tokens, world, device)
-    peak, peak_kind = measured_peak_gbs()
     bps = bytes_per_step(mk, batch)
     launch_s = kernel_ms / args.steps / 1e3
-    achieved = bps * GENERATE / launch_s / 1e9
     traffic = NCU_DRAM_BYTES_PER_STEP.get(batch)
+    r = roofline(bps * GENERATE, launch_s, "mk::batch_kernel" if batch > 1 else "mk::decode_kernel",
+                 traffic=traffic * GENERATE if traffic else None)
+    if traffic:
+        r["traffic_note"] = (f"ncu capture at a {NCU_CONTEXT}-token context scaled by decode steps: the weight and state part of a "
+                             f"launch; the KV part of this {PROMPT}-token-context launch is not in it")
+    # the same fraction with the KV cache counted at bf16 (2 B per element), the size the benchmark definition gives it
+    bf16_kv = bytes_per_step(mk, batch, kv_bytes_per_pos=mk.kv_bytes_per_pos() * 2 // (4 if mk.kv_dtype == "fp32" else 2))
+    r["frac_kv_counted_as_bf16"] = bf16_kv * GENERATE / launch_s / 1e9 / r["peak"]
     return {
-        "value": total_tokens / (total_ms / 1e3), "ms_per_step": total_ms / args.steps,
-        "e2e": {"value": total_tokens / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * 8 + 4,
+        "value": tokens / (kernel_ms / 1e3), "unit": "tok/s", "ms_per_step": kernel_ms / args.steps,
+        "e2e": {"value": tokens / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * 8 + 4,
                 "d2h_bytes_per_step": 8 * GENERATE * (8 if batch > 1 else 1) + 32 + 4},
-        "median_decode_step_us": statistics.median(step_ns) / 1e3, "bytes_per_decode_step": bps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_8TBs": achieved / 8000.0,
-                     "traffic": traffic * GENERATE if traffic else None,
-                     "algorithmic_bytes_per_launch": bps * GENERATE,
-                     "kernel": "batch_kernel" if batch > 1 else "decode_kernel"},
+        "median_decode_step_us": statistics.median(step_ns) / 1e3 if step_ns else None, "bytes_per_decode_step": bps,
+        "roofline": r,
     }
+
+
+def measure_cfg2(args, device):
+    """int8 weights: batch 8, batch 1, and speculative cycles with the MTP draft head at batch 1."""
+    from megakernels_b200.engine import Megakernel
+    from megakernels_b200.synth import make_mtp_weights, make_prompt
+    cfg, w, prompt = build_model("int8")
+    prompts = [prompt] + [make_prompt(cfg, PROMPT, seed=1000 + j) for j in range(1, 8)]
+    mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant="int8", kv_dtype=args.kv_dtype, device=device, batch=8)
+    k8, w8, launches, s8, _ = measure(mk, 8, prompts, args)
+    out = {"workload": f"qwen3.5-0.8b hybrid ({cfg.n_layers} layers, hidden 1024, vocab {cfg.vocab}), int8 per-channel weights, "
+                       f"{PROMPT}-token prompt + {GENERATE} greedy steps per launch, kv {args.kv_dtype}",
+           "batch8": report(mk, 8, k8, w8, s8, args)}
+    mk.reset()
+    k1, w1, l1, s1, _ = measure(mk, 1, prompts, args)
+    out["batch1"] = report(mk, 1, k1, w1, s1, args)
+    launches += l1
+    del mk
+    torch.cuda.empty_cache()
+    # speculative cycles (draft head proposes, one T = 2 pass verifies): cost of a cycle beside the plain step
+    try:
+        mtp = make_mtp_weights(cfg, 0)
+        mk = Megakernel((cfg, w, mtp), max_seq=PROMPT + 2 * GENERATE + 64, quant="int8", kv_dtype=args.kv_dtype, device=device, mtp=True)
+        ks, ws, ls, _, info = measure(mk, 1, prompts, args, spec=True)
+        cycles = max(1, int(info.get("cycles", GENERATE)))
+        out["spec"] = {"ms_per_cycle": ks / args.steps / cycles, "tokens_per_cycle": GENERATE / cycles,
+                       "cycles_per_launch": cycles, "plain_step_ms": k1 / args.steps / GENERATE,
+                       "value": args.steps * GENERATE / (ks / 1e3), "unit": "tok/s",
+                       "note": "random weights: the draft is almost never accepted, so tokens/cycle is about 1; ms/cycle against the "
+                               "plain step is what the T = 2 pass and the draft head cost"}
+        launches += ls
+        del mk
+    except Exception as e:                                     # the leg is informative; it must not take the line down
+        out["spec"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    torch.cuda.empty_cache()
+    return out, launches, (cfg, w, prompt)
 
 
 def measure_cfg1(args, device):
@@ -244,102 +419,96 @@ def measure_cfg1(args, device):
     try:
         cfg, w, prompt = build_model("bf16")
         mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant="bf16", kv_dtype=args.kv_dtype, device=device)
-        kernel_ms, wall_s, _, step_ns, _ = measure(mk, 1, [prompt], args, 1, device)
-        r = report(mk, 1, kernel_ms, wall_s, step_ns, args, 1, device)
+        kernel_ms, wall_s, launches, step_ns, _ = measure(mk, 1, [prompt], args)
+        r = report(mk, 1, kernel_ms, wall_s, step_ns, args)
         r["roofline"]["traffic"] = None          # no ncu capture of the bf16 kernel is committed
-        return {"workload": "bf16 weights, batch 1, 32-token prompt + 128 greedy steps", "value": r["value"], "unit": "tok/s",
-                "ms_per_step": r["ms_per_step"], "median_decode_step_us": r["median_decode_step_us"],
-                "bytes_per_decode_step": r["bytes_per_decode_step"], "e2e": r["e2e"], "roofline": r["roofline"]}
+        r["roofline"].pop("traffic_note", None)
+        r["workload"] = "qwen3.5-0.8b hybrid, bf16 weights, batch 1, 32-token prompt + 128 greedy steps"
+        return r, launches
     finally:
         PROMPT, GENERATE = saved
 
 
 def main():
-    global PROMPT, GENERATE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--quant", default="int8", choices=["int8", "bf16"])
-    ap.add_argument("--kv-dtype", default="fp32", choices=["fp32", "bf16"])
-    ap.add_argument("--batch", type=int, default=8, help="sequences of the headline measurement (1..8; bf16 weights: 1)")
-    ap.add_argument("--no-batch1", action="store_true", help="skip the batch-1 measurement beside a batched headline")
+    ap.add_argument("--batch", type=int, default=8, help="sequences of the headline measurement (1..8)")
+    ap.add_argument("--kv-dtype", default="fp32", choices=["fp32", "bf16"], help="KV cache of the 0.8B riders")
+    ap.add_argument("--layers", type=int, default=64, help="truncate the 27B model (profiling only)")
+    ap.add_argument("--cfg3-prompt", type=int, default=CFG3_PROMPT, help="shrink the case (profiling only)")
+    ap.add_argument("--cfg3-generate", type=int, default=CFG3_GENERATE, help="shrink the case (profiling only)")
+    ap.add_argument("--no-riders", action="store_true", help="only the headline measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-cfg1", action="store_true", help="skip the bf16 configuration-1 measurement reported beside the headline")
-    ap.add_argument("--prompt", type=int, default=PROMPT, help="shrink the case (profiling only)")
-    ap.add_argument("--generate", type=int, default=GENERATE, help="shrink the case (profiling only)")
     args = ap.parse_args()
-    PROMPT, GENERATE = args.prompt, args.generate
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)
-    if args.quant != "int8":
-        args.batch = 1
 
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the decode megakernel has no CPU path")
+        raise SystemExit("bench.py needs a CUDA device: the decode megakernels have no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
+    from megakernels_b200.qwen27b import tp as TP
+    ctx = TP.init(device)
 
-    from megakernels_b200.engine import Megakernel
-    from megakernels_b200.synth import make_prompt
-    cfg, w, prompt = build_model(args.quant)
-    prompts = [prompt] + [make_prompt(cfg, PROMPT, seed=1000 + j) for j in range(1, args.batch)]
-    mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant=args.quant, kv_dtype=args.kv_dtype, device=device,
-                    batch=args.batch)
     sampler = ClockSampler(local) if rank == 0 else None
-    kernel_ms, wall_s, launches, step_ns, clocks = measure(mk, args.batch, prompts, args, world, device, sampler)
-    head = report(mk, args.batch, kernel_ms, wall_s, step_ns, args, world, device)
-    single = None
-    if args.batch > 1 and not args.no_batch1:
-        mk.reset()
-        k1, w1, l1, s1, _ = measure(mk, 1, prompts, args, world, device)
-        single = report(mk, 1, k1, w1, s1, args, world, device)
-        launches += l1
-
-    # configuration 1 of the benchmark definition beside it: bf16 weights, batch 1, 32-token prompt, 128 greedy steps
-    cfg1 = None
-    if world == 1 and args.quant == "int8" and not args.no_cfg1 and (PROMPT, GENERATE) == (512, 512):
-        del mk
+    main_run = Cfg3(args, ctx, args.batch)
+    kernel_ms, wall_s, clocks = main_run.measure(args.steps, args.warmup, sampler)
+    head = main_run.report(kernel_ms, wall_s, args.steps)
+    launches = args.steps
+    riders = {}
+    full_size = (args.layers, args.cfg3_prompt, args.cfg3_generate) == (64, CFG3_PROMPT, CFG3_GENERATE)
+    if world == 1 and not args.no_riders:
+        if args.batch > 1:
+            PK = main_run.PK
+            del main_run
+            torch.cuda.empty_cache()
+            one = Cfg3(args, ctx, 1, PK=PK)
+            k1, w1, _ = one.measure(2, 1)
+            r1 = one.report(k1, w1, 2)
+            riders["cfg3_batch1"] = {"value": r1["value"], "unit": "tok/s", "ms_per_step": r1["ms_per_step"],
+                                     "median_decode_step_us": r1["median_decode_step_us"], "e2e": r1["e2e"],
+                                     "roofline": r1["roofline"]}
+            launches += 2
+            del one, PK
+        else:
+            del main_run
         torch.cuda.empty_cache()
-        cfg1 = measure_cfg1(args, device)
+        if full_size:
+            cfg2, l2, model = measure_cfg2(args, device)
+            riders["cfg2_int8"] = cfg2
+            cfg1, l1 = measure_cfg1(args, device)
+            riders["cfg1_bf16"] = cfg1
+            launches += l2 + l1
 
     if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
         return
     out = {
         "metric": METRIC, "value": head["value"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": args.quant if args.quant == "int8" else "bf16", "data": "synthetic",
-        "config": dict(workload_config(args.quant, args.batch, args.kv_dtype, cfg.vocab, cfg.n_layers),
-                       median_decode_step_us=head["median_decode_step_us"],
-                       bytes_per_decode_step=head["bytes_per_decode_step"]),
-        "clocks": clocks,
-        "e2e": head["e2e"],
-        "gpu_launches": launches,
-        "roofline": head["roofline"],
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "mxfp4 weights, bf16 activations into fp32 accumulators", "data": "synthetic",
+        "config": cfg3_config(args.batch, args.layers, world),
+        "median_decode_step_us": head["median_decode_step_us"],
+        "bytes_per_decode_step_per_gpu": head["bytes_per_decode_step_per_gpu"],
+        "clocks": clocks, "e2e": head["e2e"], "gpu_launches": launches, "roofline": head["roofline"],
     }
-    if single:
-        out["batch1"] = {"value": single["value"], "unit": "tok/s", "ms_per_step": single["ms_per_step"],
-                         "median_decode_step_us": single["median_decode_step_us"],
-                         "bytes_per_decode_step": single["bytes_per_decode_step"], "e2e": single["e2e"],
-                         "roofline": single["roofline"]}
-    if cfg1:
-        out["cfg1_bf16"] = cfg1
-    if world == 1:
-        # the library's own read-bandwidth probes on this GPU, beside the driver-measured peak the fractions use
+    out.update(riders)
+    if world == 1 and not args.no_riders:
         from megakernels_b200 import bw
         out["roofline"]["bw_probe_gbs"] = {m: round(bw.measure(m, gib=2.0, reps=3, device=device), 1) for m in bw.MODES}
     if world == 1 and not args.no_cpu_baseline:
-        n_prompt, n_decode = 32, 48
-        rate = cpu_reference_rate(cfg, w, prompt, n_prompt, n_decode)[0]
+        rate, step_s, sample = cfg3_cpu_rate(args.batch, reps=1)
         out["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"{n_prompt}-token prompt then {n_decode} greedy steps of one sequence, "
-                                         "full depth, int8-dequantised weights in fp32"}
+                               "sample": sample, "estimated_s_per_decode_step": step_s}
     print(json.dumps(out))
     if world > 1:
         torch.distributed.destroy_process_group()

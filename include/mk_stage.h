@@ -230,10 +230,11 @@ typedef struct mk_stage_args {
     uint64_t ar_base;        /* all-reduce sequence number before this launch (the host carries it)*/
     int32_t grid;            /* CTAs, 0 = one per SM                                               */
     int32_t prof_cta;        /* the CTA whose timestamps go to `prof`; -1: every CTA, prof is u64[grid][n_stages][8] */
-    int64_t pf_bytes;        /* L2 prefetch distance ahead of the shared-memory ring, per CTA (0: off) */
+    uint64_t tokens_in;      /* optional i32[n_tokens_in][batch]: the inputs of the first n_tokens_in steps (a prompt);
+                                step s < n_tokens_in feeds tokens_in[s] instead of `tok` / the previous choice    */
     int32_t xs_bytes;        /* shared staging area the program needs (mk_stage_scratch_bytes; 0: the maximum);
                                 what it leaves of the SM's shared memory becomes ring slots (2..4 per warp) */
-    int32_t reserved2;
+    int32_t n_tokens_in;
 } mk_stage_args;
 
 /* Launch.  Asynchronous on `stream`. */

@@ -63,7 +63,8 @@ struct Args {
     int tp, rank;
     unsigned long long* mailbox[MKS_MAX_RANKS];
     unsigned long long ar_base;
-    long long pf_bytes;      // L2 prefetch distance ahead of the ring, per CTA (0: off)
+    const int* tokens_in;    // [n_tokens_in][M] forced inputs of the first steps, or null
+    int n_tokens_in;
     int prof_cta;            // the CTA whose timestamps go to `prof`
     int xs_bytes;            // input staging / mixer scratch area of this launch
     int ring_depth;          // ring slots per consumer warp

@@ -140,6 +140,7 @@ extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     if (a->batch < 1 || a->batch > MKS_MAX_BATCH) return sfail(MK_ERR_BADARG, "mk_stage_launch: batch %d out of [1, %d]", a->batch, MKS_MAX_BATCH);
     if (a->n_steps < 1) return sfail(MK_ERR_BADARG, "mk_stage_launch: n_steps %d", a->n_steps);
     if (!a->tok || !a->pos || !a->barrier || !a->status) return sfail(MK_ERR_BADARG, "mk_stage_launch: tok / pos / barrier / status missing");
+    if (a->n_tokens_in < 0 || (a->n_tokens_in > 0 && !a->tokens_in)) return sfail(MK_ERR_BADARG, "mk_stage_launch: n_tokens_in %d without tokens_in", a->n_tokens_in);
     if (a->barrier & 7) return sfail(MK_ERR_BADARG, "mk_stage_launch: barrier counter not 8-byte aligned");
     if (a->tp < 1 || a->tp > MKS_MAX_RANKS || a->rank < 0 || a->rank >= a->tp) return sfail(MK_ERR_BADARG, "mk_stage_launch: rank %d of %d", a->rank, a->tp);
     if (a->tp > 1)
@@ -170,7 +171,8 @@ extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     A.rank = a->rank;
     for (int r = 0; r < MKS_MAX_RANKS; r++) A.mailbox[r] = reinterpret_cast<unsigned long long*>(a->mailbox[r]);
     A.ar_base = a->ar_base;
-    A.pf_bytes = a->pf_bytes;
+    A.tokens_in = reinterpret_cast<const int*>(a->tokens_in);
+    A.n_tokens_in = a->tokens_in ? a->n_tokens_in : 0;
     A.prof_cta = a->prof_cta;
     // shared memory: the staging area the program needs (the caller computes it with mk_stage_scratch_bytes), the rest ring slots
     const int xs = a->xs_bytes > 0 ? (a->xs_bytes + 127) / 128 * 128 : XS_BYTES;

@@ -63,6 +63,11 @@ __device__ __noinline__ void embed_stage(Shared& S, Mut& mu, const mk_stage_desc
         if (tid_() < S.A.M) S.tok_s[tid_()] = max(0, min(vocab - 1, A.tok[tid_()]));
         consumer_sync();
     }
+    if (step < A.n_tokens_in) {
+        // a prompt position: the given token replaces the choice (which tokens_out still records)
+        if (tid_() < S.A.M) S.tok_s[tid_()] = max(0, min(vocab - 1, __ldg(A.tokens_in + (size_t)step * S.A.M + tid_())));
+        consumer_sync();
+    }
     const __nv_bfloat16* table = reinterpret_cast<const __nv_bfloat16*>(d.p[MKS_P_TABLE]);
     float* h = reinterpret_cast<float*>(d.p[MKS_P_H]);
     float* ssq = reinterpret_cast<float*>(d.p[MKS_P_H_SSQ]);

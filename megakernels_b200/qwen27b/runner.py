@@ -169,6 +169,17 @@ class Engine:
         self.rt.launch(n_steps, tokens_out=out)
         return out
 
+    def prefill(self, prompts):
+        """Feeds the prompts (M lists of equal length) position by position in ONE launch and returns the logits
+        after the last position: what the reference does with one `step` per position (`mk/reference.py:378-386`)."""
+        if len(prompts) != self.M or len({len(p) for p in prompts}) != 1 or not prompts[0]:
+            raise ValueError(f"prefill takes {self.M} prompts of one common, non-zero length")
+        toks = torch.tensor(prompts, dtype=torch.int32).t().contiguous().to(self.device)      # [L, M]
+        self.rt.tok[: self.M].copy_(toks[0])
+        self.rt.launch(toks.shape[0], tokens_in=toks)
+        self._prompt = toks                                  # alive until the launch has run
+        return self.logits
+
     def check(self):
         self.rt.check()
 

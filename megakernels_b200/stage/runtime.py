@@ -131,7 +131,7 @@ class PeerMailbox:
 class Runtime:
     """Uploads a program and launches steps.  Owns tok / pos / barrier / status words."""
 
-    def __init__(self, program, mailbox=None, tp=1, rank=0, spin_limit_ms=2000, pf_bytes=0):
+    def __init__(self, program, mailbox=None, tp=1, rank=0, spin_limit_ms=2000):
         if not torch.cuda.is_available():
             raise RuntimeError("the stage-machine megakernel needs a CUDA device; there is no CPU path")
         self.lib = D.lib()
@@ -154,7 +154,6 @@ class Runtime:
         self.ar_base = 0
         self.tp, self.rank, self.mailbox = tp, rank, mailbox
         self.spin_limit_ns = int(spin_limit_ms * 1e6)
-        self.pf_bytes = pf_bytes
         self.launches = 0
 
     def reset(self):
@@ -163,7 +162,7 @@ class Runtime:
             if t.dtype == torch.int32:
                 t.zero_()
 
-    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None, prof_cta=0):
+    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None, prof_cta=0, tokens_in=None):
         """`n_stages` runs only a prefix of the program (one step; for stage-by-stage checks in tests)."""
         full = n_stages is None
         n_stages = self.n_stages if full else n_stages
@@ -173,7 +172,9 @@ class Runtime:
                         tokens_out=tokens_out.data_ptr() if tokens_out is not None else 0, barrier=self.bar.data_ptr(),
                         barrier_base=self.bar_base, status=self.status.data_ptr(), spin_limit_ns=self.spin_limit_ns,
                         prof=prof.data_ptr() if prof is not None else 0, tp=self.tp, rank=self.rank, ar_base=self.ar_base,
-                        grid=self.grid, pf_bytes=self.pf_bytes, prof_cta=prof_cta, xs_bytes=self.xs_bytes)
+                        grid=self.grid, prof_cta=prof_cta, xs_bytes=self.xs_bytes,
+                        tokens_in=tokens_in.data_ptr() if tokens_in is not None else 0,
+                        n_tokens_in=tokens_in.shape[0] if tokens_in is not None else 0)
         if self.tp > 1:
             for r in range(self.tp):
                 a.mailbox[r] = self.mailbox.addresses[r]

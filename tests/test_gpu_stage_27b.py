@@ -110,6 +110,20 @@ def test_steps_track_the_oracle_and_generate_equals_stepping(model, M):
     assert torch.equal(gen_logits, eng.logits)
 
 
+def test_prefill_in_one_launch_equals_stepping(model):
+    W, PK = model
+    M = 3
+    prompts = [make_prompt(SMALL.vocab, 9, seed=20 + j) for j in range(M)]
+    a, b = Engine(PK, M, maxlen=64), Engine(PK, M, maxlen=64)
+    got = a.prefill(prompts).clone()
+    for t in range(9):
+        want = b.step(torch.tensor([p[t] for p in prompts], device="cuda"))
+    a.check()
+    assert torch.equal(got, want) and torch.equal(a.ssm, b.ssm) and a.pos[:M].tolist() == [9] * M
+    with pytest.raises(ValueError):
+        a.prefill(prompts[:2])
+
+
 def test_two_engines_share_one_set_of_packed_weights(model):
     W, PK = model
     a, b = Engine(PK, 2, maxlen=64), Engine(PK, 2, maxlen=64)
