@@ -451,7 +451,7 @@ __device__ __forceinline__ int xs_stride_bytes(int kc) { return ((kc * 2 + 127) 
 // What matters here is the number of dependent L2 round trips (about 0.7 us each on this part), not
 // bytes: the first batch of input loads, the norm weights and the sums of squares behind 1/rms are all
 // requested before anything is awaited; the values go to shared memory as bf16 and are rescaled there.
-constexpr int XB = 2;       // float4 groups a thread keeps in flight per batch
+constexpr int XB = 4;       // float4 groups a thread keeps in flight per batch
 
 __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d, int grp, int split) {
     const int kc = d.i[MKS_I_KC], fmt = d.i[MKS_I_FMT], pieces = d.i[MKS_I_PIECES], M = S.A.M;
@@ -465,7 +465,7 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     const int k4n = kc >> 2, total = M * k4n;
     int* red_i = reinterpret_cast<int*>(S.red);
     if (tid_() < MKS_MAX_BATCH) red_i[tid_()] = 0;
-    float4 xv[XB], wv[XB];
+    float4 xv[XB];
     auto request = [&](int base) {
 #pragma unroll
         for (int u = 0; u < XB; u++) {
@@ -473,7 +473,6 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
             if (idx < total) {
                 const int m = idx / k4n, k4 = idx - m * k4n;
                 xv[u] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * xstride) + k4);
-                if (norm) wv[u] = __ldg(reinterpret_cast<const float4*>(nw) + k4);
             }
         }
     };
@@ -522,9 +521,11 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
                 const int k4 = idx - m * k4n;
                 float v[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
                 if (norm) {
+                    // the norm weights are the same few KB for every sequence: after the first they come from L1
+                    const float4 wv = __ldg(reinterpret_cast<const float4*>(nw) + k4);
                     const float r = S.rstd[m] * in_scale;
-                    v[0] = v[0] * r * (noff + wv[u].x); v[1] = v[1] * r * (noff + wv[u].y);
-                    v[2] = v[2] * r * (noff + wv[u].z); v[3] = v[3] * r * (noff + wv[u].w);
+                    v[0] = v[0] * r * (noff + wv.x); v[1] = v[1] * r * (noff + wv.y);
+                    v[2] = v[2] * r * (noff + wv.z); v[3] = v[3] * r * (noff + wv.w);
                 }
                 if (pieces == 2) {
                     // fp32 copy, parked in the two columns that sequence m's pieces will occupy... of sequence pair slot m

@@ -283,6 +283,8 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
     const int esz = KVF32 ? 4 : 2;
     const int rec = QPK * (HD + 2);                            // floats of one chunk's partial record
     const int max_chunks = d.i[MKS_I_MAX_CHUNKS];
+    // this CTA's rows behind the partial records: [16 warps][QPK][128] sums of the P x V pieces
+    float* scratch = part + (size_t)S.A.M * NKV * max_chunks * rec + (size_t)cta_() * NCW * QPK * 128;
     // shared scratch
     float* q_s = reinterpret_cast<float*>(S.xs());             // [QPK][HD]
     float* kn_s = q_s + QPK * HD;                              // [HD] the new K row
@@ -353,42 +355,56 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
             }
         }
         prof_mark(S, 4);
-        // 2. scores: a warp takes every 16th position, four at a time; a lane 8 dims of every 256 of the K row
+        // 2. scores: a warp takes every 16th position, four of them per turn, a lane 8 dims of every 256 of the K row.
+        //    The four rows are requested before the first is used; the 4 x 8 (position, head) partial dots of a lane
+        //    are summed over the warp by a transposing butterfly (31 shuffles instead of 160) that leaves sum l in lane l.
 #pragma unroll 1
-        for (int i = warp_(); i < np; i += NCW) {
+        for (int i0 = warp_(); i0 < np; i0 += NCW * 4) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = 0.f;
 #pragma unroll 1
             for (int e = lane_() * 8; e < HD; e += 256) {
-                float kv[8];
-                if (i < ncached) {
-                    load8<KVF32>(kc + (size_t)row_s[i] * esz, e, kv);
-                } else {
+                float kv[4][8];
 #pragma unroll
-                    for (int x = 0; x < 8; x++) kv[x] = kn_s[e + x];
-                }
-                // all heads' partial dots first, then their warp sums side by side (independent shuffles overlap)
-                float dot[8];
+                for (int u = 0; u < 4; u++) {
+                    const int i = i0 + u * NCW;
+                    if (i < ncached) {
+                        load8<KVF32>(kc + (size_t)row_s[i] * esz, e, kv[u]);
+                    } else {
 #pragma unroll
-                for (int hq = 0; hq < 8; hq++) {
-                    dot[hq] = 0.f;
-                    if (hq < QPK) {
-                        const float* q = q_s + hq * HD + e;
-#pragma unroll
-                        for (int x = 0; x < 8; x++) dot[hq] = fmaf(q[x], kv[x], dot[hq]);
+                        for (int x = 0; x < 8; x++) kv[u][x] = i < np ? kn_s[e + x] : 0.f;     // the new row, or past the chunk
                     }
                 }
 #pragma unroll
-                for (int o = 16; o; o >>= 1)
+                for (int hq = 0; hq < 8; hq++) {
+                    if (hq < QPK) {
+                        const float4 qa = *reinterpret_cast<const float4*>(q_s + hq * HD + e);
+                        const float4 qb = *reinterpret_cast<const float4*>(q_s + hq * HD + e + 4);
 #pragma unroll
-                    for (int hq = 0; hq < 8; hq++)
-                        if (hq < QPK) dot[hq] += __shfl_xor_sync(0xffffffffu, dot[hq], o);
-                if (lane_() < QPK) {
-                    float mine = 0.f;
-#pragma unroll
-                    for (int hq = 0; hq < 8; hq++)
-                        if (hq == lane_()) mine = dot[hq];
-                    float* dst = sc_s + lane_() * CP + i;
-                    *dst = e < 256 ? mine * scale : *dst + mine * scale;      // head dims beyond 256 come in a second turn
+                        for (int u = 0; u < 4; u++) {
+                            float a = v[u * 8 + hq];
+                            a = fmaf(qa.x, kv[u][0], a); a = fmaf(qa.y, kv[u][1], a); a = fmaf(qa.z, kv[u][2], a); a = fmaf(qa.w, kv[u][3], a);
+                            a = fmaf(qb.x, kv[u][4], a); a = fmaf(qb.y, kv[u][5], a); a = fmaf(qb.z, kv[u][6], a); a = fmaf(qb.w, kv[u][7], a);
+                            v[u * 8 + hq] = a;
+                        }
+                    }
                 }
+            }
+#pragma unroll
+            for (int o = 16, n = 16; o; o >>= 1, n >>= 1) {
+                const bool up = (lane_() & o) != 0;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (j < n) {
+                        const float send = up ? v[j] : v[j + n], keep = up ? v[j + n] : v[j];
+                        v[j] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
+                }
+            }
+            {
+                const int u = lane_() >> 3, hq = lane_() & 7, i = i0 + u * NCW;
+                if (hq < QPK && i < np) sc_s[hq * CP + i] = v[0] * scale;
             }
         }
         consumer_sync();
@@ -414,38 +430,76 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
             }
         }
         consumer_sync();
-        // 4. P x V: warp w owns dims [16 w, 16 w + 16) of every 256; lane = (query head, group of 4 dims), so a
-        //    lane adds up its four outputs over all positions and nothing is reduced across lanes
+        // 4. P x V: warp = (128-dim piece of the head, residue class of the positions), lane = 4 dims; a lane keeps
+        //    its four outputs of every query head and asks for PB rows before it uses the first.  The warps of a piece
+        //    then leave their sums in this CTA's scratch rows and every thread adds a few outputs in warp order.
         float* prec = part + ((size_t)(m * NKV + kvh) * max_chunks + ch) * rec;
         {
-            const int hq = lane_() >> 2, e4 = (lane_() & 3) * 4;
+            constexpr int PB = KVF32 ? 4 : 8;
+            const int ndc = HD / 128, nres = NCW / ndc;
+            const int dc = warp_() % ndc, res = warp_() / ndc;
+            const int e0 = dc * 128 + lane_() * 4;
+            float acc[8][4];
+#pragma unroll
+            for (int hq = 0; hq < 8; hq++) acc[hq][0] = acc[hq][1] = acc[hq][2] = acc[hq][3] = 0.f;
 #pragma unroll 1
-            for (int dbase = 0; dbase < HD; dbase += 256) {
-                const int e0 = dbase + warp_() * 16 + e4;
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-                if (hq < QPK) {
-                    const float* pr = sc_s + hq * CP;
-#pragma unroll 8
-                    for (int i = 0; i < ncached; i++) {
+            for (int i0 = res; i0 < ncached; i0 += nres * PB) {
+                float vv[PB][4];
+#pragma unroll
+                for (int u = 0; u < PB; u++) {
+                    const int i = i0 + u * nres;
+                    vv[u][0] = vv[u][1] = vv[u][2] = vv[u][3] = 0.f;
+                    if (i < ncached) {
                         const uint8_t* row = vc + (size_t)row_s[i] * esz;
-                        float v0, v1, v2, v3;
                         if (KVF32) {
-                            const float4 qv = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + e0));
-                            v0 = qv.x; v1 = qv.y; v2 = qv.z; v3 = qv.w;
+                            const float4 q4 = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(row) + e0));
+                            vv[u][0] = q4.x; vv[u][1] = q4.y; vv[u][2] = q4.z; vv[u][3] = q4.w;
                         } else {
-                            const uint2 qv = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(row) + e0));
-                            v0 = bf_lo(qv.x); v1 = bf_hi(qv.x); v2 = bf_lo(qv.y); v3 = bf_hi(qv.y);
+                            const uint2 q2 = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(row) + e0));
+                            vv[u][0] = bf_lo(q2.x); vv[u][1] = bf_hi(q2.x); vv[u][2] = bf_lo(q2.y); vv[u][3] = bf_hi(q2.y);
                         }
-                        const float w = pr[i];
-                        a0 = fmaf(w, v0, a0); a1 = fmaf(w, v1, a1); a2 = fmaf(w, v2, a2); a3 = fmaf(w, v3, a3);
                     }
-                    if (has_new) {
-                        const float w = pr[np - 1];
-                        a0 = fmaf(w, vn_s[e0], a0); a1 = fmaf(w, vn_s[e0 + 1], a1);
-                        a2 = fmaf(w, vn_s[e0 + 2], a2); a3 = fmaf(w, vn_s[e0 + 3], a3);
-                    }
-                    __stcg(reinterpret_cast<float4*>(prec + hq * HD + e0), make_float4(a0, a1, a2, a3));
                 }
+#pragma unroll
+                for (int u = 0; u < PB; u++) {
+                    const int i = min(i0 + u * nres, ncached - 1);          // rows past the end were read as zeros
+#pragma unroll
+                    for (int hq = 0; hq < 8; hq++) {
+                        if (hq < QPK) {
+                            const float w = sc_s[hq * CP + i];
+                            acc[hq][0] = fmaf(w, vv[u][0], acc[hq][0]); acc[hq][1] = fmaf(w, vv[u][1], acc[hq][1]);
+                            acc[hq][2] = fmaf(w, vv[u][2], acc[hq][2]); acc[hq][3] = fmaf(w, vv[u][3], acc[hq][3]);
+                        }
+                    }
+                }
+            }
+            if (has_new && res == 0) {
+#pragma unroll
+                for (int hq = 0; hq < 8; hq++) {
+                    if (hq < QPK) {
+                        const float w = sc_s[hq * CP + np - 1];
+                        acc[hq][0] = fmaf(w, vn_s[e0], acc[hq][0]); acc[hq][1] = fmaf(w, vn_s[e0 + 1], acc[hq][1]);
+                        acc[hq][2] = fmaf(w, vn_s[e0 + 2], acc[hq][2]); acc[hq][3] = fmaf(w, vn_s[e0 + 3], acc[hq][3]);
+                    }
+                }
+            }
+            float* mine = scratch + ((size_t)warp_() * QPK) * 128 + lane_() * 4;
+#pragma unroll
+            for (int hq = 0; hq < 8; hq++)
+                if (hq < QPK) __stcg(reinterpret_cast<float4*>(mine + hq * 128), make_float4(acc[hq][0], acc[hq][1], acc[hq][2], acc[hq][3]));
+            fence_acq_rel_gpu();
+            consumer_sync();
+#pragma unroll 1
+            for (int idx = tid_(); idx < QPK * (HD / 4); idx += NCT) {
+                const int hq = idx / (HD / 4), dd = (idx - hq * (HD / 4)) * 4;
+                const float* src = scratch + ((size_t)(dd >> 7) * QPK + hq) * 128 + (dd & 127);    // warp (residue 0, piece dd / 128)
+                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                for (int r = 0; r < nres; r++) {
+                    const float4 t4 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * ndc * QPK * 128));
+                    o.x += t4.x; o.y += t4.y; o.z += t4.z; o.w += t4.w;
+                }
+                __stcg(reinterpret_cast<float4*>(prec + hq * HD + dd), o);
             }
         }
         if (tid_() < 2 * QPK) __stcg(prec + QPK * HD + tid_(), stat_s[tid_()]);
