@@ -33,7 +33,8 @@ enum {
     MKS_OP_GDN = 3,     /* Gated DeltaNet: causal conv1d, delta-rule state update, gated RMSNorm  */
     MKS_OP_ATTN = 4,    /* split-K flash-decode attention over a paged bf16/fp32 KV cache         */
     MKS_OP_ROUTE = 5,   /* top-k expert routing tables (CTA-local, identical in every CTA)        */
-    MKS_OP_VEC = 6      /* element-wise residual / sandwich-norm step over the hidden vector      */
+    MKS_OP_VEC = 6      /* out = (base + rms(a) w_a [+ rms(b) w_b]) * F_SCALE over the hidden vector: the residual /
+                           sandwich-norm steps of the 26B model (gemma4-26b-a4b-gfx942/mk/reference.py:296-307) */
 };
 
 /* flags */
@@ -88,7 +89,8 @@ enum {
     MKS_I_ACT,           /* MKS_ACT_* of E_GLU                                                     */
     MKS_I_K_TOTAL,       /* columns of the whole input vector (the mean of P_NORM divides by it)    */
     MKS_I_BLOCK_SCALES,  /* FP8: fp32 scales per 128 k inside each chunk (0: none)                 */
-    MKS_I_PIECES,        /* 1: input rounded to bf16 (the model dtype); 2: hi + lo fp16 pieces (fp32-exact inputs, M <= 4) */
+    MKS_I_PIECES,        /* 1: input rounded to bf16 (the model dtype); 2: hi + lo pieces, fp16 (bf16 for bf16 weights):
+                            inputs exact to 16+ bits, two MMA columns per sequence, M <= 4       */
     MKS_I_GEMV_END,
 
     /* EMBED */
@@ -126,7 +128,7 @@ enum {
                             1: softmax over all experts, top-k renormalised, times per_expert_scale  */
 
     /* VEC */
-    MKS_I_VEC_KIND = 0, MKS_I_VEC_N,
+    MKS_I_VEC_N = 0,     /* elements per sequence (a multiple of 16)                               */
 
     MKS_I_COUNT = 30
 };
@@ -136,7 +138,7 @@ enum {
     MKS_F_EPS = 0,
     MKS_F_NORM_OFF,      /* 1 for zero-centred norm weights (x * (1 + w)), 0 for plain ones        */
     MKS_F_SOFTCAP,       /* E_LOGITS: cap * tanh(y / cap) if > 0                                   */
-    MKS_F_SCALE,         /* EMBED: embedding scale (0: none); ATTN: score scale                    */
+    MKS_F_SCALE,         /* EMBED: embedding scale (0: none); ATTN: score scale; VEC: factor on the result (0: none) */
     MKS_F_IN_SCALE,      /* P_NORM: extra factor on the normed input (router of the 26B model)     */
     MKS_F_COUNT = 8
 };
@@ -189,7 +191,13 @@ enum {
     MKS_P_LOGITS = 0, MKS_P_EXPERT_SCALE,
 
     /* VEC */
-    MKS_P_V0 = 0, MKS_P_V1, MKS_P_V2, MKS_P_V3, MKS_P_V4, MKS_P_V5, MKS_P_V6, MKS_P_V7,
+    MKS_P_VEC_BASE = 0,  /* fp32 [M][n] added unchanged, or 0                                        */
+    MKS_P_VEC_A,         /* fp32 [M][n]: first normed term                                           */
+    MKS_P_VEC_A_SSQ,     /* its sums of squares per 16 elements [M][n / 16] (an E_STORE / E_RESID output) */
+    MKS_P_VEC_A_W,       /* its norm weight [n]                                                      */
+    MKS_P_VEC_B, MKS_P_VEC_B_SSQ, MKS_P_VEC_B_W,   /* optional second normed term (VEC_B = 0: none)   */
+    MKS_P_VEC_OUT,       /* fp32 [M][n] (may be VEC_BASE: in place)                                  */
+    MKS_P_VEC_OUT_SSQ,   /* sums of squares of the result per 16 elements, or 0                      */
 
     MKS_P_COUNT = 16
 };

@@ -551,6 +551,26 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     }
     if (fmt == MKS_FMT_BF16) {
         if (tid_() < 8) S.xinv[tid_()] = 1.f;
+        if (pieces == 2) {
+            // fp32-exact inputs for bf16 weights: x = hi + lo, both bf16 (16 significant bits), no scaling needed
+            consumer_sync();
+            float v[16];
+            int n = 0;
+#pragma unroll 1
+            for (int idx = tid_(); idx < M * kc && n < 16; idx += NCT, n++) {
+                const int m = idx / kc, k = idx - m * kc;
+                v[n] = *reinterpret_cast<const float*>(S.xs() + (size_t)(2 * m) * stride + (size_t)k * 4);
+            }
+            consumer_sync();
+            n = 0;
+#pragma unroll 1
+            for (int idx = tid_(); idx < M * kc && n < 16; idx += NCT, n++) {
+                const int m = idx / kc, k = idx - m * kc;
+                const __nv_bfloat16 hi = __float2bfloat16_rn(v[n]);
+                reinterpret_cast<__nv_bfloat16*>(S.xs() + (size_t)m * stride)[k] = hi;
+                reinterpret_cast<__nv_bfloat16*>(S.xs() + (size_t)(M + m) * stride)[k] = __float2bfloat16_rn(v[n] - __bfloat162float(hi));
+            }
+        }
         return;
     }
     consumer_sync();
@@ -853,9 +873,14 @@ __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc&
                     fence_acq_rel_gpu();
                     __syncwarp();
                     unsigned old = 0;
-                    if (lane_() == 0) old = atomicAdd(cnt + cidx, 1u);
+                    if (lane_() == 0) {
+                        old = atomicAdd(cnt + cidx, 1u);
+                        // the last arriver puts the counter back: the number of arrivals of a routed stage changes
+                        // from step to step, and nobody touches the counter again before the stage's barrier
+                        if (old + 1u == (unsigned)arrivals) cnt[cidx] = 0u;
+                    }
                     old = __shfl_sync(0xffffffffu, old, 0);
-                    finish = ((old + 1u) % (unsigned)arrivals) == 0u;
+                    finish = old + 1u == (unsigned)arrivals;
                     if (finish) {
                         fence_acq_rel_gpu();
                         acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
@@ -901,6 +926,20 @@ __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc&
                         if (m1 < S.A.M) {
                             if (ra < nvalid) __stcg(out + (size_t)m1 * ostride + ra, acc[1]);
                             if (rb < nvalid) __stcg(out + (size_t)m1 * ostride + rb, acc[3]);
+                        }
+                        float* ssq = reinterpret_cast<float*>(d.p[MKS_P_OUT_SSQ]);
+                        if (ssq) {                              // the sums of squares a later norm of this vector needs (whole tiles only)
+                            float q0 = acc[0] * acc[0] + acc[2] * acc[2], q1 = acc[1] * acc[1] + acc[3] * acc[3];
+#pragma unroll
+                            for (int o = 4; o < 32; o <<= 1) {
+                                q0 += __shfl_xor_sync(0xffffffffu, q0, o);
+                                q1 += __shfl_xor_sync(0xffffffffu, q1, o);
+                            }
+                            if (g == 0) {
+                                const int ntile = nvalid / 16;
+                                if (m0 < S.A.M) __stcg(ssq + (size_t)m0 * ntile + tile, q0);
+                                if (m1 < S.A.M) __stcg(ssq + (size_t)m1 * ntile + tile, q1);
+                            }
                         }
                     } else if (epi == MKS_E_RESID) {
                         const int ra = tile * 16 + g, rb = ra + 8;

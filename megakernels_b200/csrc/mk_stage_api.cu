@@ -40,7 +40,6 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
             if (fmt < MKS_FMT_BF16 || fmt > MKS_FMT_INT8) return sfail(MK_ERR_BADARG, "stage %d: weight format %d", s, fmt);
             if (pieces != 1 && pieces != 2) return sfail(MK_ERR_BADARG, "stage %d: pieces %d", s, pieces);
             if (pieces * batch > 8) return sfail(MK_ERR_BADARG, "stage %d: %d input pieces x %d sequences exceed the 8 MMA columns", s, pieces, batch);
-            if (pieces == 2 && fmt == MKS_FMT_BF16) return sfail(MK_ERR_BADARG, "stage %d: two-piece inputs need an fp16 weight path", s);
             if (kc < 128) return sfail(MK_ERR_BADARG, "stage %d: fewer than 128 columns per split", s);
             if (pieces == 2 && (long long)kc * batch > 8192) return sfail(MK_ERR_BADARG, "stage %d: two-piece inputs hold at most 8192 values per panel", s);
             if (kc < 1 || kc % steps_k(fmt)) return sfail(MK_ERR_BADARG, "stage %d: %d columns per split are not whole tile steps", s, kc);
@@ -77,7 +76,12 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
             if ((d.i[MKS_I_EXPERTS] != 128 && d.i[MKS_I_EXPERTS] != 256) || d.i[MKS_I_TOPK] < 1 || d.i[MKS_I_TOPK] > 8)
                 return sfail(MK_ERR_BADARG, "stage %d: %d experts, top %d", s, d.i[MKS_I_EXPERTS], d.i[MKS_I_TOPK]);
             if (batch * d.i[MKS_I_TOPK] + 1 > MAX_GROUPS) return sfail(MK_ERR_BADARG, "stage %d: too many routed groups", s);
-        } else if (d.op != MKS_OP_EMBED && d.op != MKS_OP_VEC) {
+        } else if (d.op == MKS_OP_VEC) {
+            if (d.i[MKS_I_VEC_N] < 16 || d.i[MKS_I_VEC_N] % 16) return sfail(MK_ERR_BADARG, "stage %d: vector of %d elements", s, d.i[MKS_I_VEC_N]);
+            if (!d.p[MKS_P_VEC_A] || !d.p[MKS_P_VEC_A_SSQ] || !d.p[MKS_P_VEC_A_W] || !d.p[MKS_P_VEC_OUT])
+                return sfail(MK_ERR_BADARG, "stage %d: vector step without its term, sums of squares, weight or output", s);
+            if (d.p[MKS_P_VEC_B] && (!d.p[MKS_P_VEC_B_SSQ] || !d.p[MKS_P_VEC_B_W])) return sfail(MK_ERR_BADARG, "stage %d: second term without sums of squares / weight", s);
+        } else if (d.op != MKS_OP_EMBED) {
             return sfail(MK_ERR_BADARG, "stage %d: unknown op %d", s, d.op);
         }
     }

@@ -646,6 +646,72 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
     consumer_sync();
 }
 
+// ---- element-wise residual / sandwich-norm step ------------------------------------------------------------------
+// out[m][i] = (base[m][i] + a[m][i] rstd_a[m] (off + w_a[i]) [+ b[m][i] rstd_b[m] (off + w_b[i])]) * scale, and the sums
+// of squares of the result per 16 elements.  rstd comes from the 16-element sums of squares the producing GEMV stage
+// left (every CTA adds them up itself, in a fixed order); a CTA then takes a slice of the 16-element groups.
+__device__ __noinline__ void vec_stage(Shared& S, Mut& mu, const mk_stage_desc& d) {
+    const int N = d.i[MKS_I_VEC_N], ng = N / 16, M = S.A.M;
+    const float* base = reinterpret_cast<const float*>(d.p[MKS_P_VEC_BASE]);
+    const float* a = reinterpret_cast<const float*>(d.p[MKS_P_VEC_A]);
+    const float* b = reinterpret_cast<const float*>(d.p[MKS_P_VEC_B]);
+    const float* wa = reinterpret_cast<const float*>(d.p[MKS_P_VEC_A_W]);
+    const float* wb = reinterpret_cast<const float*>(d.p[MKS_P_VEC_B_W]);
+    float* out = reinterpret_cast<float*>(d.p[MKS_P_VEC_OUT]);
+    float* out_ssq = reinterpret_cast<float*>(d.p[MKS_P_VEC_OUT_SSQ]);
+    const float eps = d.f[MKS_F_EPS], off = d.f[MKS_F_NORM_OFF];
+    const float scale = d.f[MKS_F_SCALE] != 0.f ? d.f[MKS_F_SCALE] : 1.f;
+    // warps 0..M-1: rstd of a; warps 8..8+M-1: rstd of b
+    {
+        const int m = warp_() & 7;
+        const bool second = warp_() >= 8;
+        const float* ssq = reinterpret_cast<const float*>(d.p[second ? MKS_P_VEC_B_SSQ : MKS_P_VEC_A_SSQ]);
+        if (m < M && (!second || b)) {
+            float s = 0.f;
+#pragma unroll 4
+            for (int j = lane_(); j < ng; j += 32) s += ldcg_f(ssq + (size_t)m * ng + j);
+            s = warp_sum(s);
+            if (lane_() == 0) S.red[(second ? 8 : 0) + m] = rsqrtf(s / (float)N + eps);
+        }
+    }
+    consumer_sync();
+    const int g0 = ng * cta_() / grid_(), g1 = ng * (cta_() + 1) / grid_();
+    const int n = g1 - g0;
+#pragma unroll 1
+    for (int idx0 = 0; idx0 < n * M * 4; idx0 += NCT) {
+        // four threads share a 16-element group: each takes a float4 and the group's sum of squares is shuffled together
+        // (every lane of a warp takes part in the shuffles; the ones past the end carry zeros)
+        const int idx = idx0 + tid_();
+        const bool live = idx < n * M * 4;
+        const int q4 = idx & 3, gi = live ? idx >> 2 : 0;
+        const int m = gi / n, grp = g0 + gi - m * n;
+        const size_t o = (size_t)m * N + grp * 16 + q4 * 4;
+        float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) {
+            const float4 av = __ldcg(reinterpret_cast<const float4*>(a + o));
+            const float4 aw = __ldg(reinterpret_cast<const float4*>(wa + grp * 16 + q4 * 4));
+            const float ra = S.red[m];
+            r = make_float4(av.x * ra * (off + aw.x), av.y * ra * (off + aw.y), av.z * ra * (off + aw.z), av.w * ra * (off + aw.w));
+            if (b) {
+                const float4 bv = __ldcg(reinterpret_cast<const float4*>(b + o));
+                const float4 bw = __ldg(reinterpret_cast<const float4*>(wb + grp * 16 + q4 * 4));
+                const float rb = S.red[8 + m];
+                r.x += bv.x * rb * (off + bw.x); r.y += bv.y * rb * (off + bw.y); r.z += bv.z * rb * (off + bw.z); r.w += bv.w * rb * (off + bw.w);
+            }
+            if (base) {
+                const float4 hv = __ldcg(reinterpret_cast<const float4*>(base + o));
+                r.x += hv.x; r.y += hv.y; r.z += hv.z; r.w += hv.w;
+            }
+            r.x *= scale; r.y *= scale; r.z *= scale; r.w *= scale;
+            __stcg(reinterpret_cast<float4*>(out + o), r);
+        }
+        float q = r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
+        q += __shfl_xor_sync(0xffffffffu, q, 1);
+        q += __shfl_xor_sync(0xffffffffu, q, 2);
+        if (live && out_ssq && q4 == 0) __stcg(out_ssq + (size_t)m * ng + grp, q);
+    }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constant__ Args A_in) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -723,6 +789,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
                     else attn_stage<false>(S, mu, d);
                     break;
                 case MKS_OP_ROUTE: route_stage(S, mu, d); break;
+                case MKS_OP_VEC: vec_stage(S, mu, d); break;
                 default: break;
             }
             if (d.op != MKS_OP_GEMV) prof_mark(S, 2);

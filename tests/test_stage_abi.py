@@ -104,7 +104,6 @@ def test_a_well_formed_program_validates(lib_built):
     (dict(X=0), b"missing"),
     (dict(PROLOGUE=1), b"norm prologue"),
     (dict(EPILOGUE=3), b"key buffer"),
-    (dict(PIECES=2), b"fp16 weight path"),
     (dict(PIECES=3), b"pieces"),
     (dict(GROUPS=0), b"groups"),
     (dict(KC=32768, UNIT_STEPS=2048), b"staging area"),
