@@ -73,10 +73,9 @@ enum {
     MK_G_XL,            /* u64 [tokens, hidden]        residual stream, (epoch<<32)|fp32 words */
     MK_G_PROJL,         /* u64 [tokens, in_rows_max]   input-projection output                 */
     MK_G_MIXL,          /* u64 [tokens, 2048]          mixer (DeltaNet / attention) output     */
-    MK_G_ACTL,          /* u64 [tokens, intermediate]  MLP activation                          */
+    MK_G_ACTL,          /* u64 [tokens, intermediate]  MLP activation: mk_launch_batch only (0: never batched) */
     MK_G_LML,           /* u64 [tokens, grid, 2]       per-CTA LM-head winners                 */
     MK_G_ATTN_PART,     /* u64 [tokens, kv_heads, MK_MAX_SPLITS, MK_PART_STRIDE] split partials, flag-in-data words */
-    MK_G_ATTN_FLAG,     /* u32 [tokens, kv_heads, MK_MAX_SPLITS]                               */
     MK_G_BLOCK_TABLE,   /* int32 [max_seq / MK_KV_BLOCK]: logical KV block -> physical block   */
     MK_G_STATUS,        /* int32 [4]: [0] error code of the first wait that ran out, [1] where */
     MK_G_MTP_FC, MK_G_MTP_FC_SCALE, MK_G_MTP_NORM_E, MK_G_MTP_NORM_H, MK_G_MTP_NORM,

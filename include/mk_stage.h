@@ -189,6 +189,8 @@ enum {
 
     /* ROUTE */
     MKS_P_LOGITS = 0, MKS_P_EXPERT_SCALE,
+    MKS_P_ROUTE_OUT,     /* optional i32 [M][top k]: the chosen expert ids in rank order (for tests and traces;
+                            the reference's debug_route, gemma4-26b-a4b-gfx942/tests/test_decode.py)  */
 
     /* VEC */
     MKS_P_VEC_BASE = 0,  /* fp32 [M][n] added unchanged, or 0                                        */

@@ -22,7 +22,7 @@ LAYER_FIELDS = ["w_in", "w_out", "w_gu", "w_down", "s_in", "s_out", "s_gu", "s_d
                 "conv_w", "A_log", "dt_bias", "gdn_norm", "conv_hist", "state", "state_bak", "q_norm", "k_norm",
                 "k_cache", "v_cache", "kind", "conv_hist_b", "w_out_rows", "w_down_rows"]
 GLOBAL_FIELDS = ["embed", "embed_scale", "lm_head", "lm_scale", "final_norm", "rope_cos", "rope_sin", "xl", "projl",
-                 "mixl", "actl", "lml", "attn_part", "attn_flag", "block_table", "status", "mtp_fc", "mtp_fc_scale",
+                 "mixl", "actl", "lml", "attn_part", "block_table", "status", "mtp_fc", "mtp_fc_scale",
                  "mtp_norm_e", "mtp_norm_h", "mtp_norm", "draft_head", "draft_scale", "draft_ids", "xml", "partl"]
 QUERIES = ["SMEM_BYTES", "N_THREADS", "CONV_RING", "KV_BLOCK", "MAX_SPLITS", "PART_STRIDE", "OPS_PER_LAYER",
            "PROF_MAX_OPS", "PROF_FIELDS", "SPEC_T", "MAX_LAYERS", "LAYER_FIELDS", "GLOBAL_FIELDS", "SLOT_BYTES",

@@ -153,7 +153,6 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     p.actl = as_ptr<unsigned long long*>(g[MK_G_ACTL]);
     p.lml = as_ptr<unsigned long long*>(g[MK_G_LML]);
     p.attn_part = as_ptr<unsigned long long*>(g[MK_G_ATTN_PART]);
-    p.attn_flag = as_ptr<unsigned*>(g[MK_G_ATTN_FLAG]);
     p.block_table = as_ptr<const int*>(g[MK_G_BLOCK_TABLE]);
     p.status = as_ptr<int*>(g[MK_G_STATUS]);
     p.mtp_fc = as_ptr<const uint8_t*>(g[MK_G_MTP_FC]);
@@ -174,9 +173,11 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     if (bad16(p.embed) || bad16(p.lm_head)) return fail(MK_ERR_BADARG, "embedding / LM head null or not 16-byte aligned");
     if (q8 && (!p.embed_scale || !p.lm_scale)) return fail(MK_ERR_BADARG, "int8 embedding / LM head without scales");
     if (!p.final_norm || !p.rope_cos || !p.rope_sin) return fail(MK_ERR_BADARG, "final norm / RoPE tables missing");
-    if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.actl) || bad16(p.lml) || bad16(p.partl))
+    if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.lml) || bad16(p.partl))
         return fail(MK_ERR_BADARG, "activation word buffers null or not 16-byte aligned");
-    if (!p.attn_part || !p.attn_flag || !p.block_table || !p.status) return fail(MK_ERR_BADARG, "attention scratch / block table / status missing");
+    // the MLP activation words are a hand-off of the batched kernel only: mk_launch_batch refuses an engine without them
+    if (p.actl != nullptr && bad16(p.actl)) return fail(MK_ERR_BADARG, "MLP activation words not 16-byte aligned");
+    if (!p.attn_part || !p.block_table || !p.status) return fail(MK_ERR_BADARG, "attention scratch / block table / status missing");
     e->params_set = true;
     return MK_OK;
 }
@@ -389,6 +390,7 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
         return fail(MK_ERR_BADARG, "mk_launch_batch: batch %d, but the engine's buffers were sized for %d sequence(s) (mk_model_desc.max_batch)",
                     a->batch, e->desc.max_batch > 1 ? e->desc.max_batch : 1);
     if (a->n_steps < 1 || !a->forced || !a->tokens_out || !a->out_info) return fail(MK_ERR_BADARG, "mk_launch_batch: need n_steps >= 1, a token list, tokens_out and out_info");
+    if (!e->host.actl) return fail(MK_ERR_BADARG, "mk_launch_batch: the engine was given no MLP activation words (MK_G_ACTL)");
     if ((int64_t)a->batch * (e->desc.max_seq / KV_BLOCK) > MAX_BLOCKS)
         return fail(MK_ERR_BADARG, "mk_launch_batch: %d sequences of %d positions need more than %d KV pages", a->batch, e->desc.max_seq, MAX_BLOCKS);
     int min_forced = 1 << 30, last_pos = 0;

@@ -94,7 +94,6 @@ struct Params {
     unsigned long long* actl;
     unsigned long long* lml;
     unsigned long long* attn_part;
-    unsigned* attn_flag;
     const int* block_table;
     int* status;
     const uint8_t* mtp_fc;

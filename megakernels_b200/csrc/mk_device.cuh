@@ -132,13 +132,6 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 __device__ __forceinline__ float bf_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
-// Byte i of `w` holds q + 128.  Splicing it into the mantissa of 2^23 gives the float 2^23 + byte;
-// subtracting 2^23 + 128 leaves q exactly.
-template <int I>
-__device__ __forceinline__ float deq_u8(uint32_t w) {
-    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540 + I)) - 8388736.0f;
-}
-
 // Order-preserving float -> uint, so that an unsigned compare orders scores; the low word holds
 // ~index so that equal scores resolve to the smallest index.
 __device__ __forceinline__ uint32_t ordered_bits(float s) {

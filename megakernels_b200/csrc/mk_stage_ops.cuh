@@ -622,6 +622,8 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
         if (lane_() < topk) {
             const int id = S.r_ids[m * 8 + lane_()];
             S.r_w[m * 8 + lane_()] = myw / wsum * (kind == 1 && pes ? pes[id] : 1.f);
+            int* ids_out = reinterpret_cast<int*>(d.p[MKS_P_ROUTE_OUT]);
+            if (ids_out && cta_() == 0) ids_out[m * topk + lane_()] = id;
         }
     }
     consumer_sync();

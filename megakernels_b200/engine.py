@@ -206,7 +206,6 @@ class Megakernel:
                                                    _lib.query("SPEC_T") * self.grid * cfg.hidden)]
         max_splits, part_stride = _lib.query("MAX_SPLITS"), _lib.query("PART_STRIDE")
         self.attn_part = zeros(T * cfg.n_kv_heads * max_splits * part_stride, dtype=torch.int64)
-        self.attn_flag = zeros(cfg.n_kv_heads * max_splits, dtype=torch.int32)
         self.block_table = torch.arange(batch * n_blocks, device=device, dtype=torch.int32)   # [sequence][page]
         self.status = zeros(4, dtype=torch.int32)
 
@@ -219,8 +218,9 @@ class Megakernel:
         g = dict.fromkeys(_lib.GLOBAL_FIELDS, 0)
         g.update(embed=embed_ptr, embed_scale=embed_scale, lm_head=lm_ptr, lm_scale=lm_scale,
                  final_norm=f32(self.final_norm), rope_cos=keep(cos), rope_sin=keep(sin),
-                 xl=keep(self.ll[0]), projl=keep(self.ll[1]), mixl=keep(self.ll[2]), actl=keep(self.ll[3]),
-                 lml=keep(self.ll[4]), attn_part=keep(self.attn_part), attn_flag=keep(self.attn_flag),
+                 xl=keep(self.ll[0]), projl=keep(self.ll[1]), mixl=keep(self.ll[2]), actl=keep(self.ll[3]) if quant == "int8" else 0,      # only batched launches (int8 engines) hand activations over in words
+                
+                 lml=keep(self.ll[4]), attn_part=keep(self.attn_part),
                  block_table=keep(self.block_table), status=keep(self.status))
         g["xml"] = keep(self.ll[5])
         g["partl"] = keep(self.ll[6])
@@ -318,7 +318,6 @@ class Megakernel:
             t.zero_()
         self._mode = None              # "single" or "batch": the two kinds of launch keep separate conv histories
         self.bpos = [0] * self.batch   # position of every sequence; `pos` is that of sequence 0
-        self.attn_flag.zero_()
         self.attn_part.zero_()
         self.status.zero_()
         self.epoch = 1   # the buffers are zero, so epoch 0 never looks ready
@@ -332,70 +331,90 @@ class Megakernel:
         self.block_table.copy_(t)
 
     # ------------------------------------------------------------------------------------------
+    # One place builds the launch record, submits it and settles the host-side bookkeeping that every kind of
+    # single-sequence launch shares (status, epoch); the public methods differ in what they ask for and in how
+    # they read the result.
+    def _submit(self, n_steps, fields, buffers, timing):
+        """Launch `n_steps` steps (or cycles).  `fields`: LaunchArgs members by name; `buffers`: name -> device tensor
+        or None, passed by address under the same name.  Returns the launch's info words as a list (reading them
+        waits for the kernel)."""
+        dev = self.device
+        info = torch.zeros(8, dtype=torch.int32, device=dev)
+        stamps = torch.zeros(n_steps + 1, dtype=torch.int64, device=dev) if timing else None
+        args = dict(n_steps=n_steps, start_pos=self.pos, epoch_base=self.epoch, grid=self.grid, pf_bytes=self.pf_bytes,
+                    spin_limit_ns=self.spin_limit_ns, out_info=info.data_ptr(), step_ts=stamps.data_ptr() if timing else 0)
+        args.update(fields)
+        args.update({name: (t.data_ptr() if t is not None else 0) for name, t in buffers.items()})
+        record = _lib.LaunchArgs(**args)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(self.lib.mk_launch(self._h, ctypes.byref(record), ctypes.c_void_p(stream)))
+        self.launches += 1
+        words = info.tolist()
+        if int(self.status[0]) != 0:                       # a device-side wait ran out: raises with the wait site
+            where = ctypes.c_int32()
+            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
+        self.epoch = words[1] & 0xFFFFFFFF
+        if self.epoch > 0xFFFF0000:
+            raise RuntimeError("epoch counter exhausted; call reset()")
+        if timing:
+            n_run = words[5] if fields.get("spec") else words[0]
+            t = stamps[: n_run + 1].cpu()
+            self.last_step_ns = (t[1:] - t[:-1]).tolist()
+        return words
+
+    @staticmethod
+    def _sampling(temperature, seed, stop_ids, device):
+        """The LaunchArgs members that describe how a token is chosen and which ids end a launch."""
+        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=device)
+        return dict(seed=seed & 0xFFFFFFFF, inv_temperature=(1.0 / temperature) if temperature > 0 else 0.0,
+                    n_stop=len(stop_ids)), stops
+
     @torch.no_grad()
     def run(self, tokens, n_generate=1, temperature=0.0, seed=0, stop_ids=(), return_logits=False, prof=None,
             prof_step=0, timing=False, all_logits=False, track_mtp=False, return_resid=False):
-        """Feed `tokens`, then let the model continue for up to `n_generate` predicted tokens.
+        """Feed `tokens`, then continue with up to `n_generate` tokens of the model's own choosing, in one launch.
 
-        One kernel launch, exactly as the reference's `run` (`qwen_mk/engine.py:198-250`): prompt
-        tokens are fed one per step, each predicted token is fed back on the GPU; a predicted stop
-        id ends the launch and is reported but not fed.  Returns the predicted ids, plus their
-        logits with `return_logits`, or the logits of every fed token with `all_logits`.
+        The contract is the reference's (`qwen_mk/engine.py:198-250`): the given tokens enter one per step; from the
+        last of them on, every step's choice is fed to the next step on the GPU; choosing a stop id ends the launch,
+        and that id is returned without having been fed.  Result: the chosen ids; with `return_logits` also their
+        logits, with `all_logits` the logits behind every fed token instead.
         """
-        tokens = [int(t) for t in tokens]
-        if not tokens:
+        given = [int(t) for t in tokens]
+        if not given:
             raise ValueError("need at least one input token")
         if n_generate < 1:
             raise ValueError("n_generate must be >= 1")
         self._enter_mode("single")
-        n_forced = len(tokens)
-        n_steps = n_forced + n_generate - 1
+        n_given = len(given)
+        n_steps = n_given - 1 + n_generate
         if self.pos + n_steps > self.max_seq:
             raise ValueError(f"sequence would exceed max_seq={self.max_seq}")
-        dev = self.device
-        forced = torch.tensor(tokens, dtype=torch.int32).pin_memory().to(dev, non_blocking=True)
-        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=dev)
-        out = torch.zeros(n_steps, dtype=torch.int64, device=dev)
-        info = torch.zeros(8, dtype=torch.int32, device=dev)
-        ts = torch.zeros(n_steps + 1, dtype=torch.int64, device=dev) if timing else None
-        lm_from = 0 if all_logits else n_forced - 1
-        logits = torch.empty(n_steps, self.cfg.vocab, device=dev) if return_logits or all_logits else None
-        resid = torch.empty(n_steps, self.cfg.hidden, device=dev) if (track_mtp or return_resid) else None
-        ptr = lambda t: t.data_ptr() if t is not None else 0
-        a = _lib.LaunchArgs(forced=forced.data_ptr(), n_forced=n_forced, n_steps=n_steps, lm_from=lm_from,
-                            start_pos=self.pos, epoch_base=self.epoch, seed=seed & 0xFFFFFFFF,
-                            inv_temperature=1.0 / temperature if temperature > 0 else 0.0, n_stop=len(stop_ids),
-                            stop_ids=stops.data_ptr(), tokens_out=out.data_ptr(), logits_out=ptr(logits),
-                            resid_out=ptr(resid), step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof),
-                            prof_step=prof_step, grid=self.grid, pf_bytes=self.pf_bytes,
-                            spin_limit_ns=self.spin_limit_ns)
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        _lib.check(self.lib.mk_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
-        self.launches += 1
-        done, epoch, _ = info[:3].tolist()          # synchronises with the launch
-        if int(self.status[0]) != 0:
-            where = ctypes.c_int32()
-            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
-        track_mtp = track_mtp and self.mtp is not None
-        if track_mtp and done:
-            fed = (tokens + (0xFFFFFFFF - (out[n_forced - 1: done - 1] & 0xFFFFFFFF)).tolist())[:done]
-            self.mtp_fed(self.pos, mtp_mod.rmsnorm(resid[:done], self.final_norm, self.cfg.eps), fed)
-        elif done:
-            self.mtp_h = None
-        self.pos += done
-        self.epoch = epoch & 0xFFFFFFFF
-        if self.epoch > 0xFFFF0000:
-            raise RuntimeError("epoch counter exhausted; call reset()")
-        if timing:
-            t = ts[: done + 1].cpu()
-            self.last_step_ns = (t[1:] - t[:-1]).tolist()
-        self.last_resid = resid[:done] if resid is not None else None
-        ids = (0xFFFFFFFF - (out[n_forced - 1: done] & 0xFFFFFFFF)).tolist()
+        dev, cfg = self.device, self.cfg
+        want_hidden = track_mtp or return_resid
+        how, stops = self._sampling(temperature, seed, stop_ids, dev)
+        bufs = dict(forced=torch.tensor(given, dtype=torch.int32).pin_memory().to(dev, non_blocking=True),
+                    stop_ids=stops, tokens_out=torch.zeros(n_steps, dtype=torch.int64, device=dev),
+                    logits_out=torch.empty(n_steps, cfg.vocab, device=dev) if (return_logits or all_logits) else None,
+                    resid_out=torch.empty(n_steps, cfg.hidden, device=dev) if want_hidden else None, prof=prof)
+        first_choice = 0 if all_logits else n_given - 1            # the first step whose LM head runs
+        words = self._submit(n_steps, dict(how, n_forced=n_given, lm_from=first_choice, prof_step=prof_step), bufs, timing)
+        ran = words[0]
+        # tokens_out holds keys (ordered score << 32 | ~id): the low word, complemented, is the id
+        chosen = (0xFFFFFFFF - (bufs["tokens_out"][n_given - 1: ran] & 0xFFFFFFFF)).tolist()
+        hidden = bufs["resid_out"][:ran] if want_hidden else None
+        if ran:
+            if track_mtp and self.mtp is not None:
+                entered = (given + chosen)[:ran]                   # what positions pos .. pos + ran - 1 were fed
+                self.mtp_fed(self.pos, mtp_mod.rmsnorm(hidden, self.final_norm, cfg.eps), entered)
+            else:
+                self.mtp_h = None                                  # the draft head's cache no longer follows the sequence
+        self.pos += ran
+        self.last_resid = hidden
         if all_logits:
-            return ids, logits[:done]
+            return chosen, bufs["logits_out"][:ran]
         if return_logits:
-            return ids, logits[n_forced - 1: done]
-        return ids
+            return chosen, bufs["logits_out"][n_given - 1: ran]
+        return chosen
 
     # ------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -488,31 +507,37 @@ class Megakernel:
                            device=self.device)
 
     def prefill(self, tokens, chunk=512):
-        """Feed all but the last token; returns the last one (`qwen_mk/engine.py:296-301`)."""
-        tokens = list(tokens)
-        for i in range(0, len(tokens) - 1, chunk):
-            self.run(tokens[i: min(i + chunk, len(tokens) - 1)], track_mtp=True)
-        return tokens[-1]
+        """Take a prompt in: everything but its last token goes through the kernel (in launches of `chunk` steps,
+        keeping the draft head's cache in step); the last token is handed back for the caller to feed with the
+        first generation launch, as the reference's `prefill` does (`qwen_mk/engine.py:296-301`)."""
+        *body, tail = list(tokens)
+        for lo in range(0, len(body), chunk):
+            self.run(body[lo: lo + chunk], track_mtp=True)
+        return tail
 
-    # ---- draft-head cache for tokens fed outside speculative cycles (`qwen_mk/engine.py:178-196`)
-    # The entry at position i is built from (h_i, x_{i+1}), so it can only be written once the token
-    # after i is known.  Speculative cycles maintain it in the kernel; for prompt tokens it is
-    # computed on the host side in one batch.
+    # ---- the draft head's KV cache outside speculative cycles -------------------------------------------------
+    # Entry i of that cache is computed from the model's final hidden state at position i AND the token that
+    # entered position i + 1 (`qwen_mk/mtp.py:55-82`), so it trails the sequence by one token.  `mtp_h` holds
+    # the one entry that is still waiting for its successor: (position, its hidden state), or None.
     def mtp_fed(self, start, hidden, tokens):
-        """Positions start .. start+n-1 were fed `tokens` and produced final hidden states `hidden`."""
-        if self.mtp is None or not len(tokens):
+        """`tokens` entered positions start, start + 1, ... and left the final hidden states `hidden` (one row per
+        token).  Completes the waiting entry with tokens[0], writes the entries that are now complete, and leaves
+        the last position waiting."""
+        n = len(tokens)
+        if self.mtp is None or n == 0:
             return
-        tok = torch.as_tensor(tokens, device=self.device)
-        self._mtp_close(start, tok[0])
-        if len(tok) > 1:
-            self.mtp.fill_kv(hidden[:-1], tok[1:], start)
-        self.mtp_h = (start + len(tok) - 1, hidden[-1:])
+        ids = torch.as_tensor(tokens, device=self.device)
+        self._mtp_close(start, ids[0])
+        if n > 1:
+            self.mtp.fill_kv(hidden[: n - 1], ids[1:], start)
+        self.mtp_h = (start + n - 1, hidden[n - 1: n])
 
     def _mtp_close(self, pos, token):
-        """Token `token` is going to position `pos`: finish the entry for pos - 1 if it is pending."""
-        if self.mtp_h is not None and self.mtp_h[0] == pos - 1:
-            self.mtp.fill_kv(self.mtp_h[1], torch.as_tensor([token], device=self.device), pos - 1)
-        self.mtp_h = None
+        """`token` is about to enter position `pos`.  If the waiting entry is the one just before, it is complete
+        now; any other waiting entry belongs to a sequence that has moved on and is dropped."""
+        waiting, self.mtp_h = self.mtp_h, None
+        if waiting is not None and waiting[0] + 1 == pos:
+            self.mtp.fill_kv(waiting[1], torch.as_tensor([token], device=self.device), waiting[0])
 
     def _write_mtp_kv(self, pos, k, v):
         bt = self.block_table.long()
@@ -523,78 +548,56 @@ class Megakernel:
     @torch.no_grad()
     def run_spec(self, token, draft, n_generate, temperature=0.0, seed=0, stop_ids=(), timing=False,
                  return_logits=False, prof=None, prof_step=0):
-        """Speculative decoding: `token` is pending at self.pos and `draft` guesses the one after.
+        """Speculative decoding in one launch: up to `n_generate` cycles, each a single pass over the weights that
+        takes the pending `token` (at `self.pos`) together with a guess `draft` for its successor.
 
-        One launch of up to `n_generate` cycles, each verifying the pending token plus the draft in a
-        single pass over the weights.  Returns (ids, next_draft): the emitted ids, at most `n_generate`
-        and ending early with a stop id, exactly as `run([token], n_generate)` would produce them; the
-        state has absorbed all but the last id, which is the next pending token, and `next_draft` is the
-        draft head's guess for the token after it.  Any `draft` is correct: a wrong one only costs its
-        cycle.  `self.last_cycles` lists (tokens emitted, draft) per cycle.  Same contract as the
-        reference's `run_spec` (`qwen_mk/engine.py:252-294`).
+        Returns `(ids, next_draft)`.  `ids` are exactly the ids `run([token], n_generate)` would return (at most
+        `n_generate`, cut after a stop id); the state has taken in all of them but the last, which is the new pending
+        token, and `next_draft` is the draft head's guess for what follows it.  A wrong `draft` is never an error: it
+        costs the cycle it was offered in.  `self.last_cycles` lists (ids emitted, draft offered) per cycle.  The
+        contract of the reference's `run_spec` (`qwen_mk/engine.py:252-294`).
         """
         if self.mtp is None:
             raise RuntimeError("construct the engine with mtp=True for speculative decoding")
         self._enter_mode("single")
-        n_cycles = min(n_generate, MAX_STEPS_PER_LAUNCH)
-        if self.pos + 2 * n_cycles + 1 > self.max_seq:
+        cycles = min(n_generate, MAX_STEPS_PER_LAUNCH)
+        if self.pos + 2 * cycles + 1 > self.max_seq:
             raise ValueError(f"sequence would exceed max_seq={self.max_seq}")
         self._mtp_close(self.pos, token)
         dev = self.device
-        stops = torch.tensor(list(stop_ids) or [-1], dtype=torch.int32, device=dev)
-        out = torch.zeros(n_generate, dtype=torch.int32, device=dev)
-        cycles = torch.zeros(2 * n_cycles, dtype=torch.int32, device=dev)
-        info = torch.zeros(8, dtype=torch.int32, device=dev)
-        ts = torch.zeros(n_cycles + 1, dtype=torch.int64, device=dev) if timing else None
-        logits = torch.empty(n_cycles, 2, self.cfg.vocab, device=dev) if return_logits else None
-        ptr = lambda t: t.data_ptr() if t is not None else 0
-        a = _lib.LaunchArgs(forced=0, n_forced=0, n_steps=n_cycles, lm_from=0, start_pos=self.pos, epoch_base=self.epoch,
-                            seed=seed & 0xFFFFFFFF, inv_temperature=1.0 / temperature if temperature > 0 else 0.0,
-                            n_stop=len(stop_ids), stop_ids=stops.data_ptr(), tokens_out=0, logits_out=ptr(logits),
-                            step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof), prof_step=prof_step,
-                            grid=self.grid, pf_bytes=self.pf_bytes, spin_limit_ns=self.spin_limit_ns, spec=1,
-                            first_tok=int(token), first_draft=int(draft), limit=n_generate,
-                            spec_out=out.data_ptr(), cycle_out=cycles.data_ptr())
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        _lib.check(self.lib.mk_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
-        self.launches += 1
-        emitted, epoch, pos, pending, next_draft, n_run = info[:6].tolist()
-        if int(self.status[0]) != 0:
-            where = ctypes.c_int32()
-            _lib.check(self.lib.mk_status(self._h, ctypes.byref(where)))
-        self.pos = pos
-        self.epoch = epoch & 0xFFFFFFFF
-        if self.epoch > 0xFFFF0000:
-            raise RuntimeError("epoch counter exhausted; call reset()")
-        self.last_cycles = cycles[: 2 * n_run].view(-1, 2).tolist()
-        if timing:
-            t = ts[: n_run + 1].cpu()
-            self.last_step_ns = (t[1:] - t[:-1]).tolist()
-        ids = out[:emitted].tolist()
+        how, stops = self._sampling(temperature, seed, stop_ids, dev)
+        bufs = dict(stop_ids=stops, spec_out=torch.zeros(n_generate, dtype=torch.int32, device=dev),
+                    cycle_out=torch.zeros(2 * cycles, dtype=torch.int32, device=dev),
+                    logits_out=torch.empty(cycles, 2, self.cfg.vocab, device=dev) if return_logits else None, prof=prof)
+        words = self._submit(cycles, dict(how, forced=0, n_forced=0, lm_from=0, tokens_out=0, spec=1, first_tok=int(token),
+                                          first_draft=int(draft), limit=n_generate, prof_step=prof_step), bufs, timing)
+        emitted, _, self.pos, pending, next_draft, cycles_run = words[:6]
+        self.last_cycles = bufs["cycle_out"][: 2 * cycles_run].view(-1, 2).tolist()
+        ids = bufs["spec_out"][:emitted].tolist()
         assert ids[-1] == pending
         if return_logits:
-            self.last_logits = logits[:n_run]
+            self.last_logits = bufs["logits_out"][:cycles_run]
         return ids, next_draft
 
     def generate(self, prompt_ids, max_new_tokens=256, temperature=0.0, seed=0, stop_ids=(), chunk=16, spec=False):
-        """Yield generated ids (`qwen_mk/engine.py:307-327`).  The state ends exactly after the last
-        fed token, so a conversation can continue by passing the next prompt."""
-        last = self.prefill(prompt_ids)
-        produced = 0
-        draft = last  # any guess is valid for the first cycle; the draft head proposes every later one
-        while produced < max_new_tokens:
-            n = min(chunk, max_new_tokens - produced, MAX_STEPS_PER_LAUNCH)
+        """Generator over the ids the model produces after `prompt_ids` (`qwen_mk/engine.py:307-327`).  The engine's
+        state stops right behind the last token it was fed, and `self.pending` keeps the one produced id that has not
+        been fed yet, so a conversation continues by passing the next prompt."""
+        pending = self.prefill(prompt_ids)
+        guess = pending            # the first cycle has no draft yet: whatever is offered can only cost that cycle
+        left = max_new_tokens
+        while left > 0:
+            budget = min(chunk, left, MAX_STEPS_PER_LAUNCH)
             if spec:
-                ids, draft = self.run_spec(last, draft, n, temperature=temperature, seed=seed, stop_ids=stop_ids)
+                batch, guess = self.run_spec(pending, guess, budget, temperature=temperature, seed=seed, stop_ids=stop_ids)
             else:
-                ids = self.run([last], n_generate=n, temperature=temperature, seed=seed, stop_ids=stop_ids)
-            for t in ids:
-                yield t
-                produced += 1
-            if ids and ids[-1] in stop_ids:
+                batch = self.run([pending], n_generate=budget, temperature=temperature, seed=seed, stop_ids=stop_ids)
+            yield from batch
+            left -= len(batch)
+            if not batch or batch[-1] in stop_ids:
                 return
-            last = ids[-1]
-        self.pending = last
+            pending = batch[-1]
+        self.pending = pending
 
     # ---- state access in the oracle's layouts (for tests, snapshots and state import) -----------
     def deltanet_state(self, i, seq=0):

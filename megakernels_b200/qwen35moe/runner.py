@@ -61,6 +61,7 @@ class Engine:
         self.keys = z(M, grid, dtype=torch.int64)
         rw = -(-(s.experts + 1) // 16) * 16
         self.router = z(M, rw)                                     # router logits | shared-expert gate logit
+        self.route_ids = z(max(self.layers, 1), M, s.topk, dtype=torch.int32)      # every layer's chosen experts, rank order
         gmax = D.query("MAX_GROUPS")
         self.act = z(gmax, M, s.fi)                                # experts' activations, one slab per routed group
         cos, sin = rope_tables(s.theta, self.maxlen, dev)
@@ -129,7 +130,8 @@ class Engine:
             w, meta = PK.mats[(i, "router")]
             pr.gemv("router", w, meta, self.h, self.router, x_stride=H, out_stride=rw, n_valid=s.experts + 1, pieces=pc(meta), **norm_post)
             pr.add(D.desc(D.MKS_OP_ROUTE, D.MKS_FLAG_NO_BARRIER,
-                          i=dict(EXPERTS=s.experts, TOPK=s.topk, LOGIT_STRIDE=rw, ROUTE_KIND=0), p=dict(LOGITS=self.router.data_ptr())))
+                          i=dict(EXPERTS=s.experts, TOPK=s.topk, LOGIT_STRIDE=rw, ROUTE_KIND=0),
+                          p=dict(LOGITS=self.router.data_ptr(), ROUTE_OUT=self.route_ids[i].data_ptr())))
             w, meta = PK.mats[(i, "ex_gu")]
             ws, _ = PK.mats[(i, "sh_gu")]
             pr.gemv("ex_gu", w, meta, self.h, self.act, x_stride=H, out_stride=s.fi, out_gstride=M * s.fi, epilogue=D.MKS_E_GLU,

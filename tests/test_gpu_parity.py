@@ -191,7 +191,7 @@ def test_errors(tiny, lib_built):
         engine(qwen35_08b(n_layers=2).with_(hidden=2048), w)
 
 
-FULL = sorted(p for p in glob.glob(os.path.join(GOLDEN, "*.json")))
+FULL = sorted(p for p in glob.glob(os.path.join(GOLDEN, "*.json")) if "n_layers" in json.load(open(p)))     # the 0.8B model's fixtures
 
 
 @pytest.mark.parametrize("path", FULL, ids=[os.path.basename(p)[:-5] for p in FULL])
