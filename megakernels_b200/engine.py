@@ -45,9 +45,11 @@ def rope_tables(cfg, max_seq, device):
 
 class Megakernel:
     def __init__(self, model, max_seq=8192, device="cuda", pf_bytes=PF_BYTES, quant="bf16", mtp=False,
-                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None, batch=1):
+                 draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None, batch=1, pack_device=None):
         """`mtp` loads the multi-token-prediction head for speculative decoding (`run_spec`); its drafts
-        come from the `draft_vocab` most frequent tokens listed in `draft_ids` (0: the whole vocabulary)."""
+        come from the `draft_vocab` most frequent tokens listed in `draft_ids` (0: the whole vocabulary).
+        `pack_device="cpu"` quantises and tiles the weights on the host and uploads the result (a handful of copies
+        instead of a few hundred small GPU kernels; slower for large models)."""
         if quant not in ("bf16", "int8"):
             raise ValueError(f"quant must be 'bf16' or 'int8', got {quant!r}")
         if kv_dtype not in ("bf16", "fp32"):
@@ -91,8 +93,10 @@ class Megakernel:
         self.grid = torch.cuda.get_device_properties(device).multi_processor_count
         self._keep = []   # every tensor whose address the kernel holds
 
+        pack_dev = torch.device(pack_device) if pack_device is not None else None
+
         def keep(t):
-            t = t.contiguous()
+            t = t.to(device).contiguous()
             self._keep.append(t)
             return t.data_ptr()
 
@@ -105,7 +109,7 @@ class Megakernel:
 
         def plain(t):
             """A weight matrix in the kernel's element format, row-major: (tensor, scales or None)."""
-            t = t.to(device)
+            t = t.to(pack_dev if pack_dev is not None else device)
             if q8:
                 q, s = quantize_int8_rows(t)
                 return (q.to(torch.int16) - 128).to(torch.int8), s      # signed two's complement

@@ -53,14 +53,16 @@ def pick_splits(K, step_k, prefer, limit=3072):
 class Packed:
     """All kernel-side weights of TP rank `rank` (of `tp`) on one device."""
 
-    def __init__(self, W, device="cuda", layers=None, tp=1, rank=0):
+    def __init__(self, W, device="cuda", layers=None, tp=1, rank=0, pack_device=None):
+        """`pack_device="cpu"` tiles the weights on the host and uploads the result."""
         s = W.shape
         self.shape, self.tp, self.rank, self.fmt = s, tp, rank, W.fmt
         self.layers = layers if layers is not None else W.layers
         d = self.d = Dims(s, tp)
         self.device = torch.device(device)
         self.mats, self.small, self.keep = {}, {}, []
-        dev = self.device
+        final = self.device
+        dev = torch.device(pack_device) if pack_device is not None else final      # where the packing arithmetic runs
 
         def lin(i, name):
             """(codes-or-bf16 [N, K], scales or None) of one linear layer, on the device."""
@@ -88,6 +90,7 @@ class Packed:
             fmt = tile.FMT_MXFP4 if self.fmt == "mxfp4" else tile.FMT_BF16
             S = pick_splits(w.shape[1], tile.STEP_K[fmt], prefer_kc)
             t, meta = tile.pack_matrix(fmt, S, w, scales=sc, row_order=row_order)
+            t = t.to(final)
             self.mats[(i, name)] = (t, meta)
             self.keep.append(t)
 
@@ -135,14 +138,15 @@ class Packed:
                     t = torch.cat(parts)
                 elif n in ("linear_attn.A_log", "linear_attn.dt_bias"):
                     t = t[rows_of_heads(s.nvh, 1, tp, rank)]
-                t = t.contiguous()
+                t = t.contiguous().to(final)
                 self.small[(i, n)] = t
                 self.keep.append(t)
         lm = W["lm_head.weight"].to(dev)[rank * d.vocab: (rank + 1) * d.vocab]
         t, meta = tile.pack_matrix(tile.FMT_BF16, pick_splits(s.hidden, tile.STEP_K[tile.FMT_BF16], LM_KC), lm.contiguous())
+        t = t.to(final)
         self.lm_head = (t, meta)
-        self.embed = W["model.language_model.embed_tokens.weight"].to(dev).contiguous()
-        self.final_norm = W["model.language_model.norm.weight"].to(dev).float().contiguous()
+        self.embed = W["model.language_model.embed_tokens.weight"].to(final).contiguous()
+        self.final_norm = W["model.language_model.norm.weight"].to(final).float().contiguous()
         self.keep += [t, self.embed, self.final_norm]
 
     def weight_bytes(self):
