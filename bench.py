@@ -117,11 +117,11 @@ def roofline(bytes_per_launch, launch_s, kernel, traffic=None, **extra):
 # ======================================================================================================
 # configuration 3: the 27B MXFP4 hybrid on the stage-machine megakernel, TP 1/2/4/8
 # ======================================================================================================
-def cfg3_config(batch, layers, tp):
+def cfg3_config(batch, layers, tp, prompt=CFG3_PROMPT, generate=CFG3_GENERATE, vocab=0):
     """The `config` object both arms print: the same workload, named the same way."""
-    return {"workload": f"27B dense hybrid ({layers} layers, hidden 5120, FFN 17408, vocab 248320), MXFP4 weights + bf16 LM head, "
+    return {"workload": f"27B dense hybrid ({layers} layers, hidden 5120, FFN 17408, vocab {vocab or 248320}), MXFP4 weights + bf16 LM head, "
                         f"batch {batch}, tensor parallel over {tp} GPU(s)",
-            "batch": batch, "prompt_tokens": CFG3_PROMPT, "decode_steps_per_bench_step": CFG3_GENERATE, "kv_dtype": "bf16",
+            "batch": batch, "prompt_tokens": prompt, "decode_steps_per_bench_step": generate, "kv_dtype": "bf16",
             "parallelism": f"tp{tp}",
             "l2": "weights streamed per decode step (15.9 GB at TP 1) exceed the 126 MB L2; no flush needed"}
 
@@ -136,6 +136,8 @@ class Cfg3:
         self.ctx, self.batch, self.layers = ctx, batch, args.layers
         self.prompt, self.generate = args.cfg3_prompt, args.cfg3_generate
         shape = FULL.with_(layers=args.layers) if args.layers != FULL.layers else FULL
+        if args.vocab:
+            shape = shape.with_(vocab=args.vocab)
         if PK is None:
             # drawn on the GPU: 27 G normals on the host would take minutes; every rank draws the same values
             W = SynthWeights(shape, layers=args.layers, seed=0, device=ctx.device, draw_device=ctx.device, keep_dequant=False)
@@ -438,6 +440,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="sequences of the headline measurement (1..8)")
     ap.add_argument("--kv-dtype", default="fp32", choices=["fp32", "bf16"], help="KV cache of the 0.8B riders")
     ap.add_argument("--layers", type=int, default=64, help="truncate the 27B model (profiling only)")
+    ap.add_argument("--vocab", type=int, default=0, help="cut the 27B model's vocabulary (profiling only)")
     ap.add_argument("--cfg3-prompt", type=int, default=CFG3_PROMPT, help="shrink the case (profiling only)")
     ap.add_argument("--cfg3-generate", type=int, default=CFG3_GENERATE, help="shrink the case (profiling only)")
     ap.add_argument("--no-riders", action="store_true", help="only the headline measurement")
@@ -464,7 +467,7 @@ def main():
     head = main_run.report(kernel_ms, wall_s, args.steps)
     launches = args.steps
     riders = {}
-    full_size = (args.layers, args.cfg3_prompt, args.cfg3_generate) == (64, CFG3_PROMPT, CFG3_GENERATE)
+    full_size = (args.layers, args.cfg3_prompt, args.cfg3_generate, args.vocab) == (64, CFG3_PROMPT, CFG3_GENERATE, 0)
     if world == 1 and not args.no_riders:
         if args.batch > 1:
             PK = main_run.PK
@@ -496,7 +499,7 @@ def main():
         "metric": METRIC, "value": head["value"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "mxfp4 weights, bf16 activations into fp32 accumulators", "data": "synthetic",
-        "config": cfg3_config(args.batch, args.layers, world),
+        "config": cfg3_config(args.batch, args.layers, world, args.cfg3_prompt, args.cfg3_generate, args.vocab),
         "median_decode_step_us": head["median_decode_step_us"],
         "bytes_per_decode_step_per_gpu": head["bytes_per_decode_step_per_gpu"],
         "clocks": clocks, "e2e": head["e2e"], "gpu_launches": launches, "roofline": head["roofline"],

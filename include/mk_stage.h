@@ -128,7 +128,7 @@ enum {
                             1: softmax over all experts, top-k renormalised, times per_expert_scale  */
 
     /* VEC */
-    MKS_I_VEC_N = 0,     /* elements per sequence (a multiple of 16)                               */
+    MKS_I_VEC_N = 0,     /* elements per sequence (a multiple of 16; 0: an empty stage, its barrier only) */
 
     MKS_I_COUNT = 30
 };
@@ -265,6 +265,12 @@ int mk_stage_count(const mk_stage_desc* program, int n_stages, int64_t* barriers
 enum { MKS_Q_SMEM_BYTES = 0, MKS_Q_N_THREADS, MKS_Q_SLOT_BYTES, MKS_Q_XS_BYTES, MKS_Q_DESC_BYTES, MKS_Q_MAX_GROUPS,
        MKS_Q_MAILBOX_BYTES, MKS_Q_ATTN_MAX_CHUNK };
 int64_t mk_stage_query(int what);
+
+/* What a stage boundary costs on this GPU apart from any work.  mode 0: the kernel's grid barrier (one CTA per SM;
+ * `stores` global stores per thread before each barrier), mode 1: a flag round trip between two CTAs.  Runs
+ * `iters` iterations on the default stream, synchronously; *ns_per_iter receives the average.  The counterpart of
+ * the reference's barrier microbenchmark (qwen3.5-0.8b/bench/barrier.cu:27-59). */
+int mk_sync_probe(int device, int mode, int iters, int stores, int64_t* ns_per_iter);
 
 /* Peer-visible device memory for the tensor-parallel mailboxes: allocate on this process's device,
  * export a handle (64 bytes) another process on the same node opens.  The counterpart of the

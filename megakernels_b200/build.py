@@ -21,7 +21,8 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC"]
 
 
-def stale():
+def stale(lib=None):
+    LIB = lib if lib is not None else globals()["LIB"]
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
@@ -29,15 +30,20 @@ def stale():
     return any(os.path.getmtime(os.path.join(csrc, f)) > t for f in SOURCES + HEADERS)
 
 
-def build(force=False, verbose=False):
-    """Compile if the library is missing or older than its sources.  Returns the library path."""
-    if not force and not stale():
+CHAOS_LIB = os.path.join(HERE, "libmk_b200_chaos.so")
+
+
+def build(force=False, verbose=False, lib=None, defines=None):
+    """Compile if the library is missing or older than its sources.  Returns the library path.  `lib` / `defines`
+    override the output file and the extra -D flags (default: MK_B200_LIBNAME / MK_B200_DEFINES)."""
+    LIB = lib if lib is not None else globals()["LIB"]
+    if not force and not stale(LIB):
         return LIB
     nvcc = os.environ.get("NVCC", "nvcc")
     csrc = os.path.join(HERE, "csrc")
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    defines = shlex.split(os.environ.get("MK_B200_DEFINES", ""))
+    defines = shlex.split(os.environ.get("MK_B200_DEFINES", "")) if defines is None else list(defines)
     # one object per translation unit, compiled side by side, then one link
     jobs = []
     for src in SOURCES:
@@ -64,5 +70,13 @@ def build(force=False, verbose=False):
     return LIB
 
 
+def build_chaos(force=False):
+    """The race-detection build (-DMK_CHAOS: pseudo-random pauses before publishes), beside the normal library."""
+    return build(force=force, lib=CHAOS_LIB, defines=["-DMK_CHAOS"])
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--chaos" in sys.argv:
+        print(build_chaos(force="--force" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

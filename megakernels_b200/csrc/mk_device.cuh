@@ -10,6 +10,23 @@ typedef unsigned long long u64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// ---- race-detection build ------------------------------------------------------------------------
+// With -DMK_CHAOS every publish (a flag-in-data word, a counter increment, a barrier arrival, a ring-slot release)
+// is preceded, for about one call in eight, by a pseudo-random pause of up to four microseconds.  The results
+// of a correct protocol do not depend on when a publish happens, so a test requires the bits of this build's
+// outputs to equal those of the normal build.  What the reference's `chaos` sleeps do for its stage flags
+// (`common/mkcore/dev.py:394-416`).
+#ifdef MK_CHAOS
+__device__ __forceinline__ void chaos_delay() {
+    unsigned t;
+    asm volatile("mov.u32 %0, %%clock;" : "=r"(t));
+    const unsigned h = (t ^ (threadIdx.x * 2654435761u) ^ (blockIdx.x * 40503u)) * 2246822519u;
+    if ((h >> 29) == 0u) __nanosleep((h >> 8) & 4095u);
+}
+#else
+__device__ __forceinline__ void chaos_delay() {}
+#endif
+
 // ---- mbarrier + bulk copy ----------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
@@ -18,6 +35,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    chaos_delay();
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
@@ -78,10 +96,12 @@ __device__ __forceinline__ bool consumer_any(bool pred) {
 
 // ---- flag-in-data words: (epoch << 32) | fp32 bits ---------------------------------------------
 __device__ __forceinline__ void ll_store(u64* p, uint32_t epoch, float v) {
+    chaos_delay();
     const u64 w = ((u64)epoch << 32) | __float_as_uint(v);
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ void ll_store_bits(u64* p, uint32_t epoch, uint32_t bits) {
+    chaos_delay();
     const u64 w = ((u64)epoch << 32) | bits;
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }

@@ -171,6 +171,7 @@ __device__ __forceinline__ u64 ld_relaxed_sys_u64(const unsigned long long* p) {
     return v;
 }
 __device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, u64 v) {
+    chaos_delay();
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
@@ -178,6 +179,7 @@ __device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, u64 v)
 // The arrival is a release (everything this CTA wrote before the preceding CTA barrier is visible to
 // whoever observes the count), the poll an acquire; no sequentially-consistent fence is needed.
 __device__ __forceinline__ void red_release_add_u64(unsigned long long* p, unsigned long long v) {
+    chaos_delay();
     asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
@@ -874,6 +876,7 @@ __device__ __noinline__ void gemv_stage(Shared& S, Mut& mu, const mk_stage_desc&
                     __syncwarp();
                     unsigned old = 0;
                     if (lane_() == 0) {
+                        chaos_delay();
                         old = atomicAdd(cnt + cidx, 1u);
                         // the last arriver puts the counter back: the number of arrivals of a routed stage changes
                         // from step to step, and nobody touches the counter again before the stage's barrier

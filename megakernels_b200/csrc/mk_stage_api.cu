@@ -77,6 +77,7 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
                 return sfail(MK_ERR_BADARG, "stage %d: %d experts, top %d", s, d.i[MKS_I_EXPERTS], d.i[MKS_I_TOPK]);
             if (batch * d.i[MKS_I_TOPK] + 1 > MAX_GROUPS) return sfail(MK_ERR_BADARG, "stage %d: too many routed groups", s);
         } else if (d.op == MKS_OP_VEC) {
+            if (d.i[MKS_I_VEC_N] == 0) continue;              // an empty stage: its barrier only
             if (d.i[MKS_I_VEC_N] < 16 || d.i[MKS_I_VEC_N] % 16) return sfail(MK_ERR_BADARG, "stage %d: vector of %d elements", s, d.i[MKS_I_VEC_N]);
             if (!d.p[MKS_P_VEC_A] || !d.p[MKS_P_VEC_A_SSQ] || !d.p[MKS_P_VEC_A_W] || !d.p[MKS_P_VEC_OUT])
                 return sfail(MK_ERR_BADARG, "stage %d: vector step without its term, sums of squares, weight or output", s);
@@ -191,6 +192,89 @@ extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     MKS_CUDA(cudaFuncSetAttribute(stage_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     void* kargs[] = {&A};
     MKS_CUDA(cudaLaunchCooperativeKernel((const void*)stage_kernel, dim3(grid), dim3(mks::NTHREADS), kargs, smem, static_cast<cudaStream_t>(stream)));
+    return MK_OK;
+}
+
+
+// ---- synchronisation probes ------------------------------------------------------------------------------------
+// What a stage boundary costs on this GPU, apart from any work: (0) the grid barrier protocol of stage_kernel
+// (512 consumer threads meet, one thread adds to a global counter with release semantics and polls it with acquire
+// loads, they meet again) over one CTA per SM, with `stores` global stores per thread in front of it; (1) a flag
+// hand-off between two CTAs: CTA 0 publishes k, CTA 1 answers k, per round trip.  Both spin with a bound.
+namespace mks {
+__device__ __forceinline__ unsigned long long probe_clock() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__global__ void __launch_bounds__(NTHREADS, 1) sync_probe_kernel(unsigned long long* words, float* data, long long* out, int iters, int mode, int stores) {
+    const int tid = (int)threadIdx.x;
+    if (tid >= NCT) return;
+    const unsigned long long t0 = probe_clock();
+    bool ok = true;
+    if (mode == 0) {
+        for (int k = 1; k <= iters && ok; k++) {
+            for (int s = 0; s < stores; s++) __stcg(data + ((size_t)blockIdx.x * NCT + tid) * 4 + (s & 3), (float)k);
+            consumer_sync();
+            if (tid == 0) {
+                asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(words), "l"(1ull) : "memory");
+                const unsigned long long target = (unsigned long long)k * gridDim.x;
+                unsigned long long v = 0;
+                int spins = 0;
+                do {
+                    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(words) : "memory");
+                } while (v < target && ++spins < 4000000);
+                if (v < target) out[1] = k;                      // gave up: the host reports it
+            }
+            consumer_sync();
+        }
+    } else if (blockIdx.x < 2 && tid == 0) {
+        unsigned long long* mine = words + 16 * blockIdx.x;      // separate 128-byte lines
+        unsigned long long* theirs = words + 16 * (1 - blockIdx.x);
+        for (unsigned long long k = 1; k <= (unsigned long long)iters && ok; k++) {
+            if (blockIdx.x == 0) asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(theirs), "l"(k) : "memory");
+            unsigned long long v = 0;
+            int spins = 0;
+            do {
+                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(mine) : "memory");
+            } while (v < k && ++spins < 4000000);
+            if (v < k) {
+                out[1] = (long long)k;
+                ok = false;
+            }
+            if (blockIdx.x == 1) asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(theirs), "l"(k) : "memory");
+        }
+    }
+    if (blockIdx.x == 0 && tid == 0) out[0] = (long long)(probe_clock() - t0);
+}
+}  // namespace mks
+
+extern "C" int mk_sync_probe(int device, int mode, int iters, int stores, int64_t* ns_per_iter) {
+    if (!ns_per_iter || iters < 1 || iters > 1000000 || mode < 0 || mode > 1 || stores < 0 || stores > 64)
+        return sfail(MK_ERR_BADARG, "mk_sync_probe: bad argument");
+    MKS_CUDA(cudaSetDevice(device));
+    int n_sm = 0;
+    MKS_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
+    unsigned long long* words = nullptr;
+    float* data = nullptr;
+    long long* out = nullptr;
+    MKS_CUDA(cudaMalloc(&words, 512));
+    MKS_CUDA(cudaMalloc(&data, (size_t)n_sm * NCT * 16));
+    MKS_CUDA(cudaMalloc(&out, 64));
+    cudaMemset(words, 0, 512);
+    cudaMemset(out, 0, 64);
+    const int grid = mode == 0 ? n_sm : 2;
+    void* kargs[] = {&words, &data, &out, &iters, &mode, &stores};
+    cudaError_t err = cudaLaunchCooperativeKernel((const void*)mks::sync_probe_kernel, dim3(grid), dim3(mks::NTHREADS), kargs, 0, nullptr);
+    if (err == cudaSuccess) err = cudaDeviceSynchronize();
+    long long host[2] = {0, 0};
+    if (err == cudaSuccess) err = cudaMemcpy(host, out, 16, cudaMemcpyDeviceToHost);
+    cudaFree(words);
+    cudaFree(data);
+    cudaFree(out);
+    if (err != cudaSuccess) return sfail(MK_ERR_CUDA, "mk_sync_probe: %s", cudaGetErrorString(err));
+    if (host[1] != 0) return sfail(MK_ERR_TIMEOUT, "mk_sync_probe: a wait ran out at iteration %lld", host[1]);
+    *ns_per_iter = host[0] / iters;
     return MK_OK;
 }
 

@@ -508,6 +508,7 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
         consumer_sync();
         prof_mark(S, 6);
         if (tid_() == 0) {
+            chaos_delay();
             const unsigned old = atomicAdd(cnt + m * NKV + kvh, 1u);
             const int is_last = (int)(old + 1u == (unsigned)nch);
             if (is_last) {
@@ -654,6 +655,7 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
 // left (every CTA adds them up itself, in a fixed order); a CTA then takes a slice of the 16-element groups.
 __device__ __noinline__ void vec_stage(Shared& S, Mut& mu, const mk_stage_desc& d) {
     const int N = d.i[MKS_I_VEC_N], ng = N / 16, M = S.A.M;
+    if (N == 0) return;                                        // an empty stage: its barrier only
     const float* base = reinterpret_cast<const float*>(d.p[MKS_P_VEC_BASE]);
     const float* a = reinterpret_cast<const float*>(d.p[MKS_P_VEC_A]);
     const float* b = reinterpret_cast<const float*>(d.p[MKS_P_VEC_B]);

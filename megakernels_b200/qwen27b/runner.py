@@ -44,7 +44,7 @@ def attn_chunk(maxlen, tasks_per_pos, grid):
 
 class Engine:
     def __init__(self, PK: Packed, M: int, maxlen: int = 4096, layers=None, device="cuda", block: int = KV_BLOCK,
-                 group=None, lm_head: bool = True, spin_limit_ms=2000):
+                 group=None, lm_head: bool = True, spin_limit_ms=2000, mailbox=None):
         if block != KV_BLOCK:
             raise ValueError(f"KV pages hold {KV_BLOCK} positions")
         if not 1 <= M <= D.MAX_BATCH:
@@ -142,7 +142,8 @@ class Engine:
                     norm_w=PK.final_norm, eps=s.eps, k_total=H, epilogue=D.MKS_E_LOGITS, n_valid=d.vocab, keys=self.keys,
                     row_base=rank * d.vocab)
         self.lm_head = lm_head
-        self.peer = PeerMailbox(group, rank, tp, dev) if tp > 1 else None
+        # `mailbox`: an object with `.addresses` (every rank's mailbox as this device sees it) made by the caller
+        self.peer = mailbox if mailbox is not None else (PeerMailbox(group, rank, tp, dev) if tp > 1 else None)
         self.rt = Runtime(pr, mailbox=self.peer, tp=tp, rank=rank, spin_limit_ms=spin_limit_ms)
         self.pos = self.rt.pos
 

@@ -57,7 +57,7 @@ class StageArgs(ctypes.Structure):
                 ("tokens_in", ctypes.c_uint64), ("xs_bytes", ctypes.c_int32), ("n_tokens_in", ctypes.c_int32)]
 
 
-STAGE_EXPORTS = ["mk_stage_launch", "mk_stage_validate", "mk_stage_count", "mk_stage_query", "mk_stage_scratch_bytes", "mk_peer_alloc", "mk_peer_open",
+STAGE_EXPORTS = ["mk_stage_launch", "mk_stage_validate", "mk_stage_count", "mk_stage_query", "mk_stage_scratch_bytes", "mk_sync_probe", "mk_peer_alloc", "mk_peer_open",
                  "mk_peer_close", "mk_peer_free"]
 STAGE_QUERIES = ["SMEM_BYTES", "N_THREADS", "SLOT_BYTES", "XS_BYTES", "DESC_BYTES", "MAX_GROUPS", "MAILBOX_BYTES", "ATTN_MAX_CHUNK"]
 
@@ -77,6 +77,7 @@ def lib():
         L.mk_stage_query.restype = ctypes.c_int64
         L.mk_stage_scratch_bytes.argtypes = [P(StageDesc), ctypes.c_int, ctypes.c_int]
         L.mk_stage_scratch_bytes.restype = ctypes.c_int64
+        L.mk_sync_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, P(ctypes.c_int64)]
         L.mk_peer_alloc.argtypes = [ctypes.c_int, ctypes.c_int64, P(ctypes.c_uint64), P(ctypes.c_uint8)]
         L.mk_peer_open.argtypes = [ctypes.c_int, P(ctypes.c_uint8), P(ctypes.c_uint64)]
         L.mk_peer_close.argtypes = [ctypes.c_uint64]

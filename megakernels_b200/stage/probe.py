@@ -22,7 +22,7 @@ def barrier_us(n_barriers=2000, device="cuda", reps=5):
     h, ssq = pr.zeros(1, 16), pr.zeros(1, 1)
     pr.embed(table, h, ssq, None, 16, 1, keys_valid=False)
     for _ in range(n_barriers):
-        pr.add(D.desc(D.MKS_OP_VEC))
+        pr.add(D.desc(D.MKS_OP_VEC, i=dict(VEC_N=0)))
     rt = Runtime(pr)
     best = float("inf")
     for _ in range(reps):
@@ -36,6 +36,19 @@ def barrier_us(n_barriers=2000, device="cuda", reps=5):
     return best
 
 
+def sync_ns(mode, iters=2000, stores=0, device=0):
+    """`mk_sync_probe`: 'barrier' = the bare grid-barrier protocol over one CTA per SM, 'hop' = a flag round trip
+    between two CTAs; nanoseconds per iteration."""
+    import ctypes
+    from .. import _lib
+    out = ctypes.c_int64()
+    _lib.check(D.lib().mk_sync_probe(device, {"barrier": 0, "hop": 1}[mode], iters, stores, ctypes.byref(out)))
+    return out.value
+
+
 if __name__ == "__main__":
     for n in (200, 2000):
-        print(f"{n} barriers: {barrier_us(n):.3f} us per barrier")
+        print(f"stage kernel, {n} empty stages: {barrier_us(n):.3f} us per stage barrier")
+    for stores in (0, 1, 4):
+        print(f"bare grid barrier, {stores} store(s) per thread before it: {sync_ns('barrier', stores=stores)} ns")
+    print(f"flag round trip between two CTAs: {sync_ns('hop')} ns")

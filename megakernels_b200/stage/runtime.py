@@ -20,7 +20,7 @@ class Program:
 
     def __init__(self, device, batch, grid):
         self.device, self.batch, self.grid = torch.device(device), batch, grid
-        self.stages, self.keep, self.shared = [], [], {}
+        self.stages, self.names, self.keep, self.shared = [], [], [], {}
 
     # ---- memory -------------------------------------------------------------------------------------
     def zeros(self, *shape, dtype=torch.float32):
@@ -44,8 +44,10 @@ class Program:
         return cur
 
     # ---- stages -------------------------------------------------------------------------------------
-    def add(self, d):
+    def add(self, d, name=None):
         self.stages.append(d)
+        self.names.append(name if name is not None else {D.MKS_OP_EMBED: "embed", D.MKS_OP_GDN: "deltanet", D.MKS_OP_ATTN: "attention",
+                                                         D.MKS_OP_ROUTE: "route", D.MKS_OP_VEC: "vector"}.get(d.op, "gemv"))
         return d
 
     def embed(self, table, h, h_ssq, keys, hidden, vocab, scale=0.0, keys_valid=True):
@@ -76,7 +78,7 @@ class Program:
         p = dict(W=ptr(w), W_GSTRIDE=w_gstride, W_SHARED=ptr(w_shared), ROW_SCALE=ptr(row_scale), RS_GSTRIDE=rs_gstride,
                  RS_SHARED=ptr(rs_shared), X=ptr(x), X_SSQ=ptr(x_ssq), NORM_W=ptr(norm_w), OUT=ptr(out), OUT_SSQ=ptr(out_ssq),
                  CNT=ptr(cnt), PART=ptr(part), KEYS=ptr(keys), ROW_BASE=row_base, W_BYTES=meta["bytes"])
-        return self.add(D.desc(D.MKS_OP_GEMV, D.MKS_FLAG_NO_BARRIER if no_barrier else 0, i=i, f=f, p=p))
+        return self.add(D.desc(D.MKS_OP_GEMV, D.MKS_FLAG_NO_BARRIER if no_barrier else 0, i=i, f=f, p=p), name=name)
 
     def host_array(self):
         arr = (D.StageDesc * len(self.stages))(*self.stages)

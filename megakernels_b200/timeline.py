@@ -59,3 +59,35 @@ def profile_step(mk, context_tokens, step=8, n_generate=16):
     prof = mk.prof_buffer()
     mk.run([last], n_generate=n_generate, prof=prof, prof_step=step)
     return summarize(prof, mk.cfg)
+
+
+def main():
+    import argparse
+
+    from .config import qwen35_08b
+    from .engine import Megakernel
+    from .synth import make_prompt, make_weights
+    ap = argparse.ArgumentParser(description="Per-op timeline of one decode step of the 0.8B kernels (synthetic weights, full size).")
+    ap.add_argument("--quant", default="bf16", choices=["bf16", "int8"])
+    ap.add_argument("--context", type=int, default=32)
+    ap.add_argument("--batch", type=int, default=1)
+    args = ap.parse_args()
+    cfg = qwen35_08b()
+    w = make_weights(cfg, 0)
+    mk = Megakernel((cfg, w), max_seq=args.context + 64, quant=args.quant, batch=args.batch)
+    if args.batch == 1:
+        rows = profile_step(mk, make_prompt(cfg, args.context), step=8, n_generate=16)
+    else:
+        prompts = [make_prompt(cfg, args.context, seed=100 + j) for j in range(args.batch)]
+        prof = mk.prof_buffer()
+        mk.run_batch(prompts, n_generate=16, prof=prof, prof_step=args.context + 8)
+        rows = summarize(prof, cfg)
+    print(f"0.8B hybrid, {args.quant} weights, batch {args.batch}, context {args.context}: decode step 8 of a 16-step launch\n")
+    print(format_rows(rows))
+    print("\n(wait = entering an op until its inputs are staged; busy = entering until its outputs are published, median CTA;"
+          "\n critical = last publish of the op minus last publish of the op before, median over the op's layers; the `step` row's"
+          "\n critical column is the sum over all ops: the step's critical path)")
+
+
+if __name__ == "__main__":
+    main()
