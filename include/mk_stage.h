@@ -121,6 +121,11 @@ enum {
     MKS_I_ROPE_PAIRS,    /* cos/sin table columns (angle pairs); pair d rotates dims (d, d + HD/2) when ROT == HD, else (d, d + ROT/2) */
     MKS_I_Q_BF16,        /* 1: q rounded to bf16 before QK^T                                       */
     MKS_I_MAX_CHUNKS,    /* split records per (sequence, kv head) in A_PART                        */
+    MKS_I_KV_BLOCK,      /* positions per cache page, a power of two (0: 64)                        */
+    MKS_I_KV_S_PAGE, MKS_I_KV_S_HEAD, MKS_I_KV_S_POS,   /* element strides of the paged cache between pages, kv heads and
+                            positions (all 0: [page][kv head][64][head dim]); a serving stack's layout, e.g.
+                            [page][position][kv head][head dim], is strides (block * heads * dim, dim, heads * dim)
+                            (qwen3.8-27b-gfx942/mk/kernel.py:15-27) */
 
     /* ROUTE */
     MKS_I_EXPERTS = 0, MKS_I_TOPK, MKS_I_LOGIT_STRIDE,

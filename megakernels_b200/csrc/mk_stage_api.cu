@@ -69,6 +69,8 @@ extern "C" int mk_stage_validate(const mk_stage_desc* prog, int n_stages, int ba
             if (HD != 256 && HD != 512) return sfail(MK_ERR_BADARG, "stage %d: head dim %d", s, HD);
             if (CP < 16 || CP > ATTN_MAX_CHUNK) return sfail(MK_ERR_BADARG, "stage %d: %d positions per task", s, CP);
             if ((long long)(QPK * HD + 2 * HD + QPK * CP + QPK * ATTN_MAX_CHUNKS + 2 * QPK + CP + 4) * 4 > XS_BYTES) return sfail(MK_ERR_BADARG, "stage %d: attention scratch does not fit", s);
+            if (d.i[MKS_I_KV_BLOCK] < 0 || (d.i[MKS_I_KV_BLOCK] & (d.i[MKS_I_KV_BLOCK] - 1))) return sfail(MK_ERR_BADARG, "stage %d: %d positions per cache page (a power of two)", s, d.i[MKS_I_KV_BLOCK]);
+            if (d.i[MKS_I_KV_S_PAGE] && (d.i[MKS_I_KV_S_POS] < HD || d.i[MKS_I_KV_S_HEAD] < 1 || d.i[MKS_I_KV_S_POS] % 8)) return sfail(MK_ERR_BADARG, "stage %d: cache strides", s);
             if (d.i[MKS_I_MAX_CHUNKS] < 1 || d.i[MKS_I_MAX_CHUNKS] > ATTN_MAX_CHUNKS) return sfail(MK_ERR_BADARG, "stage %d: %d split records per head (at most %d)", s, d.i[MKS_I_MAX_CHUNKS], ATTN_MAX_CHUNKS);
         } else if (d.op == MKS_OP_GDN) {
             if (d.i[MKS_I_NKH] < 1 || d.i[MKS_I_NVH] % d.i[MKS_I_NKH]) return sfail(MK_ERR_BADARG, "stage %d: DeltaNet heads", s);

@@ -263,6 +263,11 @@ template <bool KVF32>
 __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc& d) {
     const int NQ = d.i[MKS_I_NQ], NKV = d.i[MKS_I_NKV], HD = d.i[MKS_I_HD], ROT = d.i[MKS_I_ROT];
     const int QPK = NQ / NKV, CP = d.i[MKS_I_CHUNK_POS], window = d.i[MKS_I_WINDOW], maxpages = d.i[MKS_I_MAX_PAGES];
+    const int kvb = d.i[MKS_I_KV_BLOCK] > 0 ? d.i[MKS_I_KV_BLOCK] : 64, kvb_shift = 31 - __clz(kvb);
+    const bool own_layout = d.i[MKS_I_KV_S_PAGE] == 0;
+    const uint32_t kv_s_page = own_layout ? (uint32_t)(NKV * kvb * HD) : (uint32_t)d.i[MKS_I_KV_S_PAGE];
+    const uint32_t kv_s_head = own_layout ? (uint32_t)(kvb * HD) : (uint32_t)d.i[MKS_I_KV_S_HEAD];
+    const uint32_t kv_s_pos = own_layout ? (uint32_t)HD : (uint32_t)d.i[MKS_I_KV_S_POS];
     const int pairs = d.i[MKS_I_ROPE_PAIRS], pair_dist = ROT == HD ? HD / 2 : ROT / 2;
     const int q_off = d.i[MKS_I_A_Q_OFF], q_hs = d.i[MKS_I_A_Q_HSTRIDE], gate_off = d.i[MKS_I_A_GATE_OFF];
     const int k_off = d.i[MKS_I_A_K_OFF], v_off = d.i[MKS_I_A_V_OFF];
@@ -329,8 +334,8 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
 #pragma unroll 1
             for (int i = tid_() - (QPK + 2) * 32; i < np; i += NCT - (QPK + 2) * 32) {
                 const int p = first + i;
-                const int page = __ldg(bt + (size_t)m * maxpages + p / 64);
-                const uint32_t off = (uint32_t)((((size_t)page * NKV + kvh) * 64 + (p & 63)) * HD);
+                const int page = __ldg(bt + (size_t)m * maxpages + (p >> kvb_shift));
+                const uint32_t off = (uint32_t)page * kv_s_page + (uint32_t)kvh * kv_s_head + (uint32_t)(p & (kvb - 1)) * kv_s_pos;
                 row_s[i] = off;
                 // ask the L2 for the rows now: the weight stream between two attention stages has pushed the cache's
                 // pages out of the TLBs, and the first touch of a page costs several microseconds

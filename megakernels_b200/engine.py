@@ -637,6 +637,36 @@ class Megakernel:
         v = self.v_cache[i][blk, :, off].transpose(0, 1).float()
         return k, v
 
+    # ---- state import: the inverse accessors (a batched prefill computed elsewhere hands its state over) ----
+    def set_conv_window(self, i, window, n_tokens):
+        """`window` [conv_dim, W]: the last W conv inputs (positions n_tokens - W .. n_tokens - 1) of DeltaNet layer i,
+        channels in the reference decoder's order (q | k | v).  Writes them into the single-sequence history."""
+        c, ring = self.cfg, self.conv_hist[i].shape[-1]
+        spt = c.lin_v_dim // self.GDN_SLICE
+        nqk = c.lin_heads * c.lin_k_dim
+        window = window.to(self.device, torch.float32)
+        for j in range(window.shape[1]):
+            p = n_tokens - window.shape[1] + j
+            if p < 0:
+                continue
+            col = window[:, j]
+            q = col[:nqk].reshape(c.lin_heads, 1, c.lin_k_dim).expand(-1, spt, -1).reshape(-1, c.lin_k_dim)
+            k = col[nqk: 2 * nqk].reshape(c.lin_heads, 1, c.lin_k_dim).expand(-1, spt, -1).reshape(-1, c.lin_k_dim)
+            v = col[2 * nqk:].reshape(c.lin_heads * spt, self.GDN_SLICE)
+            self.conv_hist[i][:, :, p % ring] = torch.cat([q, k, v], dim=1).to(self.conv_hist[i].dtype)   # every task keeps its head's q and k
+
+    def set_deltanet_state(self, i, state):
+        """`state` [head][k][v] (the reference decoder's layout) -> the kernel's [head][v][k]."""
+        self.bstate[i][0].copy_(state.to(self.device).transpose(1, 2))
+
+    def write_kv(self, i, start, k, v, seq=0):
+        """Store K, V [kv_head, n, head_dim] of attention layer i at positions start .. start + n - 1 of the paged cache."""
+        bt = self.block_table.long().view(self.batch, -1)[seq]
+        pos = torch.arange(start, start + k.shape[1], device=self.device)
+        blk, off = bt[pos // self.KV_BLOCK], pos % self.KV_BLOCK
+        self.k_cache[i][blk, :, off] = k.to(self.device).transpose(0, 1).to(self.k_cache[i].dtype)
+        self.v_cache[i][blk, :, off] = v.to(self.device).transpose(0, 1).to(self.v_cache[i].dtype)
+
     def snapshot(self):
         """Copy of the recurrent state (conv histories + DeltaNet state of every sequence) and the positions."""
         return [t.clone() for t in self.conv_hist + self.bconv_hist + self.bstate], list(self.bpos), self._mode

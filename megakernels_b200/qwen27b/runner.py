@@ -44,9 +44,17 @@ def attn_chunk(maxlen, tasks_per_pos, grid):
 
 class Engine:
     def __init__(self, PK: Packed, M: int, maxlen: int = 4096, layers=None, device="cuda", block: int = KV_BLOCK,
-                 group=None, lm_head: bool = True, spin_limit_ms=2000, mailbox=None):
+                 group=None, lm_head: bool = True, spin_limit_ms=2000, mailbox=None, kv_layout="pages", kv_block=KV_BLOCK):
+        """`kv_layout="serving"` keeps the KV cache as [page][position][kv head][head dim] with `kv_block` positions per
+        page (a power of two), the layout a serving stack's paged attention uses; the default is this kernel's own
+        [page][kv head][64][head dim]."""
         if block != KV_BLOCK:
-            raise ValueError(f"KV pages hold {KV_BLOCK} positions")
+            raise ValueError(f"KV pages hold {KV_BLOCK} positions (kv_block sets the page size of the serving layout)")
+        if kv_layout not in ("pages", "serving") or kv_block < 8 or kv_block & (kv_block - 1):
+            raise ValueError("kv_layout: 'pages' or 'serving'; kv_block: a power of two >= 8")
+        if kv_layout == "pages":
+            kv_block = KV_BLOCK
+        self.kv_layout, self.kv_block = kv_layout, kv_block
         if not 1 <= M <= D.MAX_BATCH:
             raise ValueError(f"M must lie in [1, {D.MAX_BATCH}]")
         if not torch.cuda.is_available():
@@ -61,8 +69,9 @@ class Engine:
             dev = torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(dev)
         self.device = dev
-        self.maxlen = -(-maxlen // KV_BLOCK) * KV_BLOCK
-        nb = self.maxlen // KV_BLOCK
+        KB = self.kv_block
+        self.maxlen = -(-maxlen // max(KB, KV_BLOCK)) * max(KB, KV_BLOCK)
+        nb = self.maxlen // KB
         grid = torch.cuda.get_device_properties(dev).multi_processor_count
         self.grid = grid
         H = s.hidden
@@ -81,8 +90,10 @@ class Engine:
         pr.hold(self.bt)
         n_att = sum(s.is_attn(i) for i in range(self.layers))
         n_gdn = self.layers - n_att
-        self.k_cache = z(n_att, M * nb + 1, d.nkv, KV_BLOCK, HD, dtype=torch.bfloat16)
-        self.v_cache = z(n_att, M * nb + 1, d.nkv, KV_BLOCK, HD, dtype=torch.bfloat16)
+        kv_shape = (M * nb + 1, d.nkv, KB, HD) if kv_layout == "pages" else (M * nb + 1, KB, d.nkv, HD)
+        self.k_cache = z(n_att, *kv_shape, dtype=torch.bfloat16)
+        self.v_cache = z(n_att, *kv_shape, dtype=torch.bfloat16)
+        kv_fields = {} if kv_layout == "pages" else dict(KV_BLOCK=KB, KV_S_PAGE=KB * d.nkv * HD, KV_S_HEAD=HD, KV_S_POS=d.nkv * HD)
         self.conv = z(n_gdn, M, d.conv_dim, 4)
         self.ssm = z(n_gdn, M, d.nvh, DV, DK)
         qpk = d.nq // d.nkv
@@ -104,7 +115,7 @@ class Engine:
                               i=dict(NQ=d.nq, NKV=d.nkv, HD=HD, ROT=ROT, A_Q_OFF=0, A_Q_HSTRIDE=2 * HD, A_GATE_OFF=HD,
                                      A_K_OFF=2 * d.nq * HD, A_V_OFF=2 * d.nq * HD + d.nkv * HD, A_Y_STRIDE=ymax, A_Y2_STRIDE=y2w,
                                      WINDOW=0, CHUNK_POS=cp, MAX_PAGES=nb, KV_F32=0, NORM_PLAIN=0, V_NORM=0, ROPE_PAIRS=ROT // 2,
-                                     Q_BF16=1, MAX_CHUNKS=max_chunks),
+                                     Q_BF16=1, MAX_CHUNKS=max_chunks, **kv_fields),
                               f=dict(EPS=s.eps, SCALE=HD ** -0.5),
                               p=dict(A_Y=self.y.data_ptr(), A_Y2=self.y2.data_ptr(), Q_NORM=sm("self_attn.q_norm.weight").data_ptr(),
                                      K_NORM=sm("self_attn.k_norm.weight").data_ptr(), K_CACHE=self.k_cache[ai].data_ptr(),
@@ -202,8 +213,10 @@ class Engine:
     def kv_rows(self, ai, m, n):
         """K, V of attention layer ai for positions [0, n) of sequence m: [kv heads, n, 256] fp32."""
         pos = torch.arange(n, device=self.device)
-        blk, off = self.bt[m].long()[pos // KV_BLOCK], pos % KV_BLOCK
-        return self.k_cache[ai][blk, :, off].transpose(0, 1).float(), self.v_cache[ai][blk, :, off].transpose(0, 1).float()
+        blk, off = self.bt[m].long()[pos // self.kv_block], pos % self.kv_block
+        if self.kv_layout == "pages":
+            return self.k_cache[ai][blk, :, off].transpose(0, 1).float(), self.v_cache[ai][blk, :, off].transpose(0, 1).float()
+        return self.k_cache[ai][blk, off].transpose(0, 1).float(), self.v_cache[ai][blk, off].transpose(0, 1).float()
 
     def bytes_per_step(self, context):
         """Algorithmic bytes one decode step moves on this rank: weights once, SSM state read + written and the KV

@@ -60,6 +60,8 @@ def main():
     torch.cuda.synchronize()
     eng.check()
     out["stage_35b"] = digest(lg, ids, eng.logits, eng.ssm, eng.route_ids)
+    from megakernels_b200 import _lib
+    out["library"] = os.path.basename(_lib.LIB_PATH)
     print("CHAOS_DIGESTS " + json.dumps(out), flush=True)
 
 

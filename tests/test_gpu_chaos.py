@@ -36,6 +36,7 @@ def test_chaos_build_produces_the_same_bits():
         from megakernels_b200 import build
         build.build_chaos()
     plain, chaos = _digests(None), _digests(CHAOS_LIB)
+    assert plain.pop("library") == "libmk_b200.so" and chaos.pop("library") == CHAOS_LIB
     assert set(plain) == set(chaos) and len(plain) >= 7
     different = [k for k in plain if plain[k] != chaos[k]]
     assert not different, f"outputs depend on the timing of publishes: {different}"

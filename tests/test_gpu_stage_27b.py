@@ -124,6 +124,23 @@ def test_prefill_in_one_launch_equals_stepping(model):
         a.prefill(prompts[:2])
 
 
+def test_serving_cache_layout_gives_the_same_bits(model):
+    """[page][position][kv head][dim] pages of 16 positions (a serving stack's layout) against this kernel's own pages."""
+    W, PK = model
+    M = 3
+    prompts = [make_prompt(SMALL.vocab, 21, seed=60 + j) for j in range(M)]
+    own, srv = Engine(PK, M, maxlen=64), Engine(PK, M, maxlen=64, kv_layout="serving", kv_block=16)
+    a, b = own.prefill(prompts).clone(), srv.prefill(prompts).clone()
+    srv.check()
+    assert torch.equal(a, b)
+    for m in range(M):
+        for x, y in zip(own.kv_rows(0, m, 21), srv.kv_rows(0, m, 21)):
+            assert torch.equal(x, y)
+    assert srv.k_cache.shape[2:] == (16, SMALL.nkv, 256)
+    with pytest.raises(ValueError):
+        Engine(PK, M, maxlen=64, kv_layout="serving", kv_block=24)
+
+
 def test_two_engines_share_one_set_of_packed_weights(model):
     W, PK = model
     a, b = Engine(PK, 2, maxlen=64), Engine(PK, 2, maxlen=64)
