@@ -58,6 +58,8 @@ def test_oracle_reproduces_the_reference_fixture(case):
 def test_oracle_equals_the_reference_decoder_bitwise(case):
     g, shape, W = case
     sys.path.insert(0, os.path.join(REFERENCE, "qwen3.8-27b-gfx942"))
+    for k in [k for k in sys.modules if k == "mk" or k.startswith("mk.")]:
+        del sys.modules[k]                      # another model's `mk` package may have been imported by an earlier test
     from mk import reference as R
     M = 2
     ref_st = R.State.new(M, 32, device="cpu")

@@ -48,6 +48,8 @@ def test_mxfp4_of_zeros_and_extremes():
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "qwen3.8-27b-gfx942")), reason="reference checkout absent")
 def test_mxfp4_dequantiser_equals_the_reference():
     sys.path.insert(0, os.path.join(REFERENCE, "qwen3.8-27b-gfx942"))
+    for k in [k for k in sys.modules if k == "mk" or k.startswith("mk.")]:
+        del sys.modules[k]                      # another model's `mk` package may have been imported by an earlier test
     from mk import reference as R
     pk, sc = Q.quantize_mxfp4(_w(64, 512, seed=3))
     assert torch.equal(Q.dequantize_mxfp4(pk, sc), R.dequant_mxfp4(pk, sc))
