@@ -145,6 +145,8 @@ enum {
     MKS_F_SOFTCAP,       /* E_LOGITS: cap * tanh(y / cap) if > 0                                   */
     MKS_F_SCALE,         /* EMBED: embedding scale (0: none); ATTN: score scale; VEC: factor on the result (0: none) */
     MKS_F_IN_SCALE,      /* P_NORM: extra factor on the normed input (router of the 26B model)     */
+    MKS_F_IN_BOUND,      /* > 0: no staged input value exceeds it in magnitude (the host knows: a normed vector is at most
+                            sqrt(K) max|weight|); lets the kernel fix the fp16 scale without a pass over the values */
     MKS_F_COUNT = 8
 };
 

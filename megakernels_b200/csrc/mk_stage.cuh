@@ -480,32 +480,29 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     };
     request(0);
     if (norm) {
-        // 1/rms of every sequence from the 16-element sums of squares of the whole input vector
-        // (every thread asks for its share of every sequence's sums at once: one L2 round trip, fixed summation order)
+        // 1/rms of every sequence from the 16-element sums of squares of the whole input vector: warp m adds up
+        // sequence m's sums (all loads of a lane in flight at once, fixed order) while the other warps only wait for x
         const int K = d.i[MKS_I_K_TOTAL], n16 = K / 16;
         const float* ssq = reinterpret_cast<const float*>(d.p[MKS_P_X_SSQ]);
-        float part[MKS_MAX_BATCH];
-#pragma unroll
-        for (int m = 0; m < MKS_MAX_BATCH; m++) {
-            part[m] = 0.f;
-            if (m < M) {
-#pragma unroll 2
-                for (int j = tid_(); j < n16; j += NCT) part[m] += ldcg_f(ssq + (size_t)m * n16 + j);
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < MKS_MAX_BATCH; m++)
-            if (m < M) {
-                const float v = warp_sum(part[m]);
-                if (lane_() == 0) S.red[16 + warp_() * MKS_MAX_BATCH + m] = v;
-            }
-        consumer_sync();
-        if (tid_() < M) {
+        if (warp_() < M) {
+            const float* row = ssq + (size_t)warp_() * n16;
             float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < NCW; w++) s += S.red[16 + w * MKS_MAX_BATCH + tid_()];
-            S.rstd[tid_()] = rsqrtf(s / (float)K + d.f[MKS_F_EPS]);
+#pragma unroll 8
+            for (int j = lane_(); j < n16; j += 32) s += ldcg_f(row + j);
+            s = warp_sum(s);
+            if (lane_() == 0) S.rstd[warp_()] = rsqrtf(s / (float)K + d.f[MKS_F_EPS]);
         }
+    }
+    // A bound on |input| known to the host (a normed vector cannot exceed sqrt(K) max|weight|) fixes the power-of-two
+    // scale of the fp16 copy up front: the values then go to shared memory in their final form in one pass.
+    const float bound = d.f[MKS_F_IN_BOUND];
+    const bool fixed_scale = bound > 0.f && fmt != MKS_FMT_BF16 && pieces == 1;
+    float fscale = 1.f;
+    if (fixed_scale) {
+        const int be = ((__float_as_int(bound) >> 23) & 0xff) - 126;          // bound < 2^be
+        const int e = max(-100, min(100, 15 - be));
+        fscale = __int_as_float((127 + e) << 23);
+        if (tid_() < MKS_MAX_BATCH) S.xinv[tid_()] = __int_as_float((127 - e) << 23);
     }
     consumer_sync();
     prof_mark(S, 4);
@@ -534,13 +531,19 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
                     *reinterpret_cast<float4*>(S.xs() + (size_t)(2 * m) * stride + (size_t)k4 * 16) = make_float4(v[0], v[1], v[2], v[3]);
                 } else {
                     const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-                    *reinterpret_cast<uint2*>(S.xs() + (size_t)m * stride + (size_t)k4 * 8) =
-                        make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
                     v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+                    if (fixed_scale) {
+                        const __half2 a2 = __floats2half2_rn(v[0] * fscale, v[1] * fscale), b2 = __floats2half2_rn(v[2] * fscale, v[3] * fscale);
+                        *reinterpret_cast<uint2*>(S.xs() + (size_t)m * stride + (size_t)k4 * 8) =
+                            make_uint2(*reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&b2));
+                    } else {
+                        *reinterpret_cast<uint2*>(S.xs() + (size_t)m * stride + (size_t)k4 * 8) =
+                            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                    }
                 }
                 mx = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
             }
-            if (fmt != MKS_FMT_BF16) {
+            if (fmt != MKS_FMT_BF16 && !fixed_scale) {
                 // a warp's 32 groups lie in at most two sequences
                 const int m0 = __shfl_sync(0xffffffffu, m, 0);
                 const float a = warp_max(live && m == m0 ? mx : 0.f), b = warp_max(live && m != m0 ? mx : 0.f);
@@ -551,6 +554,7 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
             }
         }
     }
+    if (fixed_scale) return;                                   // staged in final form; the caller's barrier publishes it
     if (fmt == MKS_FMT_BF16) {
         if (tid_() < 8) S.xinv[tid_()] = 1.f;
         if (pieces == 2) {

@@ -52,7 +52,7 @@ __device__ void choose_tokens(Shared& S, Mut& mu, const Args& A, const u64* keys
 // ---- embedding ---------------------------------------------------------------------------------------------------
 __device__ __noinline__ void embed_stage(Shared& S, Mut& mu, const mk_stage_desc& d, const Args& A, int step, uint32_t tag) {
     const int H = d.i[MKS_I_HIDDEN], vocab = d.i[MKS_I_VOCAB];
-    if (step > 0) {
+    if (step > 0 && d.i[MKS_I_KEYS_VALID] && d.p[MKS_P_E_KEYS]) {
         choose_tokens(S, mu, A, reinterpret_cast<const u64*>(d.p[MKS_P_E_KEYS]), tag, vocab);
         consumer_sync();
         if (cta_() == 0 && tid_() < S.A.M) {
@@ -812,7 +812,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
     }
     // the choice after the last step, and the positions (the program's first stage names the key buffer)
     const mk_stage_desc& d0 = A.prog[0];
-    if (!failed && d0.op == MKS_OP_EMBED && d0.i[MKS_I_KEYS_VALID]) {
+    if (!failed && d0.op == MKS_OP_EMBED && d0.i[MKS_I_KEYS_VALID] && d0.p[MKS_P_E_KEYS]) {
         choose_tokens(S, mu, A, reinterpret_cast<const u64*>(d0.p[MKS_P_E_KEYS]), (uint32_t)(A.bar_base / grid_() + bar_n) + 1u, d0.i[MKS_I_VOCAB]);
         consumer_sync();
         if (cta_() == 0 && tid_() < S.A.M) {

@@ -74,7 +74,12 @@ class Program:
                  N_VALID=n_valid if n_valid is not None else meta["rows"], X_STRIDE=x_stride, X_GSTRIDE=x_gstride,
                  OUT_STRIDE=out_stride, OUT_GSTRIDE=out_gstride, REDUCE_GROUPS=int(reduce_groups), ALLREDUCE=int(allreduce), ACT=act,
                  K_TOTAL=k_total if k_total is not None else meta["kc"] * S, BLOCK_SCALES=int(meta["block_scaled"]), PIECES=pieces)
-        f = dict(EPS=eps, NORM_OFF=norm_off, SOFTCAP=softcap, IN_SCALE=in_scale)
+        in_bound = 0.0
+        if prologue == D.MKS_P_NORM and norm_w is not None:
+            # |x_i| / rms(x) <= sqrt(K): a bound on every normed value, with a margin for the roundings
+            kt = k_total if k_total is not None else meta["kc"] * S
+            in_bound = 1.02 * (kt ** 0.5) * float((norm_w.float() + norm_off).abs().max()) * (in_scale if in_scale else 1.0)
+        f = dict(EPS=eps, NORM_OFF=norm_off, SOFTCAP=softcap, IN_SCALE=in_scale, IN_BOUND=in_bound)
         p = dict(W=ptr(w), W_GSTRIDE=w_gstride, W_SHARED=ptr(w_shared), ROW_SCALE=ptr(row_scale), RS_GSTRIDE=rs_gstride,
                  RS_SHARED=ptr(rs_shared), X=ptr(x), X_SSQ=ptr(x_ssq), NORM_W=ptr(norm_w), OUT=ptr(out), OUT_SSQ=ptr(out_ssq),
                  CNT=ptr(cnt), PART=ptr(part), KEYS=ptr(keys), ROW_BASE=row_base, W_BYTES=meta["bytes"])
