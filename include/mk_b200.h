@@ -120,7 +120,6 @@ typedef struct mk_launch_args {
     uint64_t prof;           /* optional u64 [grid, MK_PROF_MAX_OPS, MK_PROF_FIELDS]           */
     int32_t prof_step;
     int32_t grid;            /* CTAs; 0 = one per SM                                           */
-    int64_t pf_bytes;        /* L2 prefetch distance ahead of the shared-memory ring, per CTA  */
     int64_t spin_limit_ns;   /* bound on every device-side wait; 0 = library default (2 s)    */
     /* speculative cycles (spec = 1; n_steps counts cycles, each verifies the pending token and one draft;
      * needs the MTP record and draft-head fields of mk_set_params; qwen3.5-0.8b/csrc/megakernel.cu:1196-1276) */
@@ -209,7 +208,6 @@ typedef struct mk_batch_args {
     uint64_t out_info;               /* int32[8]: steps run, next epoch, bit mask of stopped sequences */
     uint64_t prof;
     int64_t spin_limit_ns;
-    int64_t pf_bytes;                /* L2 prefetch distance ahead of the shared-memory ring, per CTA */
 } mk_batch_args;
 int mk_launch_batch(mk_engine* e, const mk_batch_args* args, void* stream);
 

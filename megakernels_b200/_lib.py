@@ -49,7 +49,7 @@ class LaunchArgs(ctypes.Structure):
                 ("stop_ids", ctypes.c_uint64), ("tokens_out", ctypes.c_uint64), ("logits_out", ctypes.c_uint64),
                 ("resid_out", ctypes.c_uint64), ("step_ts", ctypes.c_uint64), ("out_info", ctypes.c_uint64),
                 ("prof", ctypes.c_uint64), ("prof_step", ctypes.c_int32), ("grid", ctypes.c_int32),
-                ("pf_bytes", ctypes.c_int64), ("spin_limit_ns", ctypes.c_int64), ("spec", ctypes.c_int32),
+                ("spin_limit_ns", ctypes.c_int64), ("spec", ctypes.c_int32),
                 ("first_tok", ctypes.c_int32), ("first_draft", ctypes.c_int32), ("limit", ctypes.c_int32),
                 ("spec_out", ctypes.c_uint64), ("cycle_out", ctypes.c_uint64)]
 
@@ -64,8 +64,7 @@ class BatchArgs(ctypes.Structure):
                 ("epoch_base", ctypes.c_uint32), ("seed", ctypes.c_uint32), ("inv_temperature", ctypes.c_float),
                 ("n_stop", ctypes.c_int32), ("prof_step", ctypes.c_int32), ("stop_ids", ctypes.c_uint64),
                 ("tokens_out", ctypes.c_uint64), ("logits_out", ctypes.c_uint64), ("step_ts", ctypes.c_uint64),
-                ("out_info", ctypes.c_uint64), ("prof", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64),
-                ("pf_bytes", ctypes.c_int64)]
+                ("out_info", ctypes.c_uint64), ("prof", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64)]
 
 
 _lib = None

@@ -249,7 +249,6 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     A.prof = as_ptr<unsigned long long*>(a->prof);
     A.spec_out = as_ptr<int*>(a->spec_out);
     A.cycle_out = as_ptr<int*>(a->cycle_out);
-    A.pf_bytes = a->pf_bytes;
     A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
     A.n_forced = a->n_forced;
     A.n_steps = a->n_steps;
@@ -358,7 +357,6 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
     A.step_ts = as_ptr<unsigned long long*>(a->step_ts);
     A.out_info = as_ptr<int*>(a->out_info);
     A.prof = as_ptr<unsigned long long*>(a->prof);
-    A.pf_bytes = a->pf_bytes;
     A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
     A.n_forced = a->n_forced;
     A.n_steps = a->n_steps;
@@ -428,7 +426,6 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     A.out_info = as_ptr<int*>(a->out_info);
     A.prof = as_ptr<unsigned long long*>(a->prof);
     A.spin_limit_ns = a->spin_limit_ns > 0 ? a->spin_limit_ns : 2000000000ll;
-    A.pf_bytes = a->pf_bytes;
     for (int j = 0; j < NB; j++) {
         A.n_forced[j] = j < a->batch ? a->n_forced[j] : 0;
         A.n_total[j] = j < a->batch ? a->n_total[j] : 0;

@@ -48,7 +48,6 @@ struct BatchArgs {
     int* out_info;
     unsigned long long* prof;
     long long spin_limit_ns;
-    long long pf_bytes;                     // L2 prefetch distance ahead of the ring, per CTA (0: off)
     int n_forced[NB];
     int n_total[NB];                        // steps sequence j takes part in; it is frozen afterwards
     int pos0[NB];
@@ -401,8 +400,8 @@ __device__ bool gdn_batch(Ctx& c, const Params& P, const LayerP& L, const BatchA
 // The weight stream of the batched kernel: the four GEMVs of every layer, then the LM head from
 // step `lm_from` on.
 template <class S>
-__device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A, bool prefetch) {
-    Producer<GeoB::NS> pr(c, prefetch, A.pf_bytes);
+__device__ void producer_batch(Ctx& c, const Params& P, const BatchArgs& A) {
+    Producer<GeoB::NS> pr(c);
     for (int s = 0; s < A.n_steps && !pr.stop; s++) {
         for (int l = 0; l < P.n_layers && !pr.stop; l++) {
             const LayerP& L = P.layer[l];
@@ -590,7 +589,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const __grid_constan
         c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
-        c.sm.pf_pos = reinterpret_cast<volatile u64*>(p); p += 8;
     }
     c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
     c.cta = blockIdx.x; c.grid = gridDim.x;
@@ -605,7 +603,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const __grid_constan
         }
         *c.sm.abort_flag = 0;
         *c.sm.quit_flag = 0;
-        *c.sm.pf_pos = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
@@ -613,8 +610,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) batch_kernel(const __grid_constan
     __syncthreads();
 
     if (c.warp == NCW) {
-        if (c.lane == 0) producer_batch<S>(c, P, A, false);
-        else if (c.lane == 1 && A.pf_bytes > 0) producer_batch<S>(c, P, A, true);
+        if (c.lane == 0) producer_batch<S>(c, P, A);
         return;
     }
 

@@ -120,7 +120,6 @@ struct Args {
     unsigned long long* prof;
     int* spec_out;
     int* cycle_out;
-    long long pf_bytes;
     long long spin_limit_ns;
     int n_forced, n_steps, lm_from, start_pos;
     unsigned epoch_base, seed;

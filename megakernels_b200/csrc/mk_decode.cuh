@@ -50,7 +50,6 @@ struct Smem {
     uint64_t* empty;    // [ring stages]
     volatile int* abort_flag;
     volatile int* quit_flag;
-    volatile u64* pf_pos;   // bytes of the weight stream the producer lane has issued so far (read by the prefetch lane)
 };
 
 struct Ctx {
@@ -530,41 +529,17 @@ __device__ __forceinline__ void gemv_mma(Ctx& c, int r0, int r1, int rb, const f
 }
 
 // ---- producer ----------------------------------------------------------------------------------------
-// A second lane of the producer warp walks the same chunk sequence ahead of the copies and asks the
-// L2 for each chunk (`cp.async.bulk.prefetch.L2`), at most `window` bytes ahead of the issuing lane,
-// so that HBM keeps streaming while the ring is full and the consumers wait for activations
-// (the reference's second cursor: qwen3.5-0.8b/csrc/megakernel.cu:171-193).
+// (The reference also runs a second cursor that asks the L2 for chunks ahead of the copies,
+// qwen3.5-0.8b/csrc/megakernel.cu:171-193.  Measured on B200 it gained nothing at any distance -- the ring is
+// never what the consumers wait for -- and its bookkeeping in this loop cost a few per cent, so it is not here.)
 template <int NS>
 struct Producer {
     Ctx& c;
     u64 policy;
     uint32_t n = 0;      // chunks issued
     bool stop = false;
-    bool pf = false;     // this lane only prefetches
-    u64 bytes = 0;       // bytes issued (or prefetched) so far
-    u64 window = 0;
 
-    __device__ Producer(Ctx& c_, bool prefetch = false, long long pf_window = 0) : c(c_), pf(prefetch), window((u64)pf_window) {
-        policy = policy_evict_first();
-    }
-
-    // Prefetch lane: ask the L2 for one chunk once the issuing lane is within `window` bytes of it.
-    __device__ void prefetch_chunk(const uint8_t* src, uint32_t nbytes) {
-        const u64 end = bytes + nbytes;
-        bytes = end;
-        uint32_t it = 0;
-        for (;;) {
-            const u64 issued = *c.sm.pf_pos;
-            if (issued >= end) return;                       // the copy itself is already under way
-            if (end <= issued + window) break;
-            if (*c.sm.quit_flag || *c.sm.abort_flag || ++it > (1u << 24)) {
-                stop = true;
-                return;
-            }
-            __nanosleep(100);
-        }
-        bulk_prefetch_l2(src, nbytes);
-    }
+    __device__ Producer(Ctx& c_) : c(c_) { policy = policy_evict_first(); }
 
     // Issue this CTA's slice of one matrix, one ring slot at a time.
     __device__ void stream(const uint8_t* w, int rows, int unit, int row_bytes) {
@@ -574,11 +549,6 @@ struct Producer {
         const int rpc = SLOT_BYTES / row_bytes;
         for (int base = r0; base < r1; base += rpc) {
             const int nr = min(rpc, r1 - base);
-            if (pf) {
-                prefetch_chunk(w + (size_t)base * row_bytes, (uint32_t)nr * (uint32_t)row_bytes);
-                if (stop) return;
-                continue;
-            }
             const int slot = (int)(n % NS);
             if (n >= NS) {
                 const uint32_t par = ((n / NS) - 1) & 1;
@@ -599,15 +569,11 @@ struct Producer {
             bulk_load(c.sm.ring + (size_t)slot * SLOT_BYTES, w + (size_t)base * row_bytes, bytes, &c.sm.full[slot],
                       policy);
             n++;
-            this->bytes += bytes;
-            *c.sm.pf_pos = this->bytes;
         }
     }
 
     // Before the CTA may exit, every copy that was issued must have landed.
     __device__ void drain() {
-        *c.sm.pf_pos = ~0ull;       // lets the prefetch lane run to the end of its walk without waiting
-        if (pf) return;
         const uint32_t first = n > NS ? n - NS : 0;
         for (uint32_t i = first; i < n; i++) {
             Spin s;
@@ -631,8 +597,8 @@ struct Producer {
 // needed; a speculative cycle continues with the draft head's fusion projection, its decoder layer
 // and the draft vocabulary rows.  Consumers consume exactly this sequence.
 template <class S, bool Q8, int T>
-__device__ void producer_main(Ctx& c, const Params& P, const Args& A, bool prefetch) {
-    Producer<Geo<T>::NS> pr(c, prefetch, A.pf_bytes);
+__device__ void producer_main(Ctx& c, const Params& P, const Args& A) {
+    Producer<Geo<T>::NS> pr(c);
     constexpr int WB = Q8 ? 1 : 2;  // bytes per weight
     auto layer = [&](const LayerP& L) {
         pr.stream(L.w_in, L.kind ? S::ATT_IN : S::GDN_IN, 1, S::HID * WB);
@@ -1613,7 +1579,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
         c.sm.xscale_s = reinterpret_cast<float*>(p); p += 8;
         c.sm.abort_flag = reinterpret_cast<volatile int*>(p); p += 4;
         c.sm.quit_flag = reinterpret_cast<volatile int*>(p); p += 4;
-        c.sm.pf_pos = reinterpret_cast<volatile u64*>(p); p += 8;
         c.sm.act_s = reinterpret_cast<float*>(p); p += SPEC_T * DOWN_K * 4;
         c.sm.mix_s = reinterpret_cast<float*>(p); p += SPEC_T * DOWN_K * 4;
     }
@@ -1630,7 +1595,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
         }
         *c.sm.abort_flag = 0;
         *c.sm.quit_flag = 0;
-        *c.sm.pf_pos = 0;
         c.sm.xscale_s[0] = c.sm.xscale_s[1] = 1.0f;
         fence_barrier_init();
         fence_proxy_async();
@@ -1639,8 +1603,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_kernel(const __grid_consta
     __syncthreads();
 
     if (c.warp == NCW) {
-        if (c.lane == 0) producer_main<S, Q8, T>(c, P, A, false);
-        else if (c.lane == 1 && A.pf_bytes > 0) producer_main<S, Q8, T>(c, P, A, true);
+        if (c.lane == 0) producer_main<S, Q8, T>(c, P, A);
         return;
     }
 

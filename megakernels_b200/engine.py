@@ -32,7 +32,6 @@ from .quant import is_gemv_weight, quantize_int8_rows, roundtrip_int8_rows
 # Steps per launch.  A step takes well under a millisecond on a B200, so this only bounds the size
 # of the per-launch output buffers.
 MAX_STEPS_PER_LAUNCH = 1024
-PF_BYTES = 0
 
 
 def rope_tables(cfg, max_seq, device):
@@ -44,7 +43,7 @@ def rope_tables(cfg, max_seq, device):
 
 
 class Megakernel:
-    def __init__(self, model, max_seq=8192, device="cuda", pf_bytes=PF_BYTES, quant="bf16", mtp=False,
+    def __init__(self, model, max_seq=8192, device="cuda", quant="bf16", mtp=False,
                  draft_vocab=0, kv_dtype="fp32", spin_limit_ms=2000, draft_ids=None, batch=1, pack_device=None):
         """`mtp` loads the multi-token-prediction head for speculative decoding (`run_spec`); its drafts
         come from the `draft_vocab` most frequent tokens listed in `draft_ids` (0: the whole vocabulary).
@@ -62,7 +61,7 @@ class Megakernel:
             raise RuntimeError("the decode megakernel needs a CUDA device; there is no CPU path")
         self.batch = batch
         self.lib = _lib.load()
-        self.quant, self.kv_dtype, self.pf_bytes = quant, kv_dtype, pf_bytes
+        self.quant, self.kv_dtype = quant, kv_dtype
         self.spin_limit_ns = int(spin_limit_ms * 1e6)
         device = torch.device(device)
         if device.index is None:
@@ -345,7 +344,7 @@ class Megakernel:
         dev = self.device
         info = torch.zeros(8, dtype=torch.int32, device=dev)
         stamps = torch.zeros(n_steps + 1, dtype=torch.int64, device=dev) if timing else None
-        args = dict(n_steps=n_steps, start_pos=self.pos, epoch_base=self.epoch, grid=self.grid, pf_bytes=self.pf_bytes,
+        args = dict(n_steps=n_steps, start_pos=self.pos, epoch_base=self.epoch, grid=self.grid,
                     spin_limit_ns=self.spin_limit_ns, out_info=info.data_ptr(), step_ts=stamps.data_ptr() if timing else 0)
         args.update(fields)
         args.update({name: (t.data_ptr() if t is not None else 0) for name, t in buffers.items()})
@@ -465,7 +464,7 @@ class Megakernel:
                            inv_temperature=1.0 / temperature if temperature > 0 else 0.0, n_stop=len(stop_ids),
                            prof_step=prof_step, stop_ids=stops.data_ptr(), tokens_out=out.data_ptr(),
                            logits_out=ptr(logits), step_ts=ptr(ts), out_info=info.data_ptr(), prof=ptr(prof),
-                           spin_limit_ns=self.spin_limit_ns, pf_bytes=self.pf_bytes)
+                           spin_limit_ns=self.spin_limit_ns)
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(self.lib.mk_launch_batch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
         self.launches += 1

@@ -49,8 +49,8 @@ def test_field_order_matches_header(lib_built):
 def test_struct_layouts(lib_built):
     assert ctypes.sizeof(_lib.ModelDesc) == 40
     a = _lib.LaunchArgs
-    assert a.stop_ids.offset == 40 and a.prof_step.offset == 96 and a.pf_bytes.offset == 104
-    assert a.spec.offset == 120 and a.spec_out.offset == 136 and ctypes.sizeof(a) == 152
+    assert a.stop_ids.offset == 40 and a.prof_step.offset == 96 and a.spin_limit_ns.offset == 104
+    assert a.spec.offset == 112 and a.spec_out.offset == 128 and ctypes.sizeof(a) == 144
 
 
 def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
@@ -58,7 +58,7 @@ def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
     import shutil
     import subprocess
     b = _lib.BatchArgs
-    assert ctypes.sizeof(b) == 200 and b.pf_bytes.offset == 192 and b.n_total.offset == 40 and b.batch.offset == 104 and b.stop_ids.offset == 136
+    assert ctypes.sizeof(b) == 192 and b.spin_limit_ns.offset == 184 and b.n_total.offset == 40 and b.batch.offset == 104 and b.stop_ids.offset == 136
     assert _lib.query("MAX_BATCH") == _lib.MAX_BATCH == 8
     assert _lib.query("BATCH_SMEM_BYTES") <= 227 * 1024
     if not shutil.which("gcc"):
@@ -71,7 +71,7 @@ def test_batch_args_layout_matches_the_header(lib_built, tmp_path):
     exe = tmp_path / "layout"
     subprocess.run(["gcc", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()]
-    assert got == [200, 40, 104, 136, ctypes.sizeof(_lib.LaunchArgs), ctypes.sizeof(_lib.ModelDesc)]
+    assert got == [192, 40, 104, 136, ctypes.sizeof(_lib.LaunchArgs), ctypes.sizeof(_lib.ModelDesc)]
 
 
 def test_constants(lib_built):
