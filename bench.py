@@ -42,6 +42,10 @@ PROMPT, GENERATE = 512, 512               # configuration 2 (0.8B int8)
 # context, the KV part does): decode_kernel at batch 1, batch_kernel at batch 8.
 NCU_DRAM_BYTES_PER_STEP = {1: (11.604932e9 + 394.075904e6) / 16, 8: (13.618422e9 + 3.158837e9) / 16}
 NCU_CONTEXT = 64
+# stage_kernel: dram bytes of the captured launch (8 of 64 layers, vocabulary 32768, batch 8, 8 steps) over the
+# algorithmic bytes of that launch; the bench scales its own algorithmic bytes by it (the capture of the full model
+# would hold 20 GB on the device under the profiler)
+NCU_STAGE_TRAFFIC_RATIO = (17.065627e9 + 2.102116e9) / 18.072158208e9
 
 
 def measured_peak_gbs():
@@ -216,7 +220,9 @@ class Cfg3:
                 "bytes_per_decode_step_per_gpu": bps,
                 "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": 4 * self.batch,
                         "d2h_bytes_per_step": 4 * self.batch * self.generate},
-                "roofline": roofline(bps * self.generate, launch_s, "mks::stage_kernel",
+                "roofline": roofline(bps * self.generate, launch_s, "mks::stage_kernel", traffic=NCU_STAGE_TRAFFIC_RATIO * bps * self.generate,
+                                     traffic_note="ncu capture of an 8-layer, vocabulary-32768, batch-8 launch (traffic / algorithmic bytes = "
+                                                  f"{NCU_STAGE_TRAFFIC_RATIO:.3f}), scaled to this launch by its algorithmic bytes",
                                      note="per GPU: this rank's weight shard, DeltaNet state and KV cache; at TP > 1 the step also "
                                           "waits for the peers' partial sums")}
 
