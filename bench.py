@@ -40,7 +40,7 @@ PROMPT, GENERATE = 512, 512               # configuration 2 (0.8B int8)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per decode step, from the ncu captures
 # summarised under profiles/ (short launches at a 64-token context; the weight part does not grow with
 # context, the KV part does): decode_kernel at batch 1, batch_kernel at batch 8.
-NCU_DRAM_BYTES_PER_STEP = {1: (11.604932e9 + 394.075904e6) / 16, 8: (13.618422e9 + 3.158837e9) / 16}
+NCU_DRAM_BYTES_PER_STEP = {1: (11.566718e9 + 328.967936e6) / 16, 8: (13.616476e9 + 2.931580e9) / 16}
 NCU_CONTEXT = 64
 # stage_kernel: dram bytes of the captured launch (8 of 64 layers, vocabulary 32768, batch 8, 8 steps) over the
 # algorithmic bytes of that launch; the bench scales its own algorithmic bytes by it (the capture of the full model
@@ -197,10 +197,12 @@ class Cfg3:
         if sampler:
             sampler.start()
         barrier()
+        torch.cuda.profiler.start()        # a profiler given --profile-from-start off sees the timed region only
         wall0 = time.perf_counter()
         events = [self.one_step() for _ in range(steps)]
         barrier()
         wall_s = time.perf_counter() - wall0
+        torch.cuda.profiler.stop()
         clocks = sampler.stop() if sampler else None
         self.eng.check()
         kernel_ms = sum(a.elapsed_time(b) for a, b in events)
@@ -346,6 +348,7 @@ def measure(mk, batch, prompts, args, spec=False):
     assert len(ids) == batch and all(len(x) >= GENERATE for x in ids)
     torch.cuda.synchronize()
     launches0 = mk.launches
+    torch.cuda.profiler.start()            # a profiler given --profile-from-start off sees the timed region only
     wall0 = time.perf_counter()
     kernel_events, step_ns = [], []
     for _ in range(args.steps):
@@ -355,6 +358,7 @@ def measure(mk, batch, prompts, args, spec=False):
             step_ns += mk.last_step_ns
     torch.cuda.synchronize()
     wall_s = time.perf_counter() - wall0
+    torch.cuda.profiler.stop()
     kernel_ms = [a.elapsed_time(b) for a, b in kernel_events]      # launch + readback of one generation
     return sum(kernel_ms), wall_s, mk.launches - launches0, step_ns, info
 
@@ -382,23 +386,28 @@ def report(mk, batch, kernel_ms, wall_s, step_ns, args):
     }
 
 
-def measure_cfg2(args, device):
+def measure_cfg2(args, device, legs=("batch8", "batch1", "spec")):
     """int8 weights: batch 8, batch 1, and speculative cycles with the MTP draft head at batch 1."""
     from megakernels_b200.engine import Megakernel
     from megakernels_b200.synth import make_mtp_weights, make_prompt
     cfg, w, prompt = build_model("int8")
     prompts = [prompt] + [make_prompt(cfg, PROMPT, seed=1000 + j) for j in range(1, 8)]
     mk = Megakernel((cfg, w), max_seq=PROMPT + GENERATE + 64, quant="int8", kv_dtype=args.kv_dtype, device=device, batch=8)
-    k8, w8, launches, s8, _ = measure(mk, 8, prompts, args)
     out = {"workload": f"qwen3.5-0.8b hybrid ({cfg.n_layers} layers, hidden 1024, vocab {cfg.vocab}), int8 per-channel weights, "
-                       f"{PROMPT}-token prompt + {GENERATE} greedy steps per launch, kv {args.kv_dtype}",
-           "batch8": report(mk, 8, k8, w8, s8, args)}
-    mk.reset()
-    k1, w1, l1, s1, _ = measure(mk, 1, prompts, args)
-    out["batch1"] = report(mk, 1, k1, w1, s1, args)
-    launches += l1
+                       f"{PROMPT}-token prompt + {GENERATE} greedy steps per launch, kv {args.kv_dtype}"}
+    launches, k1 = 0, None
+    if "batch8" in legs:
+        k8, w8, launches, s8, _ = measure(mk, 8, prompts, args)
+        out["batch8"] = report(mk, 8, k8, w8, s8, args)
+        mk.reset()
+    if "batch1" in legs:
+        k1, w1, l1, s1, _ = measure(mk, 1, prompts, args)
+        out["batch1"] = report(mk, 1, k1, w1, s1, args)
+        launches += l1
     del mk
     torch.cuda.empty_cache()
+    if "spec" not in legs:
+        return out, launches, (cfg, w, prompt)
     # speculative cycles (draft head proposes, one T = 2 pass verifies): cost of a cycle beside the plain step
     try:
         mtp = make_mtp_weights(cfg, 0)
@@ -406,7 +415,7 @@ def measure_cfg2(args, device):
         ks, ws, ls, _, info = measure(mk, 1, prompts, args, spec=True)
         cycles = max(1, int(info.get("cycles", GENERATE)))
         out["spec"] = {"ms_per_cycle": ks / args.steps / cycles, "tokens_per_cycle": GENERATE / cycles,
-                       "cycles_per_launch": cycles, "plain_step_ms": k1 / args.steps / GENERATE,
+                       "cycles_per_launch": cycles, "plain_step_ms": k1 / args.steps / GENERATE if k1 else None,
                        "value": args.steps * GENERATE / (ks / 1e3), "unit": "tok/s",
                        "note": "random weights: the draft is almost never accepted, so tokens/cycle is about 1; ms/cycle against the "
                                "plain step is what the T = 2 pass and the draft head cost"}
@@ -438,6 +447,7 @@ def measure_cfg1(args, device):
 
 
 def main():
+    global PROMPT, GENERATE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
@@ -450,6 +460,10 @@ def main():
     ap.add_argument("--cfg3-prompt", type=int, default=CFG3_PROMPT, help="shrink the case (profiling only)")
     ap.add_argument("--cfg3-generate", type=int, default=CFG3_GENERATE, help="shrink the case (profiling only)")
     ap.add_argument("--no-riders", action="store_true", help="only the headline measurement")
+    ap.add_argument("--only", default=None, choices=["cfg2", "cfg2_batch8", "cfg2_batch1", "cfg1"],
+                    help="run one rider alone and print its object (profiling only; not a bench line)")
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="context of the 0.8B int8 riders (profiling only)")
+    ap.add_argument("--generate", type=int, default=GENERATE, help="steps per launch of the 0.8B int8 riders (profiling only)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -461,6 +475,15 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the decode megakernels have no CPU path")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    if args.only:
+        PROMPT, GENERATE = args.prompt, args.generate
+        if args.only == "cfg1":
+            obj, _ = measure_cfg1(args, device)
+        else:
+            legs = ("batch8", "batch1", "spec") if args.only == "cfg2" else (args.only.split("_")[1],)
+            obj, _, _ = measure_cfg2(args, device, legs)
+        print(json.dumps({"only": args.only, "prompt": PROMPT, "generate": GENERATE, **obj}))
+        return
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
