@@ -14,9 +14,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, os.environ.get("MK_B200_LIBNAME", "libmk_b200.so"))
-SOURCES = ["mk_api.cu", "mk_stage_api.cu"]
+SOURCES = ["mk_api.cu", "mk_stage_api.cu", "mk_umma.cu"]
 HEADERS = ["mk_common.h", "mk_device.cuh", "mk_decode.cuh", "mk_batch.cuh", "mk_stage.cuh", "mk_stage_ops.cuh",
-           os.path.join("..", "..", "include", "mk_b200.h"), os.path.join("..", "..", "include", "mk_stage.h")]
+           os.path.join("..", "..", "include", "mk_b200.h"), os.path.join("..", "..", "include", "mk_stage.h"),
+           os.path.join("..", "..", "include", "mk_umma.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--fmad=false",
               "-Xcompiler", "-fPIC"]
 
