@@ -4,7 +4,7 @@
 //   warp 4, 8 lanes:  producers.  They stream this CTA's chunks (8704 bytes: 128 rows x 128 columns of e2m1 pairs and
 //                     their scale atom) into a shared-memory ring with cp.async.bulk.
 //   warp 5, one lane: issuer.  Per chunk: tcgen05.cp of the scale atom into tensor memory, two tcgen05.mma
-//                     (kind::mxf4, block scaled, M = 128, N = 8 x pieces, K = 64), tcgen05.commit onto the
+//                     (kind::mxf4, block scaled, M = 128, N = pieces x sequences rounded up to 8, K = 64), tcgen05.commit onto the
 //                     slot's `empty` barrier; after the last chunk of a row block a commit onto `d_full`.
 //   warps 0-3:        epilogue.  tcgen05.ld of the 128 x N accumulators (lane = row), sum over the digit
 //                     planes, then either the final store or a partial tile plus a counter; the CTA that
@@ -44,7 +44,7 @@ struct Args {
     unsigned long long* prof;
     long long spin_limit_ns;
     int rows, k, batch, pieces, splits, round_bf16;
-    int row_blocks, cps, ks, n, depth, amax;
+    int row_blocks, cps, ks, n, depth, amax, mp;       // mp: rows of the B operand per digit plane (1, 2, 4, 8 >= batch)
 };
 
 struct Bars {
@@ -136,7 +136,7 @@ __host__ __device__ inline int arrivals(int rb, int grid, int splits, int cps, l
 // ---- input digit planes ------------------------------------------------------------------------------------------
 // Four neighbouring lanes take one sequence's 32-column block, eight values each: q = round(|x| 2^(2P - 1 - e)) with
 // e the exponent of the block's largest value, digit p = (q >> 2p) & 3 stored as the e2m1 code of digit / 2 (codes
-// 0..3 are 0, 0.5, 1, 1.5) with block scale 2^(e + 2 - 2P + 2p).  Plane p of sequence m is row p * 8 + m of the B operand.
+// 0..3 are 0, 0.5, 1, 1.5) with block scale 2^(e + 2 - 2P + 2p).  Plane p of sequence m is row p * mp + m of the B operand.
 __device__ void stage_planes(const Args& A, uint8_t* xs, uint8_t* sfb, int slice) {
     const int P = A.pieces, nblk = A.ks / 32;
     for (int i = threadIdx.x * 16; i < A.n * A.ks / 2; i += NT * 16) *reinterpret_cast<uint4*>(xs + i) = make_uint4(0u, 0u, 0u, 0u);
@@ -179,7 +179,7 @@ __device__ void stage_planes(const Args& A, uint8_t* xs, uint8_t* sfb, int slice
             uint32_t word = sign;
 #pragma unroll
             for (int i = 0; i < 8; i++) word |= ((q[i] >> (2 * p)) & 3u) << (4 * i);
-            const int n = p * 8 + m;
+            const int n = p * A.mp + m;
             *reinterpret_cast<uint32_t*>(xs + ((size_t)(n >> 3) * nblk + kb) * 128 + (n & 7) * 16 + quarter * 4) = word;
             if (quarter == 0) sfb[(kb >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (kb & 3)] = (uint8_t)(127 + e + 2 - 2 * P + 2 * p);
         }
@@ -334,13 +334,25 @@ __global__ void __launch_bounds__(NT, 1) gemv_kernel(const Args A) {
             if (prof && threadIdx.x == 0 && qend == sh.hi) prof[4] = gtime();
             float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             const uint32_t td = tbase + T_D + buf * D_COLS + ((uint32_t)(warp * 32) << 16);
-            for (int p = 0; p < A.pieces; p++) {
+            // column n = plane * mp + sequence; the planes are added least significant first
+            for (int c = 0; c < A.n; c += 8) {
                 uint32_t r[8];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(td + p * 8));
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(td + c));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (A.mp == 8) {
 #pragma unroll
-                for (int m = 0; m < 8; m++) v[m] += __uint_as_float(r[m]);       // least significant plane first
+                    for (int j = 0; j < 8; j++) v[j] += __uint_as_float(r[j]);
+                } else if (A.mp == 4) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j & 3] += __uint_as_float(r[j]);
+                } else if (A.mp == 2) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j & 1] += __uint_as_float(r[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[0] += __uint_as_float(r[j]);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -467,7 +479,8 @@ extern "C" int mk_umma_gemv(const mk_umma_args* a) {
     A.row_blocks = (a->rows + MKU_ROWS - 1) / MKU_ROWS;
     A.ks = a->k / a->splits;
     A.cps = A.ks / MKU_CHUNK_K;
-    A.n = 8 * a->pieces;
+    A.mp = a->batch > 4 ? 8 : (a->batch > 2 ? 4 : a->batch);
+    A.n = (a->pieces * A.mp + 7) / 8 * 8;
     A.amax = max_arrivals(A.row_blocks, A.cps, a->splits, grid);
     if (A.amax > 1 && !a->part) return ufail(MK_ERR_BADARG, "mk_umma_gemv: row blocks are shared by up to %d CTAs and there is no scratch", A.amax);
     if (cudaSetDevice(a->device) != cudaSuccess) return ufail(MK_ERR_CUDA, "mk_umma_gemv: cudaSetDevice(%d) failed", a->device);

@@ -197,12 +197,13 @@ def main(argv=None):
     ap.add_argument("--shape", action="append", default=None, help="rows,k (default: the 27B gate/up and down projections)")
     ap.add_argument("--batch", type=int, action="append", default=None)
     ap.add_argument("--pieces", type=int, default=6)
+    ap.add_argument("--splits", type=int, default=0, help="K slices (0: as few as fit)")
     ap.add_argument("--reps", type=int, default=20)
     a = ap.parse_args(argv)
     shapes = [tuple(int(v) for v in s.split(",")) for s in (a.shape or ["34816,5120", "5120,17408"])]
     for rows, k in shapes:
         for batch in a.batch or [1, 8]:
-            print(json.dumps(measure(rows, k, batch, pieces=a.pieces, reps=a.reps)), flush=True)
+            print(json.dumps(measure(rows, k, batch, pieces=a.pieces, splits=a.splits or None, reps=a.reps)), flush=True)
 
 
 if __name__ == "__main__":
