@@ -446,6 +446,22 @@ def measure_cfg1(args, device):
         PROMPT, GENERATE = saved
 
 
+def measure_umma(device):
+    """The block-scaled tcgen05 GEMV (`mk_umma_gemv`) on configuration 3's two largest projections, one launch per
+    product, weights rotated through copies that exceed L2: what the tensor-memory path does with the matrices
+    that the stage kernel streams through `mma.sync` (not part of `value`: the stage machine does not call it)."""
+    from megakernels_b200.stage import umma
+    peak, kind = measured_peak_gbs()
+    rows = []
+    for name, (r, k) in (("gate_up 34816x5120", (34816, 5120)), ("down 5120x17408", (5120, 17408))):
+        for batch in (8, 1):
+            m = umma.measure(r, k, batch, pieces=6, reps=20)
+            rows.append({"matrix": name, "batch": batch, "us_per_launch": m["us_per_launch"], "GBs": m["gbs"],
+                         "frac": m["gbs"] / peak, "peak_kind": f"of {kind}", "phases_us": m["phases_us"], "splits": m["splits"]})
+    return {"kernel": "mku::gemv_kernel (tcgen05.mma kind::mxf4 block_scale, accumulators and scales in tensor memory)",
+            "launches": 4 * 24, "cases": rows}
+
+
 def main():
     global PROMPT, GENERATE
     ap = argparse.ArgumentParser()
@@ -534,9 +550,13 @@ def main():
         "clocks": clocks, "e2e": head["e2e"], "gpu_launches": launches, "roofline": head["roofline"],
     }
     out.update(riders)
+    if world == 1 and not args.no_riders and full_size:
+        out["gpu_launches"] += 4 * 24
     if world == 1 and not args.no_riders:
         from megakernels_b200 import bw
         out["roofline"]["bw_probe_gbs"] = {m: round(bw.measure(m, gib=2.0, reps=3, device=device), 1) for m in bw.MODES}
+    if world == 1 and not args.no_riders and full_size:
+        out["tcgen05_mxfp4_gemv"] = measure_umma(device)
     if world == 1 and not args.no_cpu_baseline:
         rate, step_s, sample = cfg3_cpu_rate(args.batch, reps=1)
         out["cpu_baseline"] = {"value": rate, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
