@@ -253,6 +253,11 @@ typedef struct mk_stage_args {
     int32_t xs_bytes;        /* shared staging area the program needs (mk_stage_scratch_bytes; 0: the maximum);
                                 what it leaves of the SM's shared memory becomes ring slots (2..4 per warp) */
     int32_t n_tokens_in;
+    uint64_t row_valid;      /* optional i32[batch]: 0 marks a padding row for this launch.  Its recurrent state, conv
+                                history, KV cache and position stay as they are and it selects no routed expert;
+                                what the launch writes to its activations, logits and token is undefined (the
+                                reference's `valid` / slot < 0 rows: qwen3.6-35b-a3b-gfx942/mk/runner.py:187-192,
+                                qwen3.8-27b-gfx942/mk/kernel.py:25-27)                                           */
 } mk_stage_args;
 
 /* Launch.  Asynchronous on `stream`. */

@@ -65,6 +65,7 @@ struct Args {
     unsigned long long ar_base;
     const int* tokens_in;    // [n_tokens_in][M] forced inputs of the first steps, or null
     int n_tokens_in;
+    const int* row_valid;    // [M] 0 = padding row, or null
     int prof_cta;            // the CTA whose timestamps go to `prof`
     int xs_bytes;            // input staging / mixer scratch area of this launch
     int ring_depth;          // ring slots per consumer warp
@@ -87,6 +88,7 @@ struct Shared {
     float rstd[8];                 // 1/rms of the staged input
     int tok_s[8];
     int pos_s[8];
+    int valid_s[8];                // 0: a padding row of this launch
     int r_ids[64];                 // [8][8] routed expert ids per sequence
     float r_w[64];                 // [8][8] routing weights
     float coef[MAX_GROUPS * 8];    // weight of group g for sequence m

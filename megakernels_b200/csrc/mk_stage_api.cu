@@ -180,6 +180,7 @@ extern "C" int mk_stage_launch(const mk_stage_args* a, void* stream) {
     A.ar_base = a->ar_base;
     A.tokens_in = reinterpret_cast<const int*>(a->tokens_in);
     A.n_tokens_in = a->tokens_in ? a->n_tokens_in : 0;
+    A.row_valid = reinterpret_cast<const int*>(a->row_valid);
     A.prof_cta = a->prof_cta;
     // shared memory: the staging area the program needs (the caller computes it with mk_stage_scratch_bytes), the rest ring slots
     const int xs = a->xs_bytes > 0 ? (a->xs_bytes + 127) / 128 * 128 : XS_BYTES;

@@ -125,6 +125,7 @@ __device__ __noinline__ void gdn_stage(Shared& S, Mut& mu, const mk_stage_desc& 
 #pragma unroll 1
     for (int task = cta_(); task < ntask; task += grid_()) {
         const int m = task / nvh, h = task % nvh, kh = h / rep;
+        if (!S.valid_s[m]) continue;                           // a padding row keeps its state (uniform over the CTA)
         const int pos = S.pos_s[m];
         const float* y = Y + (size_t)m * d.i[MKS_I_Y_STRIDE];
         float* S = ssm + ((size_t)(m * nvh + h) * 128) * 128;
@@ -310,6 +311,7 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
 #pragma unroll 1
     for (int task = cta_(); task < ntask; task += grid_()) {
         const int ch = task % NCH, kvh = (task / NCH) % NKV, m = task / (NCH * NKV);
+        if (!S.valid_s[m]) continue;                           // a padding row reads and writes no KV (uniform over the CTA)
         const int pos = S.pos_s[m], n = pos + 1;
         const int lo = window ? max(0, n - window) : 0;
         const int first = lo + ch * CP;
@@ -585,7 +587,7 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
 #pragma unroll 1
     for (int i = tid_(); i < MAX_GROUPS * 8; i += NCT) S.coef[i] = 0.f;
     consumer_sync();
-    if (warp_() < S.A.M) {
+    if (warp_() < S.A.M && S.valid_s[warp_()]) {              // a padding row selects no expert
         const int m = warp_();
         float v[8];
         bool used[8];
@@ -640,7 +642,7 @@ __device__ __noinline__ void route_stage(Shared& S, Mut& mu, const mk_stage_desc
         return r + __popc(S.gmask[id >> 5] & ((1u << (id & 31)) - 1u));
     };
     if (tid_() < E && (S.gmask[tid_() >> 5] >> (tid_() & 31)) & 1u) S.glist[rank_of(tid_())] = tid_();
-    if (warp_() < S.A.M && lane_() < topk) S.coef[rank_of(S.r_ids[warp_() * 8 + lane_()]) * 8 + warp_()] = S.r_w[warp_() * 8 + lane_()];
+    if (warp_() < S.A.M && S.valid_s[warp_()] && lane_() < topk) S.coef[rank_of(S.r_ids[warp_() * 8 + lane_()]) * 8 + warp_()] = S.r_w[warp_() * 8 + lane_()];
     int U = 0;
 #pragma unroll 1
     for (int w = 0; w < 8; w++) U += __popc(S.gmask[w]);
@@ -753,6 +755,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
         S.rstd[tid_()] = 1.f;
         S.tok_s[tid_()] = 0;
         S.pos_s[tid_()] = tid_() < A_in.M ? A_in.pos[tid_()] : 0;
+        S.valid_s[tid_()] = tid_() < A_in.M && (!A_in.row_valid || A_in.row_valid[tid_()] != 0);
     }
     __syncthreads();
     const Args& A = S.A;
@@ -770,7 +773,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
     bool failed = false;
 #pragma unroll 1
     for (int step = 0; step < A.n_steps && !failed; step++) {
-        if (tid_() < S.A.M) S.pos_s[tid_()] = A.pos[tid_()] + step;
+        if (tid_() < S.A.M) S.pos_s[tid_()] = A.pos[tid_()] + (S.valid_s[tid_()] ? step : 0);
         consumer_sync();
 #pragma unroll 1
         for (int si = 0; si < A.n_stages; si++) {
@@ -820,7 +823,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) stage_kernel(const __grid_constan
             if (A.tokens_out) A.tokens_out[(size_t)(A.n_steps - 1) * S.A.M + tid_()] = S.tok_s[tid_()];
         }
     }
-    if (!failed && cta_() == 0 && tid_() < S.A.M) A.pos[tid_()] = A.pos[tid_()] + A.n_steps;
+    if (!failed && cta_() == 0 && tid_() < S.A.M && S.valid_s[tid_()]) A.pos[tid_()] = A.pos[tid_()] + A.n_steps;
 }
 
 }  // namespace mks

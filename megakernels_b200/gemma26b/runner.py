@@ -167,10 +167,20 @@ class Engine:
     def reset(self):
         self.rt.reset()
 
-    def step(self, tok: torch.Tensor, stream=None):
+    def step(self, tok: torch.Tensor, valid=None, stream=None):
         self.rt.tok[: self.M].copy_(tok.to(device=self.device, dtype=torch.int32))
-        self.rt.launch(1, stream=stream)
+        self.rt.launch(1, stream=stream, row_valid=self._rows(valid))
         return self.logits
+
+    def _rows(self, valid):
+        """valid[m] False marks a padding row of one step (the reference's `valid` / slot < 0 rows): its state, caches
+        and position are left alone, it selects no routed expert, and its logits are undefined."""
+        if valid is None:
+            return None
+        if not hasattr(self, "rowv"):
+            self.rowv = torch.ones(8, dtype=torch.int32, device=self.device)
+        self.rowv[: self.M].copy_(torch.as_tensor(valid).to(device=self.device, dtype=torch.int32))
+        return self.rowv
 
     def generate(self, tok: torch.Tensor, n_steps: int):
         if not self.lm_head:

@@ -54,7 +54,8 @@ class StageArgs(ctypes.Structure):
                 ("status", ctypes.c_uint64), ("spin_limit_ns", ctypes.c_int64), ("prof", ctypes.c_uint64),
                 ("tp", ctypes.c_int32), ("rank", ctypes.c_int32), ("mailbox", ctypes.c_uint64 * MAX_RANKS),
                 ("ar_base", ctypes.c_uint64), ("grid", ctypes.c_int32), ("prof_cta", ctypes.c_int32),
-                ("tokens_in", ctypes.c_uint64), ("xs_bytes", ctypes.c_int32), ("n_tokens_in", ctypes.c_int32)]
+                ("tokens_in", ctypes.c_uint64), ("xs_bytes", ctypes.c_int32), ("n_tokens_in", ctypes.c_int32),
+                ("row_valid", ctypes.c_uint64)]
 
 
 STAGE_EXPORTS = ["mk_stage_launch", "mk_stage_validate", "mk_stage_count", "mk_stage_query", "mk_stage_scratch_bytes", "mk_sync_probe", "mk_peer_alloc", "mk_peer_open",

@@ -169,7 +169,7 @@ class Runtime:
             if t.dtype == torch.int32:
                 t.zero_()
 
-    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None, prof_cta=0, tokens_in=None):
+    def launch(self, n_steps=1, tokens_out=None, prof=None, stream=None, n_stages=None, prof_cta=0, tokens_in=None, row_valid=None):
         """`n_stages` runs only a prefix of the program (one step; for stage-by-stage checks in tests)."""
         full = n_stages is None
         n_stages = self.n_stages if full else n_stages
@@ -181,7 +181,8 @@ class Runtime:
                         prof=prof.data_ptr() if prof is not None else 0, tp=self.tp, rank=self.rank, ar_base=self.ar_base,
                         grid=self.grid, prof_cta=prof_cta, xs_bytes=self.xs_bytes,
                         tokens_in=tokens_in.data_ptr() if tokens_in is not None else 0,
-                        n_tokens_in=tokens_in.shape[0] if tokens_in is not None else 0)
+                        n_tokens_in=tokens_in.shape[0] if tokens_in is not None else 0,
+                        row_valid=row_valid.data_ptr() if row_valid is not None else 0)
         if self.tp > 1:
             for r in range(self.tp):
                 a.mailbox[r] = self.mailbox.addresses[r]

@@ -141,6 +141,40 @@ def test_serving_cache_layout_gives_the_same_bits(model):
         Engine(PK, M, maxlen=64, kv_layout="serving", kv_block=24)
 
 
+def test_a_padding_row_keeps_its_state_and_leaves_the_other_rows_alone(model):
+    """`valid[m] = False` for one step: rows 0 and 2 compute what they would have, row 1's DeltaNet state, conv history,
+    KV cache and position stay; fed the missed token in the next step, row 1 catches up bitwise."""
+    W, PK = model
+    M = 3
+    prompts = [make_prompt(SMALL.vocab, 8, seed=80 + j) for j in range(M)]
+    a, b = Engine(PK, M, maxlen=64), Engine(PK, M, maxlen=64)
+    for t in range(5):
+        tok = torch.tensor([p[t] for p in prompts], device="cuda")
+        a.step(tok)
+        b.step(tok)
+    snap = {"ssm": b.ssm.clone(), "conv": b.conv.clone(), "k": b.k_cache.clone(), "v": b.v_cache.clone()}
+    tok = torch.tensor([p[5] for p in prompts], device="cuda")
+    la = a.step(tok).clone()
+    lb = b.step(tok, valid=[True, False, True]).clone()
+    b.check()
+    assert torch.equal(la[[0, 2]], lb[[0, 2]])
+    assert b.pos[:M].tolist() == [6, 5, 6]
+    assert torch.equal(b.ssm[:, 1], snap["ssm"][:, 1]) and torch.equal(b.conv[:, 1], snap["conv"][:, 1])
+    assert torch.equal(b.ssm[:, 0], a.ssm[:, 0]) and torch.equal(b.ssm[:, 2], a.ssm[:, 2])
+    # row 1 wrote no KV row (its position-5 slot still holds what it held), rows 0 and 2 did
+    for cache, key in ((b.k_cache, "k"), (b.v_cache, "v")):
+        blk, off = int(b.bt[1][5 // b.kv_block]), 5 % b.kv_block
+        assert torch.equal(cache[:, blk, :, off], snap[key][:, blk, :, off])
+        blk0 = int(b.bt[0][5 // b.kv_block])
+        assert not torch.equal(cache[:, blk0, :, off], snap[key][:, blk0, :, off])
+    # the next step: row 1 gets the token it missed, the others move on
+    nxt = torch.tensor([prompts[0][6], prompts[1][5], prompts[2][6]], device="cuda")
+    lb2 = b.step(nxt).clone()
+    b.check()
+    assert torch.equal(lb2[1], la[1])
+    assert b.pos[:M].tolist() == [7, 6, 7]
+
+
 def test_two_engines_share_one_set_of_packed_weights(model):
     W, PK = model
     a, b = Engine(PK, 2, maxlen=64), Engine(PK, 2, maxlen=64)

@@ -158,6 +158,34 @@ def test_steps_track_the_oracle_and_generate_equals_stepping(model, M, exact):
     assert torch.equal(gen_logits, eng.logits)
 
 
+def test_a_padding_row_keeps_its_state_and_selects_no_expert(model):
+    """`valid[m] = False` (`qwen3.6-35b-a3b-gfx942/mk/runner.py:187-192`): the other rows' logits do not change, the row's
+    state and position stay, and caught up one step later it gives what it would have given."""
+    W, PK = model
+    M = 3
+    prompts = [make_prompt(SMALL.vocab, 8, seed=90 + j) for j in range(M)]
+    a, b = Engine(PK, M, maxlen=64), Engine(PK, M, maxlen=64)
+    for t in range(4):
+        tok = torch.tensor([p[t] for p in prompts], device="cuda")
+        a.step(tok)
+        b.step(tok)
+    snap_ssm, snap_conv = b.ssm.clone(), b.conv.clone()
+    tok = torch.tensor([p[4] for p in prompts], device="cuda")
+    la = a.step(tok).clone()
+    lb = b.step(tok, valid=torch.tensor([True, False, True])).clone()
+    b.check()
+    # the routed stages add the experts' partial tiles in slot order; with row 1's experts gone the slots of the
+    # others shift, their order does not, and what they add for rows 0 and 2 is the same
+    assert float((la[[0, 2]] - lb[[0, 2]]).abs().max()) <= 1e-5 * float(la.abs().max())
+    assert b.pos[:M].tolist() == [5, 4, 5]
+    assert torch.equal(b.ssm[:, 1], snap_ssm[:, 1]) and torch.equal(b.conv[:, 1], snap_conv[:, 1])
+    nxt = torch.tensor([prompts[0][5], prompts[1][4], prompts[2][5]], device="cuda")
+    lb2 = b.step(nxt).clone()
+    b.check()
+    assert float((lb2[1] - la[1]).abs().max()) <= 1e-5 * float(la.abs().max())
+    assert b.pos[:M].tolist() == [6, 5, 6]
+
+
 def test_exact_inputs_follow_the_exact_mode_closely(model):
     W, PK = model
     M = 2

@@ -41,7 +41,7 @@ def test_queries_follow_the_header_order(lib_built):
 def test_struct_layouts_match_the_c_compiler(lib_built, tmp_path):
     if not shutil.which("gcc"):
         pytest.skip("no C compiler")
-    fields = ["program", "n_steps", "tok", "barrier_base", "spin_limit_ns", "tp", "mailbox", "ar_base", "grid", "tokens_in", "xs_bytes", "n_tokens_in"]
+    fields = ["program", "n_steps", "tok", "barrier_base", "spin_limit_ns", "tp", "mailbox", "ar_base", "grid", "tokens_in", "xs_bytes", "n_tokens_in", "row_valid"]
     src = tmp_path / "layout.c"
     src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "mk_stage.h"\nint main(void) {\n'
                    '  printf("%zu %zu %zu %zu %zu ", sizeof(mk_stage_desc), offsetof(mk_stage_desc, i), offsetof(mk_stage_desc, f), '
