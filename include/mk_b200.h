@@ -164,6 +164,9 @@ int mk_launch(mk_engine* e, const mk_launch_args* args, void* stream);
  *
  *  - The first call on a device looks up the array's device address and caches it; make that first
  *    call outside any stream capture.
+ *  - Such a host need not own hand-off buffers at all: mk_set_params accepts an engine whose MK_G_XL, MK_G_PROJL,
+ *    MK_G_MIXL, MK_G_ACTL, MK_G_LML, MK_G_ATTN_PART and MK_G_PARTL are all 0 (all of them, or none).  mk_launch
+ *    and mk_launch_batch refuse that engine with MK_ERR_BADARG; mk_launch_static runs it.
  *  - A grid or shape whose hand-off words do not fit the array is refused with MK_ERR_BADARG.
  *  - Every call clears the array on `stream` before the kernel runs, because all calls (of all
  *    engines) share it and it keeps what the last call wrote.  Two calls that overlap on the GPU

@@ -190,7 +190,7 @@ enum {
     MKS_P_K_CACHE, MKS_P_V_CACHE,   /* [pages][kv heads][64][head dim]                             */
     MKS_P_BLOCK_TABLE,   /* int32 [M][max pages]                                                   */
     MKS_P_ROPE_COS, MKS_P_ROPE_SIN, /* fp32 [max_seq][pairs]                                       */
-    MKS_P_A_PART,        /* fp32 split partials [M][kv heads][max chunks][q per kv * (head dim + 2)], then
+    MKS_P_A_PART,        /* fp32 split partials [M][kv heads][max chunks][q per kv * (head dim + 2), rounded up to 4], then
                             per-CTA scratch [grid][16][q per kv][128]                               */
     MKS_P_A_CNT,         /* u32 [M][kv heads]                                                      */
 

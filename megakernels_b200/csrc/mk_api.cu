@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/mk_b200.h"
@@ -16,6 +17,7 @@ struct mk_engine {
     mk_model_desc desc;
     int n_sm;
     bool params_set;
+    bool static_only;    // the parameter block came without hand-off buffers: only mk_launch_static may run
     Params host;         // the parameter block; every launch passes it to the kernel by value
 };
 
@@ -110,6 +112,7 @@ extern "C" int mk_create(const mk_model_desc* d, mk_engine** out) {
     if (e->desc.grid == 0) e->desc.grid = n_sm;
     e->n_sm = n_sm;
     e->params_set = false;
+    e->static_only = false;
     memset(&e->host, 0, sizeof e->host);
     *out = e;
     return MK_OK;
@@ -173,11 +176,17 @@ extern "C" int mk_set_params(mk_engine* e, const int64_t* layers, int64_t n_laye
     if (bad16(p.embed) || bad16(p.lm_head)) return fail(MK_ERR_BADARG, "embedding / LM head null or not 16-byte aligned");
     if (q8 && (!p.embed_scale || !p.lm_scale)) return fail(MK_ERR_BADARG, "int8 embedding / LM head without scales");
     if (!p.final_norm || !p.rope_cos || !p.rope_sin) return fail(MK_ERR_BADARG, "final norm / RoPE tables missing");
-    if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.lml) || bad16(p.partl))
-        return fail(MK_ERR_BADARG, "activation word buffers null or not 16-byte aligned");
-    // the MLP activation words are a hand-off of the batched kernel only: mk_launch_batch refuses an engine without them
-    if (p.actl != nullptr && bad16(p.actl)) return fail(MK_ERR_BADARG, "MLP activation words not 16-byte aligned");
-    if (!p.attn_part || !p.block_table || !p.status) return fail(MK_ERR_BADARG, "attention scratch / block table / status missing");
+    // A host that may not allocate passes none of the hand-off buffers: mk_launch_static brings its own.
+    const bool no_handoff = !p.xl && !p.projl && !p.mixl && !p.actl && !p.lml && !p.partl && !p.attn_part;
+    if (!no_handoff) {
+        if (bad16(p.xl) || bad16(p.projl) || bad16(p.mixl) || bad16(p.lml) || bad16(p.partl))
+            return fail(MK_ERR_BADARG, "activation word buffers null or not 16-byte aligned (all of them, or none for a static-only engine)");
+        // the MLP activation words are a hand-off of the batched kernel only: mk_launch_batch refuses an engine without them
+        if (p.actl != nullptr && bad16(p.actl)) return fail(MK_ERR_BADARG, "MLP activation words not 16-byte aligned");
+        if (!p.attn_part) return fail(MK_ERR_BADARG, "attention scratch missing");
+    }
+    if (!p.block_table || !p.status) return fail(MK_ERR_BADARG, "block table / status missing");
+    e->static_only = no_handoff;
     e->params_set = true;
     return MK_OK;
 }
@@ -202,6 +211,7 @@ static kernel_fn pick_kernel(const mk_model_desc& d, bool spec = false) {
 extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
     if (!e || !a) return fail(MK_ERR_BADARG, "mk_launch: null argument");
     if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch: mk_set_params has not succeeded on this engine");
+    if (e->static_only) return fail(MK_ERR_BADARG, "mk_launch: this engine was given no hand-off buffers; only mk_launch_static can run it");
     const bool spec = a->spec != 0;
     if (spec) {
         // n_steps counts cycles; a cycle feeds two positions and may emit two tokens
@@ -279,7 +289,7 @@ extern "C" int mk_launch(mk_engine* e, const mk_launch_args* a, void* stream) {
 // once per device, and is what the kernel's parameter block receives.
 static __device__ __align__(256) unsigned char g_static_scratch[MK_STATIC_SCRATCH_BYTES];
 static constexpr int MAX_DEVICES = 64;
-static unsigned char* g_static_addr[MAX_DEVICES] = {};
+static std::atomic<unsigned char*> g_static_addr[MAX_DEVICES] = {};
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -323,17 +333,17 @@ extern "C" int mk_launch_static(mk_engine* e, const mk_launch_args* a, void* str
                     grid, off, (unsigned)MK_STATIC_SCRATCH_BYTES);
 
     MK_CUDA(cudaSetDevice(dev));
-    if (!g_static_addr[dev]) {
+    if (!g_static_addr[dev].load(std::memory_order_acquire)) {
         // set-up, once per device, with that device current
         std::lock_guard<std::mutex> lk(g_mu);
-        if (!g_static_addr[dev]) {
+        if (!g_static_addr[dev].load(std::memory_order_relaxed)) {
             void* p = nullptr;
             MK_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
             if (!p) return fail(MK_ERR_CUDA, "mk_launch_static: the built-in array has no device address");
-            g_static_addr[dev] = static_cast<unsigned char*>(p);
+            g_static_addr[dev].store(static_cast<unsigned char*>(p), std::memory_order_release);
         }
     }
-    unsigned char* base = g_static_addr[dev];
+    unsigned char* base = g_static_addr[dev].load(std::memory_order_acquire);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // the engine's parameter block with the hand-off words redirected into the array
     Params p = e->host;
@@ -382,6 +392,7 @@ extern "C" int mk_launch_batch(mk_engine* e, const mk_batch_args* a, void* strea
     typedef Qwen35_08B S;
     if (!e || !a) return fail(MK_ERR_BADARG, "mk_launch_batch: null argument");
     if (!e->params_set) return fail(MK_ERR_BADARG, "mk_launch_batch: mk_set_params has not succeeded on this engine");
+    if (e->static_only) return fail(MK_ERR_BADARG, "mk_launch_batch: this engine was given no hand-off buffers; only mk_launch_static can run it");
     if (e->desc.quant != MK_QUANT_INT8) return fail(MK_ERR_UNSUPPORTED, "mk_launch_batch: batched decoding is built for int8 weights only");
     if (a->batch < 1 || a->batch > NB) return fail(MK_ERR_BADARG, "mk_launch_batch: batch %d out of [1, %d]", a->batch, NB);
     if (a->batch > (e->desc.max_batch > 1 ? e->desc.max_batch : 1))

@@ -287,7 +287,7 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
     const float norm_off = d.i[MKS_I_NORM_PLAIN] ? 0.f : 1.f;
     const bool q_bf16 = d.i[MKS_I_Q_BF16] != 0;
     const int esz = KVF32 ? 4 : 2;
-    const int rec = QPK * (HD + 2);                            // floats of one chunk's partial record
+    const int rec = (QPK * (HD + 2) + 3) & ~3;                 // floats of one chunk's partial record (whole float4s: QPK may be odd)
     const int max_chunks = d.i[MKS_I_MAX_CHUNKS];
     // this CTA's rows behind the partial records: [16 warps][QPK][128] sums of the P x V pieces
     float* scratch = part + (size_t)S.A.M * NKV * max_chunks * rec + (size_t)cta_() * NCW * QPK * 128;

@@ -172,17 +172,45 @@ __device__ void stage_planes(const Args& A, uint8_t* xs, uint8_t* sfb, int slice
         if (!live || !(mx > 0.f) || e < -100 || e > 100) continue;  // a zero block stays zero (no shuffle follows)
         const float up = __uint_as_float((uint32_t)(127 + 2 * P - 1 - e) << 23);
         const uint32_t qmax = (1u << (2 * P)) - 1u;
-        uint32_t q[8];
+        // word i: the eight values' digit p in nibble p (two-bit digits spread to nibbles), the sign in every nibble
+        uint32_t y[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) q[i] = min(__float2uint_rn(v[i] * up), qmax);
-        for (int p = 0; p < P; p++) {
-            uint32_t word = sign;
-#pragma unroll
-            for (int i = 0; i < 8; i++) word |= ((q[i] >> (2 * p)) & 3u) << (4 * i);
-            const int n = p * A.mp + m;
-            *reinterpret_cast<uint32_t*>(xs + ((size_t)(n >> 3) * nblk + kb) * 128 + (n & 7) * 16 + quarter * 4) = word;
-            if (quarter == 0) sfb[(kb >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (kb & 3)] = (uint8_t)(127 + e + 2 - 2 * P + 2 * p);
+        for (int i = 0; i < 8; i++) {
+            uint32_t x = min(__float2uint_rn(v[i] * up), qmax);
+            x = (x | (x << 8)) & 0x00FF00FFu;
+            x = (x | (x << 4)) & 0x0F0F0F0Fu;
+            x = (x | (x << 2)) & 0x33333333u;
+            y[i] = x | ((sign >> (4 * i + 3)) & 1u ? 0x88888888u : 0u);
         }
+        // 8 x 8 nibble transpose: afterwards word p holds plane p's eight nibbles, value i in nibble i
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t lo = __byte_perm(y[i], y[i + 4], 0x5410), hi = __byte_perm(y[i], y[i + 4], 0x7632);
+            y[i] = lo;
+            y[i + 4] = hi;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i += 4)
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const uint32_t lo = __byte_perm(y[i + j], y[i + j + 2], 0x6240), hi = __byte_perm(y[i + j], y[i + j + 2], 0x7351);
+                y[i + j] = lo;
+                y[i + j + 2] = hi;
+            }
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const uint32_t lo = (y[i] & 0x0F0F0F0Fu) | ((y[i + 1] & 0x0F0F0F0Fu) << 4);
+            const uint32_t hi = ((y[i] >> 4) & 0x0F0F0F0Fu) | (y[i + 1] & 0xF0F0F0F0u);
+            y[i] = lo;
+            y[i + 1] = hi;
+        }
+#pragma unroll
+        for (int p = 0; p < 8; p++)
+            if (p < P) {
+                const int n = p * A.mp + m;
+                *reinterpret_cast<uint32_t*>(xs + ((size_t)(n >> 3) * nblk + kb) * 128 + (n & 7) * 16 + quarter * 4) = y[p];
+                if (quarter == 0) sfb[(kb >> 2) * 512 + (n & 31) * 16 + (n >> 5) * 4 + (kb & 3)] = (uint8_t)(127 + e + 2 - 2 * P + 2 * p);
+            }
     }
 }
 

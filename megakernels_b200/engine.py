@@ -263,6 +263,7 @@ class Megakernel:
                               draft_vocab=self.draft_vocab, device=device.index, grid=self.grid, max_batch=batch)
         self._h = ctypes.c_void_p()
         _lib.check(self.lib.mk_create(ctypes.byref(desc), ctypes.byref(self._h)))
+        self._tables = (list(layer_vals), list(mtp_vals) if mtp_vals else None, dict(g))     # what mk_set_params was given
         lv, gv = _lib.i64_array(layer_vals), _lib.i64_array([g[f] for f in _lib.GLOBAL_FIELDS])
         mv = _lib.i64_array(mtp_vals) if mtp_vals else None
         _lib.check(self.lib.mk_set_params(self._h, lv, len(lv), mv, len(mv) if mv else 0, gv, len(gv)))

@@ -85,7 +85,7 @@ class Engine:
             mc = -(-span // cp) + 1
             qpk = s.nq // nkv
             tag = "f" if full else "s"
-            part = pr.region(f"attn_{tag}.part", M * nkv * mc * qpk * (hd + 2) + grid * 16 * qpk * 128, torch.float32)
+            part = pr.region(f"attn_{tag}.part", M * nkv * mc * (-(-qpk * (hd + 2) // 4) * 4) + grid * 16 * qpk * 128, torch.float32)
             cnt = pr.region(f"attn_{tag}.cnt", M * nkv, torch.int32)
             geo[full] = (cp, mc, part, cnt)
         plain = dict(norm_off=0.0, eps=s.eps)                      # this model's norm weights are the factors themselves

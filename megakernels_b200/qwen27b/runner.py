@@ -99,7 +99,7 @@ class Engine:
         qpk = d.nq // d.nkv
         cp = self.chunk_pos = attn_chunk(self.maxlen, M * d.nkv, grid)
         max_chunks = -(-self.maxlen // cp)
-        a_part = pr.region("attn.part", M * d.nkv * max_chunks * qpk * (HD + 2) + grid * 16 * qpk * 128, torch.float32)
+        a_part = pr.region("attn.part", M * d.nkv * max_chunks * (-(-qpk * (HD + 2) // 4) * 4) + grid * 16 * qpk * 128, torch.float32)
         a_cnt = pr.region("attn.cnt", M * d.nkv, torch.int32)
         ar = tp > 1
 

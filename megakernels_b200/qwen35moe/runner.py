@@ -79,7 +79,7 @@ class Engine:
         qpk = s.nq // s.nkv
         cp = self.chunk_pos = attn_chunk(self.maxlen, M * s.nkv, grid)
         max_chunks = -(-self.maxlen // cp)
-        a_part = pr.region("attn.part", M * s.nkv * max_chunks * qpk * (HD + 2) + grid * 16 * qpk * 128, torch.float32)
+        a_part = pr.region("attn.part", M * s.nkv * max_chunks * (-(-qpk * (HD + 2) // 4) * 4) + grid * 16 * qpk * 128, torch.float32)
         a_cnt = pr.region("attn.cnt", M * s.nkv, torch.int32)
         pieces = 2 if exact_inputs else 1
         pc = lambda meta: pieces                                              # noqa: E731

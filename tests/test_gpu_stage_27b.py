@@ -175,6 +175,24 @@ def test_a_padding_row_keeps_its_state_and_leaves_the_other_rows_alone(model):
     assert b.pos[:M].tolist() == [7, 6, 7]
 
 
+def test_three_query_heads_per_kv_head_as_a_rank_of_eight_has_them():
+    """At TP 8 a rank holds 3 query heads and one (replicated) KV head: an odd number of heads per attention record."""
+    shape = SMALL.with_(nq=3, nkv=1)
+    W = SynthWeights(shape, layers=4, init="realistic", device="cuda", fmt="mxfp4")
+    eng = Engine(Packed(W, "cuda"), 3, maxlen=256)
+    st = O.State(shape, 3, 256, layers=4, device="cuda")
+    prompts = [make_prompt(shape.vocab, 140, seed=70 + j) for j in range(3)]
+    for t in range(140):                                   # past 128 positions: several chunks, odd and even record indices
+        tok = torch.tensor([p[t] for p in prompts], device="cuda")
+        got = eng.step(tok)
+        if t % 20 == 19 or t >= 136:
+            want = O.step(shape, W, tok, st, layers=4)
+            assert float((got - want).abs().max()) < LOGIT_TOL, f"step {t}"
+        else:
+            O.step(shape, W, tok, st, layers=4, lm_head=False)
+    eng.check()
+
+
 def test_two_engines_share_one_set_of_packed_weights(model):
     W, PK = model
     a, b = Engine(PK, 2, maxlen=64), Engine(PK, 2, maxlen=64)

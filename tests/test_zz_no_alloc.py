@@ -66,6 +66,33 @@ def test_static_scratch_launch_matches_ordinary_launch_twice_in_a_row(quant, lib
     assert mk.run(prompt, n_generate=12) == ids_a1
 
 
+def test_an_engine_without_hand_off_buffers_runs_only_through_the_static_entry_point(lib_built):
+    """The host that may not allocate passes 0 for all seven hand-off buffers; the results are those of an ordinary engine."""
+    from megakernels_b200.engine import Megakernel
+    cfg = qwen35_08b(n_layers=4, vocab=4096)
+    w = make_weights(cfg, 0, init="realistic")
+    mk = Megakernel((cfg, w), max_seq=256, quant="int8")
+    prompt = make_prompt(cfg, 40)
+    want = mk.run(prompt, n_generate=10)
+    mk.reset()
+    lv, mv, g = mk._tables
+    bare = dict(g)
+    for name in ("xl", "projl", "mixl", "actl", "lml", "attn_part", "partl"):
+        bare[name] = 0
+    gv = _lib.i64_array([bare[f] for f in _lib.GLOBAL_FIELDS])
+    _lib.check(mk.lib.mk_set_params(mk._h, _lib.i64_array(lv), len(lv), None, 0, gv, len(gv)))
+    got, _ = launch_static(mk, prompt, 10)
+    assert got == want
+    with pytest.raises(_lib.MkError, match="hand-off"):
+        mk.reset()
+        mk.run(prompt, n_generate=2)
+    # some but not all of them is a mistake, not a static-only engine
+    bare["xl"] = g["xl"]
+    gv = _lib.i64_array([bare[f] for f in _lib.GLOBAL_FIELDS])
+    with pytest.raises(_lib.MkError, match="all of them, or none"):
+        _lib.check(mk.lib.mk_set_params(mk._h, _lib.i64_array(lv), len(lv), None, 0, gv, len(gv)))
+
+
 def test_static_scratch_refuses_what_does_not_fit(lib_built):
     from megakernels_b200.engine import Megakernel
     cfg = qwen35_08b(n_layers=4, vocab=4096)
