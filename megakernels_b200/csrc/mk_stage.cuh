@@ -455,7 +455,7 @@ __device__ __forceinline__ int xs_stride_bytes(int kc) { return ((kc * 2 + 127) 
 // What matters here is the number of dependent L2 round trips (about 0.7 us each on this part), not
 // bytes: the first batch of input loads, the norm weights and the sums of squares behind 1/rms are all
 // requested before anything is awaited; the values go to shared memory as bf16 and are rescaled there.
-constexpr int XB = 4;       // float4 groups a thread keeps in flight per batch
+constexpr int XB = 2;       // float4 groups of one batch; two batches are in flight
 
 __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d, int grp, int split) {
     const int kc = d.i[MKS_I_KC], fmt = d.i[MKS_I_FMT], pieces = d.i[MKS_I_PIECES], M = S.A.M;
@@ -469,18 +469,21 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     const int k4n = kc >> 2, total = M * k4n;
     int* red_i = reinterpret_cast<int*>(S.red);
     if (tid_() < MKS_MAX_BATCH) red_i[tid_()] = 0;
-    float4 xv[XB];
-    auto request = [&](int base) {
+    // two batches in flight: the next one is requested before the current one is used, so a panel of eight
+    // sequences costs one exposed round trip, not one per batch
+    float4 xv[XB], xn[XB];
+    auto request = [&](int base, float4 (&dst)[XB]) {
 #pragma unroll
         for (int u = 0; u < XB; u++) {
             const int idx = base + u * NCT + tid_();
             if (idx < total) {
                 const int m = idx / k4n, k4 = idx - m * k4n;
-                xv[u] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * xstride) + k4);
+                dst[u] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)m * xstride) + k4);
             }
         }
     };
-    request(0);
+    request(0, xv);
+    if (XB * NCT < total) request(XB * NCT, xn);
     if (norm) {
         // 1/rms of every sequence from the 16-element sums of squares of the whole input vector: warp m adds up
         // sequence m's sums (all loads of a lane in flight at once, fixed order) while the other warps only wait for x
@@ -510,7 +513,11 @@ __device__ __noinline__ void stage_x(Shared& S, Mut& mu, const mk_stage_desc& d,
     prof_mark(S, 4);
 #pragma unroll 1
     for (int base = 0; base < total; base += XB * NCT) {
-        if (base) request(base);
+        if (base) {
+#pragma unroll
+            for (int u = 0; u < XB; u++) xv[u] = xn[u];
+            if (base + XB * NCT < total) request(base + XB * NCT, xn);
+        }
 #pragma unroll
         for (int u = 0; u < XB; u++) {
             const int idx = base + u * NCT + tid_();
