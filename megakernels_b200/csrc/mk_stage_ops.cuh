@@ -224,21 +224,32 @@ __device__ __forceinline__ void load8(const void* row, int elem, float (&v)[8]) 
     }
 }
 
-// RMS-norm (optional), rotate and round one head vector; one warp.  `dst` receives HD floats.
-__device__ void head_prepare(Shared& S, Mut& mu, const float* src, float* dst, int HD, const float* nw, float norm_off, bool do_norm,
-                             float eps, const float* cs, const float* sn, int pairs, int pair_dist, bool round_bf16) {
-    float s = 0.f;
-#pragma unroll 1
-    for (int i = lane_(); i < HD; i += 32) {
-        const float v = ldcg_f(src + i);
-        dst[i] = v;
-        s = fmaf(v, v, s);
+// RMS-norm (optional), rotate and round one head vector; one warp.  `dst` receives HD <= 512 floats.  All of a
+// lane's loads are requested before the first is used (one L2 round trip for the vector, one for the weights).
+__device__ __noinline__ void head_prepare(Shared& S, Mut& mu, const float* src, float* dst, int HD, const float* nw, float norm_off, bool do_norm,
+                                          float eps, const float* cs, const float* sn, int pairs, int pair_dist, bool round_bf16) {
+    float v[16], w[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int i = lane_() + 32 * j;
+        v[j] = i < HD ? ldcg_f(src + i) : 0.f;
     }
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int i = lane_() + 32 * j;
+        w[j] = nw && i < HD ? norm_off + __ldg(nw + i) : 1.f;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+        if (lane_() + 32 * j < HD) s = fmaf(v[j], v[j], s);
     s = warp_sum(s);
     const float r = do_norm ? rsqrtf(s / (float)HD + eps) : 1.f;
-    __syncwarp();
-#pragma unroll 1
-    for (int i = lane_(); i < HD; i += 32) dst[i] = dst[i] * r * (nw ? norm_off + nw[i] : 1.f);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int i = lane_() + 32 * j;
+        if (i < HD) dst[i] = v[j] * r * w[j];
+    }
     __syncwarp();
     if (cs) {
 #pragma unroll 1
@@ -339,14 +350,13 @@ __device__ __noinline__ void attn_stage(Shared& S, Mut& mu, const mk_stage_desc&
                 const int page = __ldg(bt + (size_t)m * maxpages + (p >> kvb_shift));
                 const uint32_t off = (uint32_t)page * kv_s_page + (uint32_t)kvh * kv_s_head + (uint32_t)(p & (kvb - 1)) * kv_s_pos;
                 row_s[i] = off;
-                // ask the L2 for the rows now: the weight stream between two attention stages has pushed the cache's
-                // pages out of the TLBs, and the first touch of a page costs several microseconds
-                if (i < ncached) {
-#pragma unroll 1
-                    for (int b = 0; b < HD * esz; b += 128) {
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)off * esz + b));
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)off * esz + b));
-                    }
+                // touch every cache block of the chunk once now: the weight stream between two attention stages has
+                // pushed the cache's pages out of the TLBs, and the first touch of a page costs several microseconds.
+                // (One line per block, not the rows themselves: an SM retires about one L2 prefetch per 25 cycles, and
+                // asking for all 8 lines of all 580 rows of a batch-8 chunk took 60 us.)
+                if (i < ncached && (i == 0 || (p & (kvb - 1)) == 0)) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)off * esz));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)off * esz));
                 }
             }
         }
