@@ -65,6 +65,16 @@ def pack(packed, scales, splits=1):
     return chunks.reshape(rb, splits, cps, CHUNK_BYTES).permute(1, 0, 2, 3).contiguous()
 
 
+def unpack(chunks, rows):
+    """Inverse of `pack`: [splits, row_blocks, chunks_per_split, 8704] -> (packed [rows, k/2], scales [rows, k/32])."""
+    splits, rb, cps, _ = chunks.shape
+    kc = splits * cps
+    c = chunks.permute(1, 0, 2, 3).reshape(rb, kc, CHUNK_BYTES)
+    d = c[..., :8192].reshape(rb, kc, 16, 4, 8, 16).permute(0, 2, 4, 1, 3, 5).reshape(rb * ROWS, kc * 64)
+    s = c[..., 8192:].reshape(rb, kc, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(rb * ROWS, kc * 4)
+    return d[:rows].contiguous(), s[:rows].contiguous()
+
+
 def digit_planes(x, pieces, round_bf16=True):
     """The kernel's decomposition of the inputs, in torch: x [batch, k] -> (digits int [pieces, batch, k] in -3..3,
     exponents int [pieces, batch, k/32]) with x ~ sum_p digits[p] * 0.5 * 2^exponents[p]."""

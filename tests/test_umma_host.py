@@ -66,6 +66,14 @@ def test_packed_chunks_hold_every_value_where_the_header_says(lib_built):
         U.pack(packed, scales, 3)
 
 
+@pytest.mark.parametrize("rows,k,splits", [(128, 128, 1), (200, 512, 2), (1000, 1024, 4), (384, 2176 * 2, 2)])
+def test_unpacking_the_chunks_gives_back_every_byte(rows, k, splits):
+    g = torch.Generator().manual_seed(rows + k)
+    packed, scales = Q.quantize_mxfp4(torch.randn(rows, k, generator=g) * 0.1)
+    back_p, back_s = U.unpack(U.pack(packed, scales, splits), rows)
+    assert torch.equal(back_p, packed) and torch.equal(back_s, scales)
+
+
 @pytest.mark.parametrize("pieces", [4, 6, 8])
 def test_digit_planes_restore_the_bf16_inputs(pieces):
     g = torch.Generator().manual_seed(pieces)
